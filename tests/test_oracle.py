@@ -1,0 +1,224 @@
+"""Pins the CPU oracle: golden vectors generated from the reference's own PyTorch parity
+script (tests/golden/mlp_parity.json), the reference's optimizer known-answer tests, the
+LCG-Xavier init stream, and an independent torch-autograd restatement for every
+activation x optimizer pair."""
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle.oracle import Oracle, apply_update, lcg_xavier
+
+GOLD = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "mlp_parity.json")))
+
+
+def _fixture_handle(opt, real="f32"):
+    o = Oracle(GOLD["layers"], GOLD["activation"], opt, GOLD["batch"], real=real)
+    i = GOLD["init"]
+    o.set_params(0, np.array(i["w1"], np.float32), np.array(i["b1"], np.float32))
+    o.set_params(1, np.array(i["w2"], np.float32), np.array(i["b2"], np.float32))
+    return o
+
+
+def _flat_params(o):
+    ws, bs = o.get_params()
+    return {"w1": ws[0].ravel(), "b1": bs[0].ravel(), "w2": ws[1].ravel(), "b2": bs[1].ravel()}
+
+
+@pytest.mark.parametrize("real", ["f32", "f64"])
+def test_golden_single_sgd_step(real):
+    # tests/pytorch_parity.rs one-step MLP case; expected values: examples/pytorch_parity.py:613-674
+    case = GOLD["cases"]["mlp_train_sgd"]
+    o = _fixture_handle("sgd", real)
+    d = GOLD["dataset"][0]
+    x, y = np.array(d["x"], np.float32), np.array(d["y"], np.float32)
+    o.step(x, y, 0.05)
+    assert abs(o.loss() - case["loss_before"]) < 1e-6
+    dws, dbs = o.get_grads()
+    g = case["gradients"]
+    np.testing.assert_allclose(dws[0].ravel(), g["w1"], atol=1e-6)
+    np.testing.assert_allclose(dbs[0].ravel(), g["b1"], atol=1e-6)
+    np.testing.assert_allclose(dws[1].ravel(), g["w2"], atol=1e-6)
+    np.testing.assert_allclose(dbs[1].ravel(), g["b2"], atol=1e-6)
+    for k, v in _flat_params(o).items():
+        np.testing.assert_allclose(v, case["updated_parameters"][k], atol=1e-6)
+    o.step(x, y, 0.0)  # lr 0: a pure forward/loss evaluation with the updated weights
+    assert abs(o.loss() - case["loss_after"]) < 1e-6
+
+
+@pytest.mark.parametrize("real", ["f32", "f64"])
+@pytest.mark.parametrize("name,opt", [
+    ("sgd", "sgd"), ("adam", "adam"), ("adamw", "adamw"), ("adagrad", "adagrad"),
+    ("long_sgd", "sgd"), ("long_adam", "adam"), ("long_adamw", "adamw")])
+def test_golden_training_loops(name, opt, real):
+    # tolerance 1e-5 as in tests/pytorch_parity.rs:262-281
+    case = GOLD["cases"]["mlp_train_loop_" + name]
+    hp = GOLD["hyper"][name]
+    o = _fixture_handle(opt, real)
+    # torch.optim.AdamW (and the reference's runtime apply_adamw) decays biases as well; the
+    # generated step does not (mlp_train_rust_codegen.rs:966).  Pin the formula in the torch form.
+    o.set_decay_bias(opt == "adamw")
+    trace = []
+    for _ in range(hp["epochs"]):
+        for d in GOLD["dataset"]:
+            o.step(np.array(d["x"], np.float32), np.array(d["y"], np.float32), hp["lr"])
+            trace.append(o.loss())
+    np.testing.assert_allclose(trace, case["loss_trace"], atol=1e-5)
+    for k, v in _flat_params(o).items():
+        np.testing.assert_allclose(v, case["final_parameters"][k], atol=1e-5)
+
+
+def test_optimizer_known_answers():
+    # src/engine/ir/optimizer.rs:676-701: w=1.0, g=0.5, lr=0.1 -> 0.95
+    p, _, _ = apply_update("sgd", [1.0], [0.5], lr=0.1)
+    assert abs(p[0] - 0.95) < 1e-6
+    # src/engine/ir/optimizer.rs:830-862: w=0.5, g=0.1, Adam lr=1e-3 -> ~0.499
+    p, m, v = apply_update("adam", [0.5], [0.1], lr=1e-3, t=1)
+    assert abs(p[0] - 0.499) < 1e-5
+    assert abs(m[0] - 0.01) < 1e-7 and abs(v[0] - 1e-5) < 1e-9
+    # src/engine/ir/optimizer.rs:1010-1044: three SGD steps of lr 0.1 on g=0.5 -> 0.85
+    p = np.array([1.0], np.float32)
+    for _ in range(3):
+        p, _, _ = apply_update("sgd", p, [0.5], lr=0.1)
+    assert abs(p[0] - 0.85) < 1e-6
+
+
+def test_lcg_xavier_stream():
+    # src/engine/ir/codegen/mlp_train_rust_codegen.rs:630-658, restated independently in Python ints
+    layers = [5, 7, 3]
+    ws = lcg_xavier(layers)
+    rng = 42
+    mask = (1 << 64) - 1
+    for (r, c), w in zip(zip(layers[:-1], layers[1:]), ws):
+        lim = np.sqrt(np.float32(6.0) / (np.float32(r) + np.float32(c)), dtype=np.float32)
+        for k in range(r * c):
+            rng = (rng * 6364136223846793005 + 1442695040888963407) & mask
+            f = np.float32((rng >> 11) & ((1 << 53) - 1)) / np.float32(2.0 ** 53)
+            ref = (f * np.float32(2.0) - np.float32(1.0)) * lim
+            assert w.ravel()[k] == ref
+        assert np.all(np.abs(w) <= lim)
+    # a fresh handle holds exactly that stream
+    o = Oracle(layers, "relu", "sgd", 2)
+    hw, hb = o.get_params()
+    for a, b in zip(hw, ws):
+        assert np.array_equal(a, b)
+    assert all(np.all(b == 0) for b in hb)
+
+
+def _torch_act(name, x):
+    if name == "relu":
+        return torch.relu(x)
+    if name == "sigmoid":
+        return torch.sigmoid(x)
+    if name == "tanh":
+        return torch.tanh(x)
+    if name == "leaky_relu":
+        return torch.nn.functional.leaky_relu(x, 0.01)
+    if name == "silu":
+        return torch.nn.functional.silu(x)
+    if name == "gelu":
+        return torch.nn.functional.gelu(x, approximate="tanh")
+    raise ValueError(name)
+
+
+def _torch_opt(name, params, lr):
+    if name == "sgd":
+        return torch.optim.SGD(params, lr=lr)
+    if name == "sgd_momentum":
+        return torch.optim.SGD(params, lr=lr, momentum=0.9)
+    if name == "adam":
+        return torch.optim.Adam(params, lr=lr, betas=(0.9, 0.999), eps=1e-8)
+    if name == "adagrad":
+        return torch.optim.Adagrad(params, lr=lr, eps=1e-8)
+    raise ValueError(name)
+
+
+@pytest.mark.parametrize("act", ["relu", "sigmoid", "tanh", "leaky_relu", "silu", "gelu"])
+@pytest.mark.parametrize("opt", ["sgd", "sgd_momentum", "adam", "adamw", "adagrad"])
+def test_oracle_matches_torch_autograd(act, opt):
+    """Independent fp64 torch restatement of the same step (W is [in x out], MSE is the
+    mean over all elements).  AdamW follows the reference's form w -= lr*(step + wd*w)
+    with decay on weights only (mlp_train_rust_codegen.rs:962-966)."""
+    rs = np.random.RandomState(7)
+    layers, B, steps, lr = [6, 9, 8, 3], 5, 4, 0.02
+    x = rs.randn(B, layers[0]).astype(np.float32)
+    y = rs.randn(B, layers[-1]).astype(np.float32)
+    o = Oracle(layers, act, opt, B, real="f64")
+    ws, bs = o.get_params()
+    tw = [torch.tensor(w, dtype=torch.float64, requires_grad=True) for w in ws]
+    tb = [torch.tensor(rs.randn(*b.shape) * 0.1, dtype=torch.float64, requires_grad=True) for b in bs]
+    for i in range(len(ws)):
+        o.set_params(i, ws[i].astype(np.float32), tb[i].detach().numpy().astype(np.float32))
+    tb = [torch.tensor(b.detach().numpy().astype(np.float32).astype(np.float64), requires_grad=True) for b in tb]
+    if opt == "adamw":
+        topt = torch.optim.Adam(tw + tb, lr=lr, betas=(0.9, 0.999), eps=1e-8)
+    else:
+        topt = _torch_opt(opt, tw + tb, lr)
+    tx, ty = torch.tensor(x, dtype=torch.float64), torch.tensor(y, dtype=torch.float64)
+    for _ in range(steps):
+        h = tx
+        for i in range(len(tw)):
+            h = h @ tw[i] + tb[i]
+            if i < len(tw) - 1:
+                h = _torch_act(act, h)
+        loss = torch.mean((h - ty) ** 2)
+        topt.zero_grad()
+        loss.backward()
+        if opt == "adamw":
+            decay = [w.detach().clone() for w in tw]
+        topt.step()
+        if opt == "adamw":
+            with torch.no_grad():
+                for w, w0 in zip(tw, decay):
+                    w -= lr * 0.01 * w0
+        o.step(x, y, lr)
+        assert abs(o.loss() - float(loss)) < 1e-6 * max(1.0, abs(float(loss)))
+    ows, obs = o.get_params()
+    for a, b in zip(ows, tw):
+        np.testing.assert_allclose(a, b.detach().numpy(), rtol=2e-6, atol=2e-7)
+    for a, b in zip(obs, tb):
+        np.testing.assert_allclose(a, b.detach().numpy(), rtol=2e-6, atol=2e-7)
+
+
+def test_f32_tracks_f64_shadow():
+    rs = np.random.RandomState(3)
+    layers, B = [32, 48, 40, 1], 16
+    x = rs.randn(B, layers[0]).astype(np.float32)
+    y = rs.randn(B, 1).astype(np.float32)
+    a, b = Oracle(layers, "gelu", "adamw", B, "f32"), Oracle(layers, "gelu", "adamw", B, "f64")
+    for _ in range(10):
+        a.step(x, y, 1e-3)
+        b.step(x, y, 1e-3)
+    assert abs(a.loss() - b.loss()) < 1e-5 * abs(b.loss())
+    for wa, wb in zip(a.get_params()[0], b.get_params()[0]):
+        assert np.max(np.abs(wa - wb)) <= 1e-5 * np.max(np.abs(wb))
+
+
+def test_reference_gemm_shim_agrees_with_golden_loops():
+    """The timed flavour (compiled reference gemm_shim.c) must compute the same step."""
+    rs = np.random.RandomState(5)
+    layers, B = [64, 96, 80, 1], 64
+    x = rs.randn(B, layers[0]).astype(np.float32)
+    y = rs.randn(B, 1).astype(np.float32)
+    g, t = Oracle(layers, "relu", "sgd", B), Oracle(layers, "relu", "sgd", B)
+    if t.use_reference_gemm() is None:
+        pytest.skip("no prebuilt reference gemm shim usable on this CPU")
+    for _ in range(5):
+        g.step(x, y, 0.01)
+        t.step(x, y, 0.01)
+    assert abs(g.loss() - t.loss()) < 1e-4 * abs(g.loss())
+    for wa, wb in zip(g.get_params()[0], t.get_params()[0]):
+        assert np.max(np.abs(wa - wb)) <= 1e-5 * np.max(np.abs(wb))
+
+
+def test_set_params_ignores_out_of_range_layer():
+    o = Oracle([3, 4, 2], "relu", "sgd", 2)
+    before = o.get_params()
+    o.set_params(7, np.ones(12, np.float32), np.ones(4, np.float32))
+    o.set_params(-1, np.ones(12, np.float32), np.ones(4, np.float32))
+    after = o.get_params()
+    for a, b in zip(before[0] + before[1], after[0] + after[1]):
+        assert np.array_equal(a, b)
