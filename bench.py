@@ -1,0 +1,356 @@
+#!/usr/bin/env python
+"""Benchmark of the compiled MLP training step on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4] [--impl b200|reference]
+
+One "step" is one full training step (forward, MSE, backward, optimizer update) on one
+batch of seeded synthetic input.  Prints ONE JSON line:
+  value       whole-job samples/s with inputs resident in HBM, timed with CUDA events on the
+              library's own stream, max over ranks
+  e2e         the same metric through the C-ABI step call with pinned HOST inputs (host->device
+              copy of X and Y and a device->host read of the loss inside the timed region)
+  roofline    the dominant kernel against the measured tensor / HBM peak
+  cpu_baseline  the reference's CPU path (its gemm_shim.c, compiled unmodified, under the
+              restated step) timed on this host's cores on a bounded sample (N = 1 only)
+`--impl reference` times only that CPU path and prints the same line shape.
+Under torchrun (N > 1) the global batch is sharded over the ranks (strong scaling).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+L2_BYTES = 126e6
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU every 200 ms while running."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.stop_flag, self.sm, self.reasons, self.sm_max, self.power = index, False, [], set(), None, []
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.dev = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = int(pynvml.nvmlDeviceGetMaxClockInfo(self.dev, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        while not self.stop_flag and self.nv is not None:
+            try:
+                self.sm.append(int(self.nv.nvmlDeviceGetClockInfo(self.dev, self.nv.NVML_CLOCK_SM)))
+                self.power.append(self.nv.nvmlDeviceGetPowerUsage(self.dev) / 1000.0)
+                mask = int(self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.dev))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.2)
+
+    def summary(self):
+        if not self.sm:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(self.sm)), "sm_max_mhz": self.sm_max, "reasons": sorted(self.reasons),
+                "samples": len(self.sm), "power_w_max": max(self.power) if self.power else None}
+
+
+# ------------------------------------------------------------------------------ CPU arm
+def cpu_reference_run(cfg, steps: int, warmup: int, sample_batch: int | None = None):
+    """Times the reference's CPU implementation of the step on a bounded sample of the
+    workload.  Returns the cpu_baseline object and ms/step of the sample."""
+    from oracle.oracle import Oracle
+    from volta_b200 import synth
+
+    layers = list(cfg.layers)
+    # ~10-30 s of CPU work: the shim sustains roughly 10-15 GFLOP/s on one core
+    budget_flops = 2.0e11
+    B = sample_batch or cfg.batch
+    per_step = cfg.flops_per_step(B)
+    while sample_batch is None and B > 64 and per_step * (steps + warmup) > budget_flops:
+        B //= 2
+        per_step = cfg.flops_per_step(B)
+    o = Oracle(layers, cfg.activation, cfg.optimizer, B)
+    flavour = o.use_reference_gemm()
+    kind = "reference" if flavour else "port"
+    ws, bs = synth.kaiming_uniform_weights(layers, 42)
+    for i, (w, b) in enumerate(zip(ws, bs)):
+        o.set_params(i, w, b)
+    x = synth.rows(cfg.x_dist, 1234, 0, B, layers[0])
+    y = synth.rows(cfg.y_dist, 4321, 0, B, layers[-1])
+    for _ in range(warmup):
+        o.step(x, y, cfg.lr)
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        o.step(x, y, cfg.lr)
+        times.append(time.perf_counter() - t0)
+    med = float(np.median(times))
+    sample = "workload %s at batch %d of %d, %d warm-up + %d timed steps, median; GEMMs through the reference's " \
+             "gemm_shim.c (%s build, single thread: its OpenMP branch is not thread-safe), step restated in C" % (
+                 cfg.name, B, cfg.batch, warmup, steps, flavour or "none; oracle loops")
+    base = {"value": B / med, "unit": "samples/s", "cores": 1, "kind": kind, "sample": sample,
+            "ms_per_step_sample": med * 1e3, "sample_batch": B, "gflops": cfg.flops_per_step(B) / med / 1e9,
+            "host_cpus": os.cpu_count(), "loss": o.loss()}
+    o.free()
+    return base, med * 1e3
+
+
+def torch_cpu_run(cfg, B: int, steps: int = 3):
+    """Second CPU line: PyTorch eager on all host cores, as examples/bench_pytorch.py does."""
+    import torch
+    torch.set_num_threads(os.cpu_count() or 1)
+    layers = list(cfg.layers)
+    acts = {"relu": torch.relu, "silu": torch.nn.functional.silu, "sigmoid": torch.sigmoid, "tanh": torch.tanh,
+            "leaky_relu": lambda t: torch.nn.functional.leaky_relu(t, 0.01),
+            "gelu": lambda t: torch.nn.functional.gelu(t, approximate="tanh")}
+    ws = [torch.randn(r, c, requires_grad=True) for r, c in zip(layers[:-1], layers[1:])]
+    bs = [torch.zeros(c, requires_grad=True) for c in layers[1:]]
+    opt = {"sgd": lambda p: torch.optim.SGD(p, lr=cfg.lr), "sgd_momentum": lambda p: torch.optim.SGD(p, lr=cfg.lr, momentum=0.9),
+           "adam": lambda p: torch.optim.Adam(p, lr=cfg.lr), "adamw": lambda p: torch.optim.AdamW(p, lr=cfg.lr),
+           "adagrad": lambda p: torch.optim.Adagrad(p, lr=cfg.lr)}[cfg.optimizer](ws + bs)
+    x, y = torch.randn(B, layers[0]), torch.randn(B, layers[-1])
+    times = []
+    for it in range(steps + 1):
+        t0 = time.perf_counter()
+        h = x
+        for i, (w, b) in enumerate(zip(ws, bs)):
+            h = h @ w + b
+            if i < len(ws) - 1:
+                h = acts[cfg.activation](h)
+        loss = torch.mean((h - y) ** 2)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        if it:
+            times.append(time.perf_counter() - t0)
+    med = float(np.median(times))
+    return {"value": B / med, "unit": "samples/s", "cores": os.cpu_count(), "batch": B, "ms_per_step": med * 1e3}
+
+
+# ------------------------------------------------------------------------------ main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="c4")
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--gemm-path", default="auto", choices=["auto", "ffma", "tensor"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    from volta_b200 import CONFIGS
+    cfg = CONFIGS[args.workload]
+    steps = args.steps if args.steps is not None else (10 if cfg.batch > 4096 else cfg.steps)
+    warmup = max(args.warmup, 0)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    workload_desc = {"workload": "%s: MLP %s, %s, MSE, %s lr=%g, fp32, global batch %d" % (
+        cfg.name, "->".join(map(str, cfg.layers)), cfg.activation, cfg.optimizer, cfg.lr, cfg.batch),
+        "global_batch": cfg.batch, "x_dist": cfg.x_dist, "y_dist": cfg.y_dist,
+        "weights": "Kaiming-uniform, seed 42", "parallelism": "dp%d" % world, "note": cfg.note}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        base, ms = cpu_reference_run(cfg, max(1, min(steps, 5)), min(warmup, 1))
+        line = {"impl": "reference", "metric": "train_samples_per_s", "value": base["value"], "unit": "samples/s",
+                "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": cfg.batch / base["value"] * 1e3,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": workload_desc, "cpu_baseline": base,
+                "e2e": {"value": base["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from volta_b200 import TrainHandle, synth
+    from volta_b200.train import dp_unique_id
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    uid = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        box = [dp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        uid = box[0]
+    assert cfg.batch % world == 0
+    B = cfg.batch // world
+    layers = list(cfg.layers)
+
+    h = TrainHandle(layers, cfg.activation, cfg.optimizer, B, global_batch=cfg.batch, world_size=world, rank=rank,
+                    unique_id=uid, gemm_path=args.gemm_path)
+    ws, bs = synth.kaiming_uniform_weights(layers, 42)
+    for i, (w, b) in enumerate(zip(ws, bs)):
+        h.set_params(i, w, b)
+    del ws, bs
+    x_host = torch.from_numpy(synth.rows(cfg.x_dist, 1234, rank * B, B, layers[0])).pin_memory()
+    y_host = torch.from_numpy(synth.rows(cfg.y_dist, 4321, rank * B, B, layers[-1])).pin_memory()
+    x_dev, y_dev = x_host.cuda(), y_host.cuda()
+    stream = torch.cuda.ExternalStream(h.stream)
+
+    def barrier():
+        h.synchronize()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    working_set = h.arena_bytes
+    flush_needed = working_set < 2 * L2_BYTES
+    flush_buf = torch.empty(int(256e6) // 4, device="cuda") if flush_needed else None
+
+    for _ in range(warmup):
+        h.step(x_dev, y_dev, cfg.lr)
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    # ---- device-resident timing
+    if flush_needed:
+        per = []
+        for _ in range(steps):
+            with torch.cuda.stream(stream):
+                flush_buf.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            h.step(x_dev, y_dev, cfg.lr)
+            e1.record(stream)
+            per.append((e0, e1))
+        barrier()
+        ms_total = sum(a.elapsed_time(b) for a, b in per)
+    else:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            h.step(x_dev, y_dev, cfg.lr)
+        e1.record(stream)
+        barrier()
+        ms_total = e0.elapsed_time(e1)
+    ms_total = max_over_ranks(ms_total)
+    ms_per_step = ms_total / steps
+    value = cfg.batch / (ms_per_step * 1e-3)
+    loss_dev = h.loss()
+
+    # ---- end to end through the host-pointer step call
+    for _ in range(min(warmup, 2)):
+        h.step(x_host, y_host, cfg.lr)
+        h.loss()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        if flush_needed:
+            with torch.cuda.stream(stream):
+                flush_buf.zero_()
+        h.step(x_host, y_host, cfg.lr)
+        last = h.loss()
+    h.synchronize()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+    sampler.stop_flag = True
+    sampler.join(timeout=2)
+    e2e = {"value": cfg.batch / (e2e_s / steps), "unit": "samples/s", "ms_per_step": e2e_s / steps * 1e3,
+           "h2d_bytes_per_step": int(world * 4 * B * (layers[0] + layers[-1])), "d2h_bytes_per_step": int(world * 8),
+           "timer": "host wall clock, max over ranks", "includes_l2_flush": bool(flush_needed)}
+
+    # ---- per-kernel times for the roofline (single GPU only; plain launches, event pairs)
+    peaks = measured_peaks()
+    roofline, kernel_table = None, None
+    if world == 1:
+        agg = {}
+        reps = 3
+        for _ in range(reps):
+            for name, ms, fl, by in h.profile_step(x_dev, y_dev, cfg.lr):
+                a = agg.setdefault(name, [0.0, fl, by])
+                a[0] += ms / reps
+        tot = sum(v[0] for v in agg.values())
+        kernel_table = [{"kernel": k, "ms": round(v[0], 5), "share": round(v[0] / tot, 4),
+                         "tflops": round(v[1] / v[0] / 1e9, 2) if v[1] else None,
+                         "gbs": round(v[2] / v[0] / 1e6, 1)} for k, v in sorted(agg.items(), key=lambda kv: -kv[1][0])]
+        top, tv = max(agg.items(), key=lambda kv: kv[1][0])
+        if "gemm" in top and tv[1] / max(tv[2], 1) > 50:
+            peak = peaks["bf16_tflops_sustained"] / 6.0
+            ach = tv[1] / tv[0] / 1e9
+            roofline = {"kernel": top, "bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
+                        "frac": ach / peak, "traffic": None,
+                        "peak_basis": "%s bf16 sustained %.1f TFLOP/s / 6 (TF32 runs at half the bf16 rate and a "
+                                      "3xTF32 product issues three MMAs); achieved counts logical fp32 flops" % (
+                                          peaks["source"], peaks["bf16_tflops_sustained"])}
+        else:
+            ach = tv[2] / tv[0] / 1e6
+            roofline = {"kernel": top, "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": ach / peaks["hbm_gbs"], "traffic": None,
+                        "peak_basis": "%s STREAM-style copy" % peaks["source"]}
+        gemm_ms = sum(v[0] for k, v in agg.items() if "gemm" in k)
+        gemm_fl = sum(v[1] for k, v in agg.items() if "gemm" in k)
+        roofline["all_gemms_tflops"] = gemm_fl / gemm_ms / 1e9 if gemm_ms else None
+        opt = agg.get("optimizer")
+        if opt:
+            roofline["optimizer_gbs"] = opt[2] / opt[0] / 1e6
+            roofline["optimizer_frac_of_hbm"] = opt[2] / opt[0] / 1e6 / peaks["hbm_gbs"]
+
+    cpu_baseline = None
+    if world == 1 and rank == 0 and not args.no_cpu_baseline:
+        cpu_baseline, _ = cpu_reference_run(cfg, 3, 1)
+        try:
+            cpu_baseline["torch_cpu_eager"] = torch_cpu_run(cfg, cpu_baseline["sample_batch"])
+        except Exception as exc:  # secondary line only
+            cpu_baseline["torch_cpu_eager"] = {"error": str(exc)}
+
+    if rank == 0:
+        line = {"metric": "train_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": world, "steps": steps,
+                "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": dict(workload_desc, per_gpu_batch=B, gemm_path=args.gemm_path,
+                               l2="inputs larger than L2" if not flush_needed else "L2 flushed between steps",
+                               arena_gb=round(working_set / 1e9, 3)),
+                "tflops_logical_fp32": cfg.flops_per_step() / (ms_per_step * 1e-3) / 1e12,
+                "loss": loss_dev, "loss_e2e": last, "e2e": e2e, "gpu_launches": h.kernels_per_step * steps,
+                "kernels_per_step": h.kernels_per_step, "clocks": sampler.summary(), "roofline": roofline,
+                "cpu_baseline": cpu_baseline, "kernels": kernel_table}
+        print(json.dumps(line))
+    h.free()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,166 @@
+/*
+ * libvolta_b200 — C ABI of the B200 (sm_100a) implementation of Volta's compiled MLP
+ * training step.  Plain pointers and sizes only; no C++ or torch types cross this line.
+ *
+ * Two groups of entry points:
+ *
+ *  1. volta_b200_*  — exported by libvolta_b200.so.  A handle-based, topology-agnostic
+ *     restatement of the six functions every Volta training library exports, plus the
+ *     few extensions the GPU build needs (topology passed at run time instead of being
+ *     compiled in, device-resident inputs, data-parallel ranks, error reporting).
+ *
+ *  2. volta_train_* — the reference's own symbol names.  They are exported by the small
+ *     per-model library that `volta-b200-codegen` emits (include/volta_train.h), whose
+ *     bodies forward to group 1 with the model's topology compiled in, exactly as the
+ *     reference compiles one shared object per model.
+ *
+ * Every function cites the reference interface it replaces, as
+ * src/engine/ir/codegen/mlp_train_rust_codegen.rs:<lines> in the Volta source tree.
+ */
+#ifndef VOLTA_B200_H
+#define VOLTA_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VB200_MAX_LAYERS 32
+
+/* Hidden-layer activation (MlpTopology::activation, mlp_train_rust_codegen.rs:268-275). */
+enum { VB200_ACT_RELU = 0, VB200_ACT_SIGMOID = 1, VB200_ACT_TANH = 2, VB200_ACT_LEAKY_RELU = 3,
+       VB200_ACT_SILU = 4, VB200_ACT_GELU = 5 };
+
+/* Optimizer (MlpTopology::optimizer, mlp_train_rust_codegen.rs:263-267).  SGD with
+ * momentum has no counterpart in the reference; it is an extension. */
+enum { VB200_OPT_SGD = 0, VB200_OPT_ADAM = 1, VB200_OPT_ADAMW = 2, VB200_OPT_ADAGRAD = 3,
+       VB200_OPT_SGD_MOMENTUM = 4 };
+
+/* GEMM path selection. AUTO picks the tcgen05 kernel for shapes it supports. */
+enum { VB200_GEMM_AUTO = 0, VB200_GEMM_FFMA = 1, VB200_GEMM_TENSOR = 2 };
+
+/* Error codes (0 = success). The reference reports no errors on this path
+ * (void functions, mlp_train_rust_codegen.rs:670-699); the replacement never traps and
+ * reports through these codes and volta_b200_last_error(). */
+enum { VB200_OK = 0, VB200_ERR_INVALID = 1, VB200_ERR_CUDA = 2, VB200_ERR_OOM = 3, VB200_ERR_NCCL = 4,
+       VB200_ERR_DEVICE_WAIT = 5, VB200_ERR_UNSUPPORTED = 6 };
+
+/* Replaces MlpTopology (mlp_train_rust_codegen.rs:28-39) plus the `batch` argument of
+ * volta_train_init.  Hyper-parameters other than lr are fixed in the reference's
+ * template (beta1 0.9, beta2 0.999, eps 1e-8, AdamW decay 0.01 on weights only,
+ * leaky slope 0.01: mlp_train_rust_codegen.rs:573, 807-813); a zero here selects
+ * those defaults. */
+typedef struct vb200_config {
+    int32_t n_sizes;                   /* number of layer widths (>= 2) */
+    int32_t layers[VB200_MAX_LAYERS];  /* widths L0..Ln */
+    int32_t activation;                /* VB200_ACT_* */
+    int32_t optimizer;                 /* VB200_OPT_* */
+    int32_t batch;                     /* rows this handle processes per step (its shard) */
+    int32_t global_batch;              /* rows over all ranks; 0 = batch */
+    int32_t world_size;                /* data-parallel ranks; 0 or 1 = single GPU */
+    int32_t rank;
+    uint8_t nccl_unique_id[128];       /* from volta_b200_dp_unique_id, same on all ranks */
+    float momentum;                    /* SGD momentum; 0 = 0.9 */
+    float weight_decay;                /* AdamW; 0 = 0.01 */
+    int32_t gemm_path;                 /* VB200_GEMM_* */
+    int32_t use_graph;                 /* 0 = default (captured CUDA graph), 1 = graph, 2 = plain launches */
+    int32_t reserved[8];
+} vb200_config;
+
+typedef struct vb200_handle vb200_handle;
+
+/* volta_train_init(batch) -> Handle*  (mlp_train_rust_codegen.rs:641-667).
+ * Allocates one device arena for the whole handle, initialises weights with the
+ * reference's LCG-Xavier stream (seed 42, :630-638), biases zero, captures the step graph. */
+int volta_b200_create(const vb200_config *cfg, vb200_handle **out);
+
+/* volta_train_free (mlp_train_rust_codegen.rs:689-696). NULL is a no-op. */
+void volta_b200_destroy(vb200_handle *h);
+
+/* volta_train_step(h, X, Y, lr) (mlp_train_rust_codegen.rs:699-994).
+ * X is [batch x L0], Y is [batch x Ln], row-major fp32; each may be a host pointer
+ * (pageable or pinned; copied to the device inside the call) or a device pointer.
+ * The call returns once X and Y have been consumed from host memory; the step itself
+ * completes asynchronously on the handle's stream. */
+int volta_b200_step(vb200_handle *h, const float *X, const float *Y, float lr);
+
+/* volta_train_loss (mlp_train_rust_codegen.rs:686): loss of the last step (computed
+ * before that step's update). Waits for the step to finish. */
+float volta_b200_loss(vb200_handle *h);
+
+/* volta_train_set_params(h, li, w, b) (mlp_train_rust_codegen.rs:670-675).
+ * Host pointers; an out-of-range li is ignored, as in the reference. */
+int volta_b200_set_params(vb200_handle *h, int32_t li, const float *w, const float *b);
+
+/* volta_train_get_params(h, wo, bo) (mlp_train_rust_codegen.rs:678-684).
+ * Fills wo[i], bo[i] (i < n layers) with pointers into a pinned host mirror owned by
+ * the handle; the mirror is refreshed by this call (device -> host copy + wait) and
+ * stays valid until destroy. */
+int volta_b200_get_params(vb200_handle *h, float **wo, float **bo);
+
+/* Test/diagnostic extensions (no counterpart in the reference): gradients of the
+ * last step (same mirror convention), optimizer-state export/import for checkpoints
+ * (the reference cannot export Adam moments, :670-684), and the Adam step counter. */
+int volta_b200_get_grads(vb200_handle *h, float **dwo, float **dbo);
+int64_t volta_b200_state_floats(vb200_handle *h);
+int volta_b200_save_state(vb200_handle *h, float *out, int64_t n, uint64_t *step_out);
+int volta_b200_load_state(vb200_handle *h, const float *in, int64_t n, uint64_t step);
+
+/* Error reporting: last error code / message of this handle (or of the last failed
+ * create when h is NULL).  The message pointer stays valid until the next call. */
+int volta_b200_status(vb200_handle *h);
+const char *volta_b200_last_error(vb200_handle *h);
+
+/* The CUDA stream the handle launches on (a cudaStream_t), so that a harness can
+ * record its own events on it; and a wait for everything queued on it. */
+void *volta_b200_stream(vb200_handle *h);
+int volta_b200_synchronize(vb200_handle *h);
+
+/* Arena introspection: total bytes, and how many kernels one step launches
+ * (graph nodes that are kernels, collectives excluded). */
+int64_t volta_b200_arena_bytes(vb200_handle *h);
+/* The memory plan of a configuration without creating anything (needs no GPU): total
+ * arena bytes, the bytes it would take without reuse, and optionally one text line per
+ * buffer, "name offset bytes first_use last_use persistent".  Mirrors what Volta's
+ * memory planner reports (src/engine/ir/memory_planner.rs:47-144). */
+int volta_b200_plan(const vb200_config *cfg, int64_t *arena_bytes, int64_t *unshared_bytes, char *report,
+                    int64_t report_len);
+int32_t volta_b200_kernels_per_step(vb200_handle *h);
+
+/* Runs one step as plain launches with a CUDA event pair around every kernel and
+ * returns up to `max` records: name (<= 47 chars), milliseconds, algorithmic flops and
+ * bytes of that launch. Returns the number of records, or a negative error code. */
+typedef struct vb200_kernel_record {
+    char name[48];
+    float ms;
+    double flops;
+    double bytes;
+} vb200_kernel_record;
+int volta_b200_profile_step(vb200_handle *h, const float *X, const float *Y, float lr,
+                            vb200_kernel_record *out, int32_t max);
+
+/* Data-parallel bootstrap: rank 0 obtains an id and hands the same 128 bytes to every
+ * rank's config (any host transport).  Uses NCCL, loaded at run time. */
+int volta_b200_dp_unique_id(uint8_t out[128]);
+
+/* Stand-alone kernel entry points on device pointers (used by parity tests to check
+ * single kernels against the oracle; `stream` is a cudaStream_t or NULL). */
+int volta_b200_optimizer_apply(int32_t optimizer, float *p, float *s1, float *s2, const float *g, int64_t n,
+                               int64_t n_decay, float lr, float weight_decay, float momentum, uint64_t t,
+                               void *stream);
+/* C[m x n] = op(A) . op(B): layout 0 = NN (A[m x k], B[k x n]), 1 = NT (A[m x k], B[n x k]),
+ * 2 = TN (A[k x m], B[k x n]); path is VB200_GEMM_*. */
+int volta_b200_gemm(int32_t layout, int32_t path, float *C, const float *A, const float *B, int64_t m,
+                    int64_t n, int64_t k, void *stream);
+/* out[j] = sum over rows of in[rows x cols] in a fixed order; scratch must hold
+ * volta_b200_colsum_scratch_floats(rows, cols) floats. */
+int64_t volta_b200_colsum_scratch_floats(int64_t rows, int64_t cols);
+int volta_b200_colsum(float *out, const float *in, int64_t rows, int64_t cols, float *scratch, void *stream);
+
+const char *volta_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VOLTA_B200_H */

@@ -29,7 +29,7 @@ REF = os.path.join(HERE, "_ref")
 REFERENCE_ROOT = os.environ.get("VOLTA_REFERENCE_ROOT", "/root/reference")
 SHIM_SRC = os.path.join(REFERENCE_ROOT, "src", "engine", "ir", "codegen", "gemm_shim.c")
 
-STRICT = ["-O2", "-fPIC", "-shared", "-std=c11", "-ffp-contract=off", "-fno-fast-math",
+STRICT = ["-O3", "-mavx2", "-fPIC", "-shared", "-std=c11", "-ffp-contract=off", "-fno-fast-math",
           "-fno-unsafe-math-optimizations", "-Wall", "-Wno-unused-function"]
 
 

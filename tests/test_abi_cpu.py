@@ -1,0 +1,105 @@
+"""CPU-side checks of the C-ABI boundary: the library loads, exports every symbol the
+header declares, plans memory without a GPU, and refuses to run without one."""
+import ctypes as C
+import os
+import re
+
+import pytest
+import torch
+
+from volta_b200 import CONFIGS, VoltaB200Error, load_library
+from volta_b200.lib import EXPORTS, Config
+from volta_b200.train import ACTIVATIONS, OPTIMIZERS, TrainHandle
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "volta_b200.h")).read()
+    return sorted(set(re.findall(r"\b(volta_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = load_library()
+    declared = _declared_symbols()
+    assert len(declared) >= 20
+    for name in declared:
+        assert hasattr(lib, name), "libvolta_b200.so does not export %s" % name
+    assert sorted(EXPORTS) == declared, "volta_b200/lib.py and include/volta_b200.h disagree"
+    assert b"sm_100a" in lib.volta_b200_version()
+
+
+def _cfg(cfg, batch=None, world=1):
+    c = Config()
+    c.n_sizes = len(cfg.layers)
+    for i, v in enumerate(cfg.layers):
+        c.layers[i] = v
+    c.activation = ACTIVATIONS[cfg.activation]
+    c.optimizer = OPTIMIZERS[cfg.optimizer]
+    c.batch = (batch or cfg.batch) // world
+    c.global_batch = batch or cfg.batch
+    c.world_size = world
+    return c
+
+
+def _plan(c):
+    lib = load_library()
+    total, unshared = C.c_int64(), C.c_int64()
+    report = C.create_string_buffer(1 << 16)
+    rc = lib.volta_b200_plan(C.byref(c), C.byref(total), C.byref(unshared), report, len(report))
+    assert rc == 0, lib.volta_b200_last_error(None)
+    bufs = []
+    for line in report.value.decode().splitlines():
+        name, off, size, first, last, pers = line.split()
+        bufs.append((name, int(off), int(size), int(first), int(last), int(pers)))
+    return total.value, unshared.value, bufs
+
+
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_memory_plan_has_no_live_overlap(name):
+    total, unshared, bufs = _plan(_cfg(CONFIGS[name]))
+    assert total <= unshared
+    for i, a in enumerate(bufs):
+        assert a[1] % 1024 == 0 and a[1] + a[2] <= total
+        for b in bufs[i + 1:]:
+            live = a[5] or b[5] or (a[3] <= b[4] and b[3] <= a[4])
+            if live:
+                assert a[1] + a[2] <= b[1] or b[1] + b[2] <= a[1], (a, b)
+
+
+def test_memory_plan_reuses_temporaries_and_fits_one_gpu():
+    total, unshared, bufs = _plan(_cfg(CONFIGS["c5"]))
+    assert total < unshared            # deltas and activations share storage
+    assert total < 170e9               # the largest configuration fits one 180 GB GPU
+    temps = [b for b in bufs if not b[5]]
+    assert any(a[1] == b[1] for i, a in enumerate(temps) for b in temps[i + 1:])
+    # sharded over 8 ranks the activations shrink 8x, parameters do not
+    total8, _, _ = _plan(_cfg(CONFIGS["c5"], world=8))
+    assert total8 < total
+
+
+def test_plan_rejects_bad_configs():
+    lib = load_library()
+    c = _cfg(CONFIGS["c1"])
+    c.n_sizes = 1
+    assert lib.volta_b200_plan(C.byref(c), None, None, None, 0) != 0
+    c = _cfg(CONFIGS["c1"])
+    c.optimizer = 17       # e.g. RMSprop: outside the generated step's list (executor.rs:3147-3189)
+    assert lib.volta_b200_plan(C.byref(c), None, None, None, 0) == 6
+    c = _cfg(CONFIGS["c1"])
+    c.batch = 0
+    assert lib.volta_b200_plan(C.byref(c), None, None, None, 0) == 1
+
+
+def test_unsupported_names_are_rejected_before_the_library_is_called():
+    with pytest.raises(VoltaB200Error):
+        TrainHandle([4, 4, 1], "relu", "rmsprop", 2)
+    with pytest.raises(VoltaB200Error):
+        TrainHandle([4, 4, 1], "softplus", "sgd", 2)
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU behaviour")
+def test_create_fails_loudly_without_a_gpu():
+    with pytest.raises(VoltaB200Error) as e:
+        TrainHandle([4, 4, 1], "relu", "sgd", 2)
+    assert "no CPU fallback" in str(e.value)

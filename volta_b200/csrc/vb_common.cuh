@@ -1,0 +1,163 @@
+// Shared declarations of libvolta_b200: error helpers, the epilogue descriptor that every
+// GEMM kernel applies to its accumulators, and the device-side activation math.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/volta_b200.h"
+
+namespace vb {
+
+// ---------------------------------------------------------------------------------------
+// Activation math, following the reference's generated helpers
+// (src/engine/ir/codegen/mlp_train_rust_codegen.rs:563-596, 725-743, 894-916).
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+__device__ __forceinline__ float act_forward(int act, float x) {
+    switch (act) {
+    case VB200_ACT_RELU: return x > 0.0f ? x : 0.0f;
+    case VB200_ACT_SIGMOID: return sigmoidf_(x);
+    case VB200_ACT_TANH: return tanhf(x);
+    case VB200_ACT_LEAKY_RELU: return x > 0.0f ? x : 0.01f * x;
+    case VB200_ACT_SILU: return x * sigmoidf_(x);
+    case VB200_ACT_GELU: {
+        const float c = 0.7978845608f, k = 0.044715f;
+        float v = c * (x + k * x * x * x);
+        return 0.5f * x * (1.0f + tanhf(v));
+    }
+    }
+    return x;
+}
+
+// `saved` is whatever the forward pass kept for this activation: the pre-activation for
+// silu/gelu, the post-activation for relu/leaky (same sign as the pre-activation, so the
+// reference's `pre > 0` mask is reproduced exactly) and for sigmoid/tanh (whose
+// derivatives the reference also takes from the post-activation).
+__device__ __forceinline__ float act_backward(int act, float saved) {
+    switch (act) {
+    case VB200_ACT_RELU: return saved > 0.0f ? 1.0f : 0.0f;
+    case VB200_ACT_SIGMOID: return saved * (1.0f - saved);
+    case VB200_ACT_TANH: return 1.0f - saved * saved;
+    case VB200_ACT_LEAKY_RELU: return saved > 0.0f ? 1.0f : 0.01f;
+    case VB200_ACT_SILU: { float s = sigmoidf_(saved); return s * (1.0f + saved * (1.0f - s)); }
+    case VB200_ACT_GELU: {
+        const float c = 0.7978845608f, k = 0.044715f;
+        float v = c * (saved + k * saved * saved * saved);
+        float t = tanhf(v), t2 = 1.0f - t * t;
+        return 0.5f * (1.0f + t) + 0.5f * saved * t2 * c * (1.0f + 3.0f * k * saved * saved);
+    }
+    }
+    return 1.0f;
+}
+
+// True when backward needs the pre-activation kept separately from the post-activation.
+__host__ __device__ inline bool act_needs_pre(int act) { return act == VB200_ACT_SILU || act == VB200_ACT_GELU; }
+
+// ---------------------------------------------------------------------------------------
+// Epilogue applied to each accumulator element (row m, column n of the GEMM output).
+// ---------------------------------------------------------------------------------------
+enum EpiMode {
+    EPI_STORE = 0,     // out0[m,n] = acc                                   (dW)
+    EPI_BIAS_ACT = 1,  // z = acc + bias[n]; out1[m,n] = z (if out1); out0[m,n] = f(z)   (forward, hidden)
+    EPI_BIAS = 2,      // out0[m,n] = acc + bias[n]                         (forward, last layer)
+    EPI_DACT = 3,      // out0[m,n] = acc * f'(saved[m,n])                  (dX + activation backward)
+};
+
+struct Epilogue {
+    int mode;
+    int act;
+    float *out0;        // leading dimension ld
+    float *out1;        // optional second output (pre-activation), same ld
+    const float *bias;  // [n]
+    const float *saved; // [m x n], same ld
+    long long ld;
+
+    __device__ __forceinline__ void apply(long long m, long long n, float acc) const {
+        long long idx = m * ld + n;
+        switch (mode) {
+        case EPI_STORE: out0[idx] = acc; break;
+        case EPI_BIAS_ACT: {
+            float z = acc + bias[n];
+            if (out1) out1[idx] = z;
+            out0[idx] = act_forward(act, z);
+            break;
+        }
+        case EPI_BIAS: out0[idx] = acc + bias[n]; break;
+        case EPI_DACT: out0[idx] = acc * act_backward(act, saved[idx]); break;
+        }
+    }
+    // Same for four consecutive columns n..n+3 (idx 16-byte aligned, all in range).
+    __device__ __forceinline__ void apply4(long long m, long long n, float4 acc) const {
+        long long idx = m * ld + n;
+        switch (mode) {
+        case EPI_STORE: *reinterpret_cast<float4 *>(out0 + idx) = acc; break;
+        case EPI_BIAS_ACT: {
+            float4 b = *reinterpret_cast<const float4 *>(bias + n);
+            float4 z = make_float4(acc.x + b.x, acc.y + b.y, acc.z + b.z, acc.w + b.w);
+            if (out1) *reinterpret_cast<float4 *>(out1 + idx) = z;
+            *reinterpret_cast<float4 *>(out0 + idx) =
+                make_float4(act_forward(act, z.x), act_forward(act, z.y), act_forward(act, z.z), act_forward(act, z.w));
+            break;
+        }
+        case EPI_BIAS: {
+            float4 b = *reinterpret_cast<const float4 *>(bias + n);
+            *reinterpret_cast<float4 *>(out0 + idx) = make_float4(acc.x + b.x, acc.y + b.y, acc.z + b.z, acc.w + b.w);
+            break;
+        }
+        case EPI_DACT: {
+            float4 s = *reinterpret_cast<const float4 *>(saved + idx);
+            *reinterpret_cast<float4 *>(out0 + idx) =
+                make_float4(acc.x * act_backward(act, s.x), acc.y * act_backward(act, s.y),
+                            acc.z * act_backward(act, s.z), acc.w * act_backward(act, s.w));
+            break;
+        }
+        }
+    }
+};
+
+// GEMM operand layouts: C[m x n] = op(A) . op(B)
+enum GemmLayout {
+    GEMM_NN = 0,  // A[m x k], B[k x n]   forward:  act . W
+    GEMM_NT = 1,  // A[m x k], B[n x k]   dX:       delta . W^T
+    GEMM_TN = 2,  // A[k x m], B[k x n]   dW:       act^T . delta
+};
+
+// Per-step scalars read by the optimizer kernel; written by a one-thread kernel ahead of
+// the captured step so that the graph itself never changes.
+struct StepScalars {
+    float lr;
+    float bc1, bc2;       // Adam bias corrections 1 - beta^t (host powf, mlp_train_rust_codegen.rs:811)
+    float beta1, beta2;
+    float eps;
+    float weight_decay;
+    float momentum;
+    float inv_unused;
+    unsigned int pad[7];
+};
+
+// ---------------------------------------------------------------------------------------
+// Kernel launchers (defined in the .cu files of this directory).
+// ---------------------------------------------------------------------------------------
+cudaError_t launch_gemm_ffma(int layout, const float *A, const float *B, long long m, long long n, long long k,
+                             const Epilogue &epi, cudaStream_t s);
+// Returns cudaErrorNotSupported when the shape/alignment cannot take the tensor path.
+cudaError_t launch_gemm_tc(int layout, const float *A, const float *B, long long m, long long n, long long k,
+                           const Epilogue &epi, unsigned int *status_word, cudaStream_t s);
+bool gemm_tc_supported(int layout, const float *A, const float *B, long long m, long long n, long long k,
+                       const Epilogue &epi);
+
+cudaError_t launch_optimizer(int optimizer, float *p, float *s1, float *s2, const float *g, long long n,
+                             long long n_decay, const StepScalars *sc, cudaStream_t s);
+cudaError_t launch_set_scalars(StepScalars *dst, StepScalars v, cudaStream_t s);
+
+long long colsum_chunks(long long rows, long long cols);
+cudaError_t launch_colsum(float *out, const float *in, long long rows, long long cols, float *scratch, cudaStream_t s);
+
+long long loss_blocks(long long nt);
+// delta[k] = 2*(out[k]-y[k])/nt_global ; *loss_sum = sum_k (out[k]-y[k])^2 (fixed order)
+cudaError_t launch_mse_seed(float *delta, float *loss_sum, const float *out, const float *y, long long nt,
+                            float nt_global, float *scratch, cudaStream_t s);
+
+}  // namespace vb

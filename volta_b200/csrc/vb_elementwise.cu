@@ -1,0 +1,282 @@
+// Bandwidth-bound kernels of the training step: the fused optimizer update, the bias-gradient
+// column reduction and the MSE loss + seed gradient.  All reductions use a fixed order and no
+// atomics, so a step is bit-identical from run to run.
+#include "vb_common.cuh"
+
+namespace vb {
+
+// ---------------------------------------------------------------------------------------
+// Optimizer: one 128-bit-vectorised pass over the flat parameter region.
+//
+// Arithmetic follows the reference expression trees with separate roundings (the
+// reference's x86 build uses AVX2 mul/add/div/sqrt without FMA,
+// src/engine/ir/codegen/mlp_train_rust_codegen.rs:352-367), hence the __f*_rn intrinsics,
+// which the compiler never contracts:
+//   Adam/AdamW  :358-367  m = b1*m + (1-b1)*g ; v = b2*v + (1-b2)*(g*g)
+//                         w = w - lr*((m/bc1)/(sqrt(v/bc2)+eps) + wd*w)
+//   Adagrad     :972-977  G += g*g ; p -= lr*g/(sqrt(G)+eps)
+//   SGD         :988-991  p -= lr*g
+//   SGD+momentum (extension, not in the reference) v = mu*v + g ; p -= lr*v
+// Weight decay applies to the first n_decay elements only (the weights; biases follow
+// them in the flat layout), as the generated step decays weights but not biases (:962-966).
+// ---------------------------------------------------------------------------------------
+template <int OPT>
+__device__ __forceinline__ void update_one(float &p, float &s1, float &s2, float g, const StepScalars &sc, float wd) {
+    if (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW) {
+        float one_m_b1 = __fsub_rn(1.0f, sc.beta1), one_m_b2 = __fsub_rn(1.0f, sc.beta2);
+        float m1 = __fadd_rn(__fmul_rn(sc.beta1, s1), __fmul_rn(one_m_b1, g));
+        float v1 = __fadd_rn(__fmul_rn(sc.beta2, s2), __fmul_rn(one_m_b2, __fmul_rn(g, g)));
+        s1 = m1;
+        s2 = v1;
+        float mhat = __fdiv_rn(m1, sc.bc1);
+        float vhat = __fdiv_rn(v1, sc.bc2);
+        float denom = __fadd_rn(__fsqrt_rn(vhat), sc.eps);
+        float step = __fmul_rn(sc.lr, __fadd_rn(__fdiv_rn(mhat, denom), __fmul_rn(wd, p)));
+        p = __fsub_rn(p, step);
+    } else if (OPT == VB200_OPT_ADAGRAD) {
+        float G = __fadd_rn(s1, __fmul_rn(g, g));
+        s1 = G;
+        p = __fsub_rn(p, __fdiv_rn(__fmul_rn(sc.lr, g), __fadd_rn(__fsqrt_rn(G), sc.eps)));
+    } else if (OPT == VB200_OPT_SGD_MOMENTUM) {
+        float v = __fadd_rn(__fmul_rn(sc.momentum, s1), g);
+        s1 = v;
+        p = __fsub_rn(p, __fmul_rn(sc.lr, v));
+    } else {
+        p = __fsub_rn(p, __fmul_rn(sc.lr, g));
+    }
+}
+
+template <int OPT>
+__global__ void __launch_bounds__(256) optimizer_kernel(float *__restrict__ p, float *__restrict__ s1,
+                                                        float *__restrict__ s2, const float *__restrict__ g,
+                                                        long long n, long long n_decay,
+                                                        const StepScalars *__restrict__ scp) {
+    const StepScalars sc = *scp;
+    constexpr bool HAS1 = (OPT != VB200_OPT_SGD);
+    constexpr bool HAS2 = (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW);
+    const long long n4 = n >> 2;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 pv = reinterpret_cast<float4 *>(p)[i];
+        float4 gv = __ldcs(reinterpret_cast<const float4 *>(g) + i);
+        float4 a = HAS1 ? reinterpret_cast<float4 *>(s1)[i] : make_float4(0, 0, 0, 0);
+        float4 b = HAS2 ? reinterpret_cast<float4 *>(s2)[i] : make_float4(0, 0, 0, 0);
+        long long e = i << 2;
+        float wd0 = (OPT == VB200_OPT_ADAMW && e + 0 < n_decay) ? sc.weight_decay : 0.0f;
+        float wd1 = (OPT == VB200_OPT_ADAMW && e + 1 < n_decay) ? sc.weight_decay : 0.0f;
+        float wd2 = (OPT == VB200_OPT_ADAMW && e + 2 < n_decay) ? sc.weight_decay : 0.0f;
+        float wd3 = (OPT == VB200_OPT_ADAMW && e + 3 < n_decay) ? sc.weight_decay : 0.0f;
+        update_one<OPT>(pv.x, a.x, b.x, gv.x, sc, wd0);
+        update_one<OPT>(pv.y, a.y, b.y, gv.y, sc, wd1);
+        update_one<OPT>(pv.z, a.z, b.z, gv.z, sc, wd2);
+        update_one<OPT>(pv.w, a.w, b.w, gv.w, sc, wd3);
+        reinterpret_cast<float4 *>(p)[i] = pv;
+        if (HAS1) reinterpret_cast<float4 *>(s1)[i] = a;
+        if (HAS2) reinterpret_cast<float4 *>(s2)[i] = b;
+    }
+    // scalar tail (n not a multiple of 4): handled by the first threads of block 0
+    if (blockIdx.x == 0) {
+        long long e = (n4 << 2) + threadIdx.x;
+        if (e < n) {
+            float pv = p[e], a = HAS1 ? s1[e] : 0.0f, b = HAS2 ? s2[e] : 0.0f;
+            float wd = (OPT == VB200_OPT_ADAMW && e < n_decay) ? sc.weight_decay : 0.0f;
+            update_one<OPT>(pv, a, b, g[e], sc, wd);
+            p[e] = pv;
+            if (HAS1) s1[e] = a;
+            if (HAS2) s2[e] = b;
+        }
+    }
+}
+
+static int g_sm_count = 0;
+static int sm_count() {
+    if (!g_sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (g_sm_count <= 0) g_sm_count = 148;
+    }
+    return g_sm_count;
+}
+
+cudaError_t launch_optimizer(int optimizer, float *p, float *s1, float *s2, const float *g, long long n,
+                             long long n_decay, const StepScalars *sc, cudaStream_t s) {
+    if (n <= 0) return cudaSuccess;
+    if ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(s1) |
+         reinterpret_cast<uintptr_t>(s2)) & 15)
+        return cudaErrorMisalignedAddress;
+    long long n4 = n >> 2;
+    long long want = (n4 + 255) / 256;
+    long long cap = (long long)sm_count() * 8;  // 8 resident CTAs of 256 threads per SM, grid-stride beyond
+    int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+    switch (optimizer) {
+    case VB200_OPT_SGD: optimizer_kernel<VB200_OPT_SGD><<<blocks, 256, 0, s>>>(p, s1, s2, g, n, n_decay, sc); break;
+    case VB200_OPT_ADAM: optimizer_kernel<VB200_OPT_ADAM><<<blocks, 256, 0, s>>>(p, s1, s2, g, n, n_decay, sc); break;
+    case VB200_OPT_ADAMW: optimizer_kernel<VB200_OPT_ADAMW><<<blocks, 256, 0, s>>>(p, s1, s2, g, n, n_decay, sc); break;
+    case VB200_OPT_ADAGRAD: optimizer_kernel<VB200_OPT_ADAGRAD><<<blocks, 256, 0, s>>>(p, s1, s2, g, n, n_decay, sc); break;
+    case VB200_OPT_SGD_MOMENTUM:
+        optimizer_kernel<VB200_OPT_SGD_MOMENTUM><<<blocks, 256, 0, s>>>(p, s1, s2, g, n, n_decay, sc);
+        break;
+    default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+__global__ void set_scalars_kernel(StepScalars *dst, StepScalars v) { *dst = v; }
+
+cudaError_t launch_set_scalars(StepScalars *dst, StepScalars v, cudaStream_t s) {
+    set_scalars_kernel<<<1, 1, 0, s>>>(dst, v);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------
+// Bias gradient: out[j] = sum_rows in[row, j]  (mlp_train_rust_codegen.rs:931-933).
+// Two passes, fixed order: pass 1 sums each chunk of rows per column (8 row-lanes per
+// column, combined in lane order), pass 2 adds the chunk partials in chunk order.
+// ---------------------------------------------------------------------------------------
+static const int CS_COLS = 128;  // columns per block (32 threads x float4)
+static const int CS_TY = 8;      // row lanes per block
+
+long long colsum_chunks(long long rows, long long cols) {
+    long long col_blocks = (cols + CS_COLS - 1) / CS_COLS;
+    long long target = 4LL * 148;  // aim for a few blocks per SM; depends only on the shape
+    long long chunks = (target + col_blocks - 1) / col_blocks;
+    long long max_chunks = (rows + 63) / 64;  // at least 64 rows per chunk
+    if (chunks > max_chunks) chunks = max_chunks;
+    if (chunks < 1) chunks = 1;
+    if (chunks > 1024) chunks = 1024;
+    return chunks;
+}
+
+__global__ void __launch_bounds__(32 * CS_TY) colsum_pass1(float *__restrict__ partial, const float *__restrict__ in,
+                                                           long long rows, long long cols, long long rows_per_chunk) {
+    __shared__ float4 sm[CS_TY][32];
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    const long long c0 = (long long)blockIdx.x * CS_COLS + tx * 4;
+    const long long r0 = (long long)blockIdx.y * rows_per_chunk;
+    long long r1 = r0 + rows_per_chunk;
+    if (r1 > rows) r1 = rows;
+    float4 acc = make_float4(0, 0, 0, 0);
+    const bool vec = ((cols & 3) == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
+    if (vec) {
+        if (c0 < cols)
+            for (long long r = r0 + ty; r < r1; r += CS_TY) {
+                float4 v = __ldg(reinterpret_cast<const float4 *>(in + r * cols + c0));
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+    } else {
+        for (long long r = r0 + ty; r < r1; r += CS_TY) {
+            const float *row = in + r * cols;
+            if (c0 + 0 < cols) acc.x += row[c0 + 0];
+            if (c0 + 1 < cols) acc.y += row[c0 + 1];
+            if (c0 + 2 < cols) acc.z += row[c0 + 2];
+            if (c0 + 3 < cols) acc.w += row[c0 + 3];
+        }
+    }
+    sm[ty][tx] = acc;
+    __syncthreads();
+    if (ty == 0) {
+        float4 t = sm[0][tx];
+#pragma unroll
+        for (int j = 1; j < CS_TY; ++j) {
+            float4 v = sm[j][tx];
+            t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+        }
+        float *dst = partial + (long long)blockIdx.y * cols;
+        if (c0 + 0 < cols) dst[c0 + 0] = t.x;
+        if (c0 + 1 < cols) dst[c0 + 1] = t.y;
+        if (c0 + 2 < cols) dst[c0 + 2] = t.z;
+        if (c0 + 3 < cols) dst[c0 + 3] = t.w;
+    }
+}
+
+__global__ void colsum_pass2(float *__restrict__ out, const float *__restrict__ partial, long long chunks,
+                             long long cols) {
+    long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float t = partial[c];
+    for (long long j = 1; j < chunks; ++j) t += partial[j * cols + c];
+    out[c] = t;
+}
+
+cudaError_t launch_colsum(float *out, const float *in, long long rows, long long cols, float *scratch,
+                          cudaStream_t s) {
+    if (rows <= 0 || cols <= 0) return cudaErrorInvalidValue;
+    long long chunks = colsum_chunks(rows, cols);
+    long long rpc = (rows + chunks - 1) / chunks;
+    dim3 grid((unsigned)((cols + CS_COLS - 1) / CS_COLS), (unsigned)chunks), block(32, CS_TY);
+    colsum_pass1<<<grid, block, 0, s>>>(scratch, in, rows, cols, rpc);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    colsum_pass2<<<(unsigned)((cols + 255) / 256), 256, 0, s>>>(out, scratch, chunks, cols);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------
+// MSE loss and seed gradient (mlp_train_rust_codegen.rs:793-798):
+//   d = out - y ; delta = (2*d)/nt ; loss = (sum d*d)/nt     (division by nt on the host)
+// nt is the GLOBAL element count under data parallelism, so that shard gradients add up.
+// The reference sums sequentially; here each block sums 256 interleaved lanes and then a
+// fixed shuffle/shared tree, and a single block adds the block partials in order.
+// ---------------------------------------------------------------------------------------
+static const int MSE_THREADS = 256;
+static const int MSE_PER_BLOCK = 4096;
+
+long long loss_blocks(long long nt) {
+    long long b = (nt + MSE_PER_BLOCK - 1) / MSE_PER_BLOCK;
+    return b < 1 ? 1 : b;
+}
+
+__device__ __forceinline__ float block_sum_256(float v, float *sm) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.0f;
+    if (threadIdx.x == 0) {
+        t = sm[0];
+#pragma unroll
+        for (int j = 1; j < MSE_THREADS / 32; ++j) t += sm[j];
+    }
+    return t;  // valid on thread 0
+}
+
+__global__ void __launch_bounds__(MSE_THREADS) mse_pass1(float *__restrict__ delta, float *__restrict__ partial,
+                                                         const float *__restrict__ out, const float *__restrict__ y,
+                                                         long long nt, float nt_global) {
+    __shared__ float sm[MSE_THREADS / 32];
+    long long base = (long long)blockIdx.x * MSE_PER_BLOCK;
+    float acc = 0.0f;
+#pragma unroll 4
+    for (int j = 0; j < MSE_PER_BLOCK / MSE_THREADS; ++j) {
+        long long k = base + j * MSE_THREADS + threadIdx.x;
+        if (k < nt) {
+            float d = __fsub_rn(out[k], y[k]);
+            acc = __fadd_rn(acc, __fmul_rn(d, d));
+            delta[k] = __fdiv_rn(__fmul_rn(2.0f, d), nt_global);
+        }
+    }
+    float t = block_sum_256(acc, sm);
+    if (threadIdx.x == 0) partial[blockIdx.x] = t;
+}
+
+__global__ void __launch_bounds__(MSE_THREADS) mse_pass2(float *__restrict__ loss_sum,
+                                                         const float *__restrict__ partial, long long nblocks) {
+    __shared__ float sm[MSE_THREADS / 32];
+    float acc = 0.0f;
+    for (long long k = threadIdx.x; k < nblocks; k += MSE_THREADS) acc += partial[k];
+    float t = block_sum_256(acc, sm);
+    if (threadIdx.x == 0) *loss_sum = t;
+}
+
+cudaError_t launch_mse_seed(float *delta, float *loss_sum, const float *out, const float *y, long long nt,
+                            float nt_global, float *scratch, cudaStream_t s) {
+    long long nb = loss_blocks(nt);
+    mse_pass1<<<(unsigned)nb, MSE_THREADS, 0, s>>>(delta, scratch, out, y, nt, nt_global);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    mse_pass2<<<1, MSE_THREADS, 0, s>>>(loss_sum, scratch, nb);
+    return cudaGetLastError();
+}
+
+}  // namespace vb

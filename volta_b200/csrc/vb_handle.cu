@@ -1,0 +1,804 @@
+// Training handle of libvolta_b200: one device arena, a fixed launch schedule captured as a
+// CUDA graph, and the C ABI on top of it.
+//
+// The step restates volta_train_step of the reference's generated library
+// (src/engine/ir/codegen/mlp_train_rust_codegen.rs:699-994) for a GPU:
+//   forward   i = 0..n-1   GEMM(act_i, W_i) with bias + activation in the epilogue  (:708-743)
+//   loss                    MSE sum and seed gradient                                 (:793-798)
+//   backward  i = n-1..0   dW_i = act_i^T.delta_i ; db_i = colsum(delta_i) ;
+//                           delta_{i-1} = (delta_i.W_i^T) * f'(.) in the dX epilogue   (:820-934, 958-988)
+//   update                  one fused optimizer pass over all parameters              (:958-993)
+// All dX GEMMs read W before any update, as in the reference, because the single
+// optimizer launch comes last.  Under data parallelism each layer's dW bucket is
+// all-reduced on a side stream as soon as it is produced, overlapping the remaining
+// backward GEMMs; the optimizer waits for every bucket.
+#include <math.h>
+#include <string.h>
+
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "vb_arena.h"
+#include "vb_common.cuh"
+#include "vb_dp.h"
+
+using namespace vb;
+
+namespace {
+
+std::mutex g_err_mutex;
+std::string g_create_error;
+int g_create_status = VB200_OK;
+
+struct KernelRecord {
+    std::string name;
+    double flops, bytes;
+    cudaEvent_t e0, e1;
+};
+
+}  // namespace
+
+struct vb200_handle {
+    vb200_config cfg;
+    int n = 0;  // weight layers
+    std::vector<int> L;
+    int B = 0;
+    long long global_nt = 0;
+    int world = 1, rank = 0;
+    int status = VB200_OK;
+    std::string error;
+
+    ArenaPlan plan;
+    char *arena = nullptr;
+    int64_t arena_bytes = 0;
+
+    // flat parameter layout (floats): all weights, then all biases, each padded to 64 floats
+    std::vector<int64_t> off_w, off_b;
+    int64_t n_weights_padded = 0, n_params_padded = 0;
+    float *params = nullptr, *grads = nullptr, *s1 = nullptr, *s2 = nullptr;
+    float *loss_sum = nullptr;  // lives right behind the gradients so that it joins the bias bucket
+    StepScalars *scalars = nullptr;
+    unsigned int *status_word = nullptr;
+    float *mse_scratch = nullptr, *colsum_scratch = nullptr;
+    float *xin[2] = {nullptr, nullptr}, *yin[2] = {nullptr, nullptr};
+    std::vector<float *> act, pre, delta;  // act[0] unused (slot dependent)
+
+    // host side
+    float *mirror_params = nullptr, *mirror_grads = nullptr;  // pinned
+    float *host_loss = nullptr;                               // pinned, one float per slot
+    unsigned int *host_status = nullptr;                      // pinned
+    uint64_t adam_step = 0;
+    uint64_t steps_done = 0;
+    int last_slot = 0;
+
+    cudaStream_t stream = nullptr, copy_stream = nullptr, comm_stream = nullptr;
+    cudaEvent_t ev_copied[2] = {nullptr, nullptr}, ev_slot_free[2] = {nullptr, nullptr};
+    cudaEvent_t ev_join = nullptr;
+    std::vector<cudaEvent_t> ev_bucket;
+    cudaGraphExec_t graph[2] = {nullptr, nullptr};
+    bool use_graph = true;
+    int kernels_per_step = 0;
+
+    DpComm *dp = nullptr;
+
+    // profiling (plain launches with an event pair per kernel)
+    bool profiling = false;
+    std::vector<KernelRecord> records;
+
+    int fail(int code, const std::string &msg) {
+        status = code;
+        error = msg;
+        return code;
+    }
+};
+
+namespace {
+
+#define VB_CUDA(h, expr)                                                                              \
+    do {                                                                                              \
+        cudaError_t _e = (expr);                                                                      \
+        if (_e != cudaSuccess)                                                                        \
+            return (h)->fail(_e == cudaErrorMemoryAllocation ? VB200_ERR_OOM : VB200_ERR_CUDA,        \
+                             std::string(#expr) + ": " + cudaGetErrorString(_e));                     \
+    } while (0)
+
+int64_t pad64(int64_t v) { return (v + 63) / 64 * 64; }
+
+int pos_fwd(int i) { return i; }
+int pos_loss(int n) { return n; }
+int pos_bwd(int n, int i) { return n + 1 + (n - 1 - i); }
+
+// The reference's LCG-Xavier stream (mlp_train_rust_codegen.rs:630-638, 653-658).
+void lcg_xavier(float *w, int64_t n, int r, int c, uint64_t *rng) {
+    float lim = sqrtf(6.0f / ((float)r + (float)c));
+    for (int64_t i = 0; i < n; ++i) {
+        *rng = *rng * 6364136223846793005ULL + 1442695040888963407ULL;
+        float f = (float)((*rng >> 11) & ((1ULL << 53) - 1)) / (float)(1ULL << 53);
+        w[i] = (f * 2.0f - 1.0f) * lim;
+    }
+}
+
+struct Scope {
+    vb200_handle *h;
+    bool on;
+    Scope(vb200_handle *h_, const char *name, double flops, double bytes) : h(h_), on(h_->profiling) {
+        h->kernels_per_step++;
+        if (!on) return;
+        KernelRecord r;
+        r.name = name;
+        r.flops = flops;
+        r.bytes = bytes;
+        cudaEventCreate(&r.e0);
+        cudaEventCreate(&r.e1);
+        cudaEventRecord(r.e0, h->stream);
+        h->records.push_back(r);
+    }
+    ~Scope() {
+        if (on) cudaEventRecord(h->records.back().e1, h->stream);
+    }
+};
+
+cudaError_t run_gemm(vb200_handle *h, int layout, const float *A, const float *Bm, long long m, long long n,
+                     long long k, const Epilogue &epi) {
+    if (h->cfg.gemm_path != VB200_GEMM_FFMA && gemm_tc_supported(layout, A, Bm, m, n, k, epi))
+        return launch_gemm_tc(layout, A, Bm, m, n, k, epi, h->status_word, h->stream);
+    return launch_gemm_ffma(layout, A, Bm, m, n, k, epi, h->stream);
+}
+
+// Enqueue one whole step on h->stream reading inputs from `slot`.
+int enqueue_step(vb200_handle *h, int slot) {
+    const int n = h->n, B = h->B, act = h->cfg.activation;
+    const std::vector<int> &L = h->L;
+    cudaStream_t s = h->stream;
+    h->kernels_per_step = 0;
+    const float *act0 = h->xin[slot];
+    auto A = [&](int i) -> float * { return i == 0 ? const_cast<float *>(act0) : h->act[i]; };
+    char nm[48];
+
+    // forward
+    for (int i = 0; i < n; ++i) {
+        const long long r = L[i], c = L[i + 1];
+        Epilogue e{};
+        e.act = act;
+        e.ld = c;
+        e.bias = h->params + h->off_b[i];
+        if (i == n - 1) {
+            e.mode = EPI_BIAS;
+            e.out0 = h->act[n];
+        } else {
+            e.mode = EPI_BIAS_ACT;
+            e.out0 = h->act[i + 1];
+            e.out1 = act_needs_pre(act) ? h->pre[i] : nullptr;
+        }
+        snprintf(nm, sizeof nm, "fwd%d_gemm_nn_%lldx%lldx%lld", i, (long long)B, c, r);
+        Scope sc(h, nm, 2.0 * B * r * c, 4.0 * (B * r + r * c + B * c * (e.out1 ? 2 : 1)));
+        VB_CUDA(h, run_gemm(h, GEMM_NN, A(i), h->params + h->off_w[i], B, c, r, e));
+    }
+    // loss + seed gradient
+    {
+        long long nt = (long long)B * L[n];
+        Scope sc(h, "mse_seed", 3.0 * nt, 12.0 * nt);
+        h->kernels_per_step++;  // two launches
+        VB_CUDA(h, launch_mse_seed(h->delta[n - 1], h->loss_sum, h->act[n], h->yin[slot], nt, (float)h->global_nt,
+                                   h->mse_scratch, s));
+    }
+    // backward
+    for (int i = n - 1; i >= 0; --i) {
+        const long long r = L[i], c = L[i + 1];
+        {
+            Epilogue e{};
+            e.mode = EPI_STORE;
+            e.out0 = h->grads + h->off_w[i];
+            e.ld = c;
+            snprintf(nm, sizeof nm, "dW%d_gemm_tn_%lldx%lldx%lld", i, r, c, (long long)B);
+            Scope sc(h, nm, 2.0 * B * r * c, 4.0 * (B * r + B * c + r * c));
+            VB_CUDA(h, run_gemm(h, GEMM_TN, A(i), h->delta[i], r, c, B, e));
+        }
+        if (h->dp) {
+            // bucket i = dW_i: reduce on the side stream while the main stream goes on
+            VB_CUDA(h, cudaEventRecord(h->ev_bucket[i], s));
+            VB_CUDA(h, cudaStreamWaitEvent(h->comm_stream, h->ev_bucket[i], 0));
+            int rc = h->dp->all_reduce_sum(h->grads + h->off_w[i], pad64(r * c), h->comm_stream);
+            if (rc) return h->fail(VB200_ERR_NCCL, h->dp->error());
+        }
+        {
+            snprintf(nm, sizeof nm, "db%d_colsum_%lldx%lld", i, (long long)B, c);
+            Scope sc(h, nm, (double)B * c, 4.0 * (B * c + c));
+            h->kernels_per_step++;
+            VB_CUDA(h, launch_colsum(h->grads + h->off_b[i], h->delta[i], B, c, h->colsum_scratch, s));
+        }
+        if (i > 0) {
+            Epilogue e{};
+            e.mode = EPI_DACT;
+            e.act = act;
+            e.out0 = h->delta[i - 1];
+            e.saved = act_needs_pre(act) ? h->pre[i - 1] : h->act[i];
+            e.ld = r;
+            snprintf(nm, sizeof nm, "dX%d_gemm_nt_%lldx%lldx%lld", i, (long long)B, r, c);
+            Scope sc(h, nm, 2.0 * B * r * c, 4.0 * (B * c + r * c + 2.0 * B * r));
+            VB_CUDA(h, run_gemm(h, GEMM_NT, h->delta[i], h->params + h->off_w[i], B, r, c, e));
+        }
+    }
+    if (h->dp) {
+        // last bucket: every bias gradient plus the loss sum, contiguous behind the weights
+        VB_CUDA(h, cudaEventRecord(h->ev_bucket[n], s));
+        VB_CUDA(h, cudaStreamWaitEvent(h->comm_stream, h->ev_bucket[n], 0));
+        int64_t cnt = h->n_params_padded - h->n_weights_padded + 64;
+        int rc = h->dp->all_reduce_sum(h->grads + h->n_weights_padded, cnt, h->comm_stream);
+        if (rc) return h->fail(VB200_ERR_NCCL, h->dp->error());
+        VB_CUDA(h, cudaEventRecord(h->ev_join, h->comm_stream));
+        VB_CUDA(h, cudaStreamWaitEvent(s, h->ev_join, 0));
+    }
+    // update
+    {
+        const int opt = h->cfg.optimizer;
+        double bpp = opt == VB200_OPT_SGD ? 12.0 : (opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW) ? 28.0 : 20.0;
+        Scope sc(h, "optimizer", 0.0, bpp * h->n_params_padded);
+        VB_CUDA(h, launch_optimizer(opt, h->params, h->s1, h->s2, h->grads, h->n_params_padded, h->n_weights_padded,
+                                    h->scalars, s));
+    }
+    VB_CUDA(h, cudaMemcpyAsync(&h->host_loss[slot], h->loss_sum, sizeof(float), cudaMemcpyDeviceToHost, s));
+    VB_CUDA(h, cudaMemcpyAsync(h->host_status, h->status_word, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
+    return VB200_OK;
+}
+
+int capture_graphs(vb200_handle *h) {
+    for (int slot = 0; slot < 2; ++slot) {
+        cudaGraph_t g = nullptr;
+        VB_CUDA(h, cudaStreamBeginCapture(h->stream, cudaStreamCaptureModeThreadLocal));
+        int rc = enqueue_step(h, slot);
+        cudaError_t e = cudaStreamEndCapture(h->stream, &g);
+        if (rc) {
+            if (g) cudaGraphDestroy(g);
+            return rc;
+        }
+        if (e != cudaSuccess) return h->fail(VB200_ERR_CUDA, std::string("cudaStreamEndCapture: ") + cudaGetErrorString(e));
+        e = cudaGraphInstantiate(&h->graph[slot], g, 0);
+        cudaGraphDestroy(g);
+        if (e != cudaSuccess) return h->fail(VB200_ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
+    }
+    return VB200_OK;
+}
+
+StepScalars make_scalars(vb200_handle *h, float lr) {
+    StepScalars sc{};
+    sc.lr = lr;
+    sc.beta1 = 0.9f;
+    sc.beta2 = 0.999f;
+    sc.eps = 1e-8f;
+    sc.weight_decay = h->cfg.weight_decay != 0.0f ? h->cfg.weight_decay : 0.01f;
+    sc.momentum = h->cfg.momentum != 0.0f ? h->cfg.momentum : 0.9f;
+    // mlp_train_rust_codegen.rs:805-811: the counter is bumped before the update and the
+    // corrections use f32 powf
+    float t = (float)h->adam_step;
+    sc.bc1 = 1.0f - powf(sc.beta1, t);
+    sc.bc2 = 1.0f - powf(sc.beta2, t);
+    return sc;
+}
+
+int copy_inputs(vb200_handle *h, int slot, const float *X, const float *Y, bool *host_wait) {
+    const size_t xb = (size_t)h->B * h->L[0] * sizeof(float), yb = (size_t)h->B * h->L[h->n] * sizeof(float);
+    cudaPointerAttributes ax{}, ay{};
+    cudaError_t ex = cudaPointerGetAttributes(&ax, X), ey = cudaPointerGetAttributes(&ay, Y);
+    if (ex != cudaSuccess || ey != cudaSuccess) {
+        cudaGetLastError();
+        ax.type = cudaMemoryTypeUnregistered;
+        ay.type = cudaMemoryTypeUnregistered;
+    }
+    const bool xdev = ax.type == cudaMemoryTypeDevice || ax.type == cudaMemoryTypeManaged;
+    const bool ydev = ay.type == cudaMemoryTypeDevice || ay.type == cudaMemoryTypeManaged;
+    // the slot is free once the step that last read it has finished
+    VB_CUDA(h, cudaStreamWaitEvent(h->copy_stream, h->ev_slot_free[slot], 0));
+    VB_CUDA(h, cudaMemcpyAsync(h->xin[slot], X, xb, xdev ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice,
+                               h->copy_stream));
+    VB_CUDA(h, cudaMemcpyAsync(h->yin[slot], Y, yb, ydev ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice,
+                               h->copy_stream));
+    VB_CUDA(h, cudaEventRecord(h->ev_copied[slot], h->copy_stream));
+    VB_CUDA(h, cudaStreamWaitEvent(h->stream, h->ev_copied[slot], 0));
+    *host_wait = !(xdev && ydev);
+    return VB200_OK;
+}
+
+int do_step(vb200_handle *h, const float *X, const float *Y, float lr, bool profile) {
+    if (!X || !Y) return h->fail(VB200_ERR_INVALID, "volta_b200_step: null input pointer");
+    const int slot = profile ? 0 : (int)(h->steps_done & 1);
+    bool host_wait = false;
+    int rc = copy_inputs(h, slot, X, Y, &host_wait);
+    if (rc) return rc;
+    const int opt = h->cfg.optimizer;
+    if (opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW) h->adam_step += 1;
+    VB_CUDA(h, launch_set_scalars(h->scalars, make_scalars(h, lr), h->stream));
+    if (profile || !h->use_graph) {
+        h->profiling = profile;
+        rc = enqueue_step(h, slot);
+        h->profiling = false;
+        if (rc) return rc;
+    } else {
+        VB_CUDA(h, cudaGraphLaunch(h->graph[slot], h->stream));
+    }
+    VB_CUDA(h, cudaEventRecord(h->ev_slot_free[slot], h->stream));
+    h->last_slot = slot;
+    h->steps_done += 1;
+    // X and Y are borrowed for the call only (mlp_train_rust_codegen.rs:704-707 copies X
+    // before returning): wait until the device has taken them out of host memory.
+    if (host_wait) VB_CUDA(h, cudaEventSynchronize(h->ev_copied[slot]));
+    return VB200_OK;
+}
+
+int check_device_status(vb200_handle *h) {
+    if (h->host_status && *h->host_status != 0) {
+        char buf[96];
+        snprintf(buf, sizeof buf, "a device-side wait gave up (status word 0x%08x)", *h->host_status);
+        return h->fail(VB200_ERR_DEVICE_WAIT, buf);
+    }
+    return VB200_OK;
+}
+
+void destroy(vb200_handle *h) {
+    if (!h) return;
+    if (h->stream) cudaStreamSynchronize(h->stream);
+    if (h->copy_stream) cudaStreamSynchronize(h->copy_stream);
+    if (h->comm_stream) cudaStreamSynchronize(h->comm_stream);
+    if (h->dp) {
+        delete h->dp;
+        h->dp = nullptr;
+    }
+    for (int s = 0; s < 2; ++s) {
+        if (h->graph[s]) cudaGraphExecDestroy(h->graph[s]);
+        if (h->ev_copied[s]) cudaEventDestroy(h->ev_copied[s]);
+        if (h->ev_slot_free[s]) cudaEventDestroy(h->ev_slot_free[s]);
+    }
+    if (h->ev_join) cudaEventDestroy(h->ev_join);
+    for (auto e : h->ev_bucket) cudaEventDestroy(e);
+    if (h->arena) cudaFree(h->arena);
+    if (h->mirror_params) cudaFreeHost(h->mirror_params);
+    if (h->mirror_grads) cudaFreeHost(h->mirror_grads);
+    if (h->host_loss) cudaFreeHost(h->host_loss);
+    if (h->host_status) cudaFreeHost(h->host_status);
+    if (h->stream) cudaStreamDestroy(h->stream);
+    if (h->copy_stream) cudaStreamDestroy(h->copy_stream);
+    if (h->comm_stream) cudaStreamDestroy(h->comm_stream);
+    delete h;
+}
+
+int validate(const vb200_config *c, std::string *why) {
+    if (!c) { *why = "null config"; return VB200_ERR_INVALID; }
+    if (c->n_sizes < 2 || c->n_sizes > VB200_MAX_LAYERS) { *why = "need between 2 and 32 layer sizes"; return VB200_ERR_INVALID; }
+    for (int i = 0; i < c->n_sizes; ++i)
+        if (c->layers[i] <= 0) { *why = "layer widths must be positive"; return VB200_ERR_INVALID; }
+    if (c->batch <= 0) { *why = "batch must be positive"; return VB200_ERR_INVALID; }
+    if (c->activation < VB200_ACT_RELU || c->activation > VB200_ACT_GELU) { *why = "unknown activation"; return VB200_ERR_UNSUPPORTED; }
+    if (c->optimizer < VB200_OPT_SGD || c->optimizer > VB200_OPT_SGD_MOMENTUM) { *why = "unknown optimizer"; return VB200_ERR_UNSUPPORTED; }
+    int world = c->world_size > 1 ? c->world_size : 1;
+    if (c->rank < 0 || c->rank >= world) { *why = "rank out of range"; return VB200_ERR_INVALID; }
+    if (c->global_batch != 0 && c->global_batch < c->batch) { *why = "global_batch smaller than batch"; return VB200_ERR_INVALID; }
+    if (c->gemm_path < VB200_GEMM_AUTO || c->gemm_path > VB200_GEMM_TENSOR) { *why = "unknown gemm_path"; return VB200_ERR_INVALID; }
+    return VB200_OK;
+}
+
+struct PlanIdx {
+    int params, grads, s1, s2, sc, mse, cs, x[2], y[2];
+    std::vector<int> act, pre, delta;
+};
+
+// Lay the step's buffers out on the fixed schedule (forward 0..n-1, loss n, backward
+// n+1..2n, update 2n+1).  Parameters, gradients, optimizer state, scratch and the two input
+// slots are persistent; activations, pre-activations and deltas are temporaries that may
+// share storage when their lifetimes do not meet.
+void make_plan(const vb200_config &c, ArenaPlan &pl, PlanIdx &ix, std::vector<int64_t> &off_w,
+               std::vector<int64_t> &off_b, int64_t &n_weights_padded, int64_t &n_params_padded) {
+    const int n = c.n_sizes - 1;
+    const int *L = c.layers;
+    const int B = c.batch;
+    off_w.resize(n);
+    off_b.resize(n);
+    int64_t off = 0;
+    for (int i = 0; i < n; ++i) { off_w[i] = off; off += pad64((int64_t)L[i] * L[i + 1]); }
+    n_weights_padded = off;
+    for (int i = 0; i < n; ++i) { off_b[i] = off; off += pad64(L[i + 1]); }
+    n_params_padded = off;
+    const int64_t P = off;
+    const int opt = c.optimizer;
+    const bool has1 = opt != VB200_OPT_SGD, has2 = (opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW);
+    const int end = 2 * n + 1;
+    ix.params = pl.add("params", P * 4, 0, end, true);
+    ix.grads = pl.add("grads+loss", (P + 64) * 4, 0, end, true);
+    ix.s1 = pl.add("opt_state1", has1 ? P * 4 : 4, 0, end, true);
+    ix.s2 = pl.add("opt_state2", has2 ? P * 4 : 4, 0, end, true);
+    ix.sc = pl.add("scalars+status", 1024, 0, end, true);
+    ix.mse = pl.add("mse_scratch", loss_blocks((long long)B * L[n]) * 4, 0, end, true);
+    long long cs = 0;
+    for (int i = 0; i < n; ++i) cs = std::max(cs, colsum_chunks(B, L[i + 1]) * (long long)L[i + 1]);
+    ix.cs = pl.add("colsum_scratch", cs * 4, 0, end, true);
+    for (int s = 0; s < 2; ++s) {
+        ix.x[s] = pl.add(s ? "x_slot1" : "x_slot0", (int64_t)B * L[0] * 4, 0, end, true);
+        ix.y[s] = pl.add(s ? "y_slot1" : "y_slot0", (int64_t)B * L[n] * 4, 0, end, true);
+    }
+    ix.act.assign(n + 1, -1);
+    ix.pre.assign(n, -1);
+    ix.delta.assign(n, -1);
+    for (int i = 1; i < n; ++i) {
+        ix.act[i] = pl.add("act" + std::to_string(i), (int64_t)B * L[i] * 4, pos_fwd(i - 1), pos_bwd(n, i), false);
+        if (act_needs_pre(c.activation))
+            ix.pre[i - 1] = pl.add("pre" + std::to_string(i - 1), (int64_t)B * L[i] * 4, pos_fwd(i - 1), pos_bwd(n, i), false);
+    }
+    ix.act[n] = pl.add("act" + std::to_string(n), (int64_t)B * L[n] * 4, pos_fwd(n - 1), pos_loss(n), false);
+    for (int i = n - 1; i >= 0; --i) {
+        int first = (i == n - 1) ? pos_loss(n) : pos_bwd(n, i + 1);
+        ix.delta[i] = pl.add("delta" + std::to_string(i), (int64_t)B * L[i + 1] * 4, first, pos_bwd(n, i), false);
+    }
+    pl.plan();
+}
+
+int build(vb200_handle *h) {
+    const vb200_config &c = h->cfg;
+    const int n = c.n_sizes - 1;
+    h->n = n;
+    h->L.assign(c.layers, c.layers + c.n_sizes);
+    h->B = c.batch;
+    h->world = c.world_size > 1 ? c.world_size : 1;
+    h->rank = c.rank;
+    const long long gb = c.global_batch ? c.global_batch : (long long)c.batch * h->world;
+    h->global_nt = gb * h->L[n];
+    h->use_graph = c.use_graph != 2;
+    const int B = h->B;
+    const std::vector<int> &L = h->L;
+
+    PlanIdx ix;
+    make_plan(c, h->plan, ix, h->off_w, h->off_b, h->n_weights_padded, h->n_params_padded);
+    ArenaPlan &pl = h->plan;
+    const int64_t P = h->n_params_padded;
+    std::string why;
+    if (!pl.verify(&why)) return h->fail(VB200_ERR_INVALID, "memory plan rejected: " + why);
+    const int i_params = ix.params, i_grads = ix.grads, i_s1 = ix.s1, i_s2 = ix.s2, i_sc = ix.sc, i_mse = ix.mse,
+              i_cs = ix.cs;
+    const int *i_x = ix.x, *i_y = ix.y;
+    const std::vector<int> &i_act = ix.act, &i_pre = ix.pre, &i_delta = ix.delta;
+
+    // ---- one allocation
+    h->arena_bytes = pl.total();
+    cudaError_t e = cudaMalloc(&h->arena, (size_t)h->arena_bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        char buf[128];
+        snprintf(buf, sizeof buf, "cudaMalloc of the %.2f GB arena failed: %s", h->arena_bytes / 1e9, cudaGetErrorString(e));
+        return h->fail(VB200_ERR_OOM, buf);
+    }
+    auto at = [&](int idx) -> float * { return reinterpret_cast<float *>(h->arena + pl.offset(idx)); };
+    h->params = at(i_params);
+    h->grads = at(i_grads);
+    h->loss_sum = h->grads + P;
+    h->s1 = at(i_s1);
+    h->s2 = at(i_s2);
+    h->scalars = reinterpret_cast<StepScalars *>(at(i_sc));
+    h->status_word = reinterpret_cast<unsigned int *>(reinterpret_cast<char *>(at(i_sc)) + 512);
+    h->mse_scratch = at(i_mse);
+    h->colsum_scratch = at(i_cs);
+    for (int s = 0; s < 2; ++s) { h->xin[s] = at(i_x[s]); h->yin[s] = at(i_y[s]); }
+    h->act.assign(n + 1, nullptr);
+    h->pre.assign(n, nullptr);
+    h->delta.assign(n, nullptr);
+    for (int i = 1; i <= n; ++i) h->act[i] = at(i_act[i]);
+    for (int i = 0; i < n; ++i) { if (i_pre[i] >= 0) h->pre[i] = at(i_pre[i]); h->delta[i] = at(i_delta[i]); }
+
+    VB_CUDA(h, cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking));
+    VB_CUDA(h, cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking));
+    for (int s = 0; s < 2; ++s) {
+        VB_CUDA(h, cudaEventCreateWithFlags(&h->ev_copied[s], cudaEventDisableTiming));
+        VB_CUDA(h, cudaEventCreateWithFlags(&h->ev_slot_free[s], cudaEventDisableTiming));
+    }
+    // zero everything persistent (the reference zero-initialises every buffer, :608-611)
+    VB_CUDA(h, cudaMemsetAsync(h->arena, 0, (size_t)h->arena_bytes, h->stream));
+
+    VB_CUDA(h, cudaMallocHost(&h->mirror_params, (size_t)P * 4));
+    VB_CUDA(h, cudaMallocHost(&h->host_loss, 2 * sizeof(float)));
+    VB_CUDA(h, cudaMallocHost(&h->host_status, sizeof(unsigned int)));
+    h->host_loss[0] = h->host_loss[1] = 0.0f;
+    *h->host_status = 0;
+    memset(h->mirror_params, 0, (size_t)P * 4);
+    uint64_t rng = 42;
+    for (int i = 0; i < n; ++i)
+        lcg_xavier(h->mirror_params + h->off_w[i], (int64_t)L[i] * L[i + 1], L[i], L[i + 1], &rng);
+    VB_CUDA(h, cudaMemcpyAsync(h->params, h->mirror_params, (size_t)P * 4, cudaMemcpyHostToDevice, h->stream));
+    VB_CUDA(h, cudaStreamSynchronize(h->stream));
+
+    if (h->world > 1) {
+        VB_CUDA(h, cudaStreamCreateWithFlags(&h->comm_stream, cudaStreamNonBlocking));
+        VB_CUDA(h, cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming));
+        h->ev_bucket.resize(n + 1);
+        for (auto &ev : h->ev_bucket) VB_CUDA(h, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        h->dp = new DpComm();
+        if (h->dp->init(c.nccl_unique_id, h->world, h->rank)) return h->fail(VB200_ERR_NCCL, h->dp->error());
+    }
+    if (h->use_graph) {
+        int rc = capture_graphs(h);
+        if (rc) return rc;
+    } else {
+        // count the launches of one step without running it: the schedule is fixed
+        h->kernels_per_step = 0;
+    }
+    return VB200_OK;
+}
+
+}  // namespace
+
+// =========================================================================================
+// C ABI
+// =========================================================================================
+extern "C" {
+
+const char *volta_b200_version(void) { return "volta_b200 0.1 (sm_100a)"; }
+
+int volta_b200_create(const vb200_config *cfg, vb200_handle **out) {
+    if (out) *out = nullptr;
+    std::string why;
+    int rc = validate(cfg, &why);
+    if (!out && rc == VB200_OK) { rc = VB200_ERR_INVALID; why = "null output pointer"; }
+    if (rc == VB200_OK) {
+        int ndev = 0;
+        cudaError_t e = cudaGetDeviceCount(&ndev);
+        if (e != cudaSuccess || ndev == 0) {
+            cudaGetLastError();
+            rc = VB200_ERR_CUDA;
+            why = "no CUDA device available: libvolta_b200 has no CPU fallback";
+        }
+    }
+    if (rc != VB200_OK) {
+        std::lock_guard<std::mutex> lk(g_err_mutex);
+        g_create_status = rc;
+        g_create_error = why;
+        return rc;
+    }
+    vb200_handle *h = new vb200_handle();
+    h->cfg = *cfg;
+    rc = build(h);
+    if (rc != VB200_OK) {
+        {
+            std::lock_guard<std::mutex> lk(g_err_mutex);
+            g_create_status = rc;
+            g_create_error = h->error;
+        }
+        destroy(h);
+        return rc;
+    }
+    *out = h;
+    return VB200_OK;
+}
+
+void volta_b200_destroy(vb200_handle *h) { destroy(h); }
+
+int volta_b200_step(vb200_handle *h, const float *X, const float *Y, float lr) {
+    if (!h) return VB200_ERR_INVALID;
+    return do_step(h, X, Y, lr, false);
+}
+
+float volta_b200_loss(vb200_handle *h) {
+    if (!h) return NAN;
+    if (cudaStreamSynchronize(h->stream) != cudaSuccess) {
+        h->fail(VB200_ERR_CUDA, std::string("stream failed: ") + cudaGetErrorString(cudaGetLastError()));
+        return NAN;
+    }
+    check_device_status(h);
+    // mlp_train_rust_codegen.rs:798: last_loss = lacc / nt
+    return h->host_loss[h->last_slot] / (float)h->global_nt;
+}
+
+int volta_b200_set_params(vb200_handle *h, int32_t li, const float *w, const float *b) {
+    if (!h) return VB200_ERR_INVALID;
+    if (li < 0 || li >= h->n) return VB200_OK;  // ignored, as in the reference
+    if (!w || !b) return h->fail(VB200_ERR_INVALID, "set_params: null pointer");
+    const size_t wn = (size_t)h->L[li] * h->L[li + 1], bn = (size_t)h->L[li + 1];
+    VB_CUDA(h, cudaStreamSynchronize(h->stream));
+    VB_CUDA(h, cudaMemcpy(h->params + h->off_w[li], w, wn * 4, cudaMemcpyHostToDevice));
+    VB_CUDA(h, cudaMemcpy(h->params + h->off_b[li], b, bn * 4, cudaMemcpyHostToDevice));
+    return VB200_OK;
+}
+
+int volta_b200_get_params(vb200_handle *h, float **wo, float **bo) {
+    if (!h || !wo || !bo) return VB200_ERR_INVALID;
+    VB_CUDA(h, cudaMemcpyAsync(h->mirror_params, h->params, (size_t)h->n_params_padded * 4, cudaMemcpyDeviceToHost,
+                               h->stream));
+    VB_CUDA(h, cudaStreamSynchronize(h->stream));
+    for (int i = 0; i < h->n; ++i) {
+        wo[i] = h->mirror_params + h->off_w[i];
+        bo[i] = h->mirror_params + h->off_b[i];
+    }
+    return check_device_status(h);
+}
+
+int volta_b200_get_grads(vb200_handle *h, float **dwo, float **dbo) {
+    if (!h || !dwo || !dbo) return VB200_ERR_INVALID;
+    if (!h->mirror_grads) VB_CUDA(h, cudaMallocHost(&h->mirror_grads, (size_t)h->n_params_padded * 4));
+    VB_CUDA(h, cudaMemcpyAsync(h->mirror_grads, h->grads, (size_t)h->n_params_padded * 4, cudaMemcpyDeviceToHost,
+                               h->stream));
+    VB_CUDA(h, cudaStreamSynchronize(h->stream));
+    for (int i = 0; i < h->n; ++i) {
+        dwo[i] = h->mirror_grads + h->off_w[i];
+        dbo[i] = h->mirror_grads + h->off_b[i];
+    }
+    return VB200_OK;
+}
+
+int64_t volta_b200_state_floats(vb200_handle *h) {
+    if (!h) return 0;
+    const int opt = h->cfg.optimizer;
+    if (opt == VB200_OPT_SGD) return 0;
+    return (opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW) ? 2 * h->n_params_padded : h->n_params_padded;
+}
+
+int volta_b200_save_state(vb200_handle *h, float *out, int64_t n, uint64_t *step_out) {
+    if (!h) return VB200_ERR_INVALID;
+    const int64_t need = volta_b200_state_floats(h);
+    if (n < need || (need && !out)) return h->fail(VB200_ERR_INVALID, "save_state: buffer too small");
+    VB_CUDA(h, cudaStreamSynchronize(h->stream));
+    const int64_t P = h->n_params_padded;
+    if (need >= P) VB_CUDA(h, cudaMemcpy(out, h->s1, (size_t)P * 4, cudaMemcpyDeviceToHost));
+    if (need >= 2 * P) VB_CUDA(h, cudaMemcpy(out + P, h->s2, (size_t)P * 4, cudaMemcpyDeviceToHost));
+    if (step_out) *step_out = h->adam_step;
+    return VB200_OK;
+}
+
+int volta_b200_load_state(vb200_handle *h, const float *in, int64_t n, uint64_t step) {
+    if (!h) return VB200_ERR_INVALID;
+    const int64_t need = volta_b200_state_floats(h);
+    if (n < need || (need && !in)) return h->fail(VB200_ERR_INVALID, "load_state: buffer too small");
+    VB_CUDA(h, cudaStreamSynchronize(h->stream));
+    const int64_t P = h->n_params_padded;
+    if (need >= P) VB_CUDA(h, cudaMemcpy(h->s1, in, (size_t)P * 4, cudaMemcpyHostToDevice));
+    if (need >= 2 * P) VB_CUDA(h, cudaMemcpy(h->s2, in + P, (size_t)P * 4, cudaMemcpyHostToDevice));
+    h->adam_step = step;
+    return VB200_OK;
+}
+
+int volta_b200_status(vb200_handle *h) {
+    if (!h) {
+        std::lock_guard<std::mutex> lk(g_err_mutex);
+        return g_create_status;
+    }
+    return h->status;
+}
+
+const char *volta_b200_last_error(vb200_handle *h) {
+    if (!h) {
+        std::lock_guard<std::mutex> lk(g_err_mutex);
+        return g_create_error.c_str();
+    }
+    return h->error.c_str();
+}
+
+void *volta_b200_stream(vb200_handle *h) { return h ? (void *)h->stream : nullptr; }
+
+int volta_b200_synchronize(vb200_handle *h) {
+    if (!h) return VB200_ERR_INVALID;
+    VB_CUDA(h, cudaStreamSynchronize(h->copy_stream));
+    VB_CUDA(h, cudaStreamSynchronize(h->stream));
+    return check_device_status(h);
+}
+
+int64_t volta_b200_arena_bytes(vb200_handle *h) { return h ? h->arena_bytes : 0; }
+
+int volta_b200_plan(const vb200_config *cfg, int64_t *arena_bytes, int64_t *unshared_bytes, char *report,
+                    int64_t report_len) {
+    std::string why;
+    int rc = validate(cfg, &why);
+    if (rc) {
+        std::lock_guard<std::mutex> lk(g_err_mutex);
+        g_create_status = rc;
+        g_create_error = why;
+        return rc;
+    }
+    ArenaPlan pl;
+    PlanIdx ix;
+    std::vector<int64_t> ow, ob;
+    int64_t nw = 0, np = 0;
+    make_plan(*cfg, pl, ix, ow, ob, nw, np);
+    if (!pl.verify(&why)) {
+        std::lock_guard<std::mutex> lk(g_err_mutex);
+        g_create_status = VB200_ERR_INVALID;
+        g_create_error = "memory plan rejected: " + why;
+        return VB200_ERR_INVALID;
+    }
+    if (arena_bytes) *arena_bytes = pl.total();
+    if (unshared_bytes) *unshared_bytes = pl.sum_unshared();
+    if (report && report_len > 0) {
+        std::string txt;
+        char line[160];
+        for (auto &b : pl.buffers()) {
+            snprintf(line, sizeof line, "%s %lld %lld %d %d %d\n", b.name.c_str(), (long long)b.offset,
+                     (long long)b.bytes, b.first_use, b.last_use, b.persistent ? 1 : 0);
+            txt += line;
+        }
+        strncpy(report, txt.c_str(), (size_t)report_len - 1);
+        report[report_len - 1] = 0;
+    }
+    return VB200_OK;
+}
+int32_t volta_b200_kernels_per_step(vb200_handle *h) { return h ? h->kernels_per_step : 0; }
+
+int volta_b200_profile_step(vb200_handle *h, const float *X, const float *Y, float lr, vb200_kernel_record *out,
+                            int32_t max) {
+    if (!h) return -VB200_ERR_INVALID;
+    if (h->dp) {
+        h->fail(VB200_ERR_UNSUPPORTED, "profile_step is single-GPU only");
+        return -VB200_ERR_UNSUPPORTED;
+    }
+    for (auto &r : h->records) { cudaEventDestroy(r.e0); cudaEventDestroy(r.e1); }
+    h->records.clear();
+    int rc = do_step(h, X, Y, lr, true);
+    if (rc) return -rc;
+    if (cudaStreamSynchronize(h->stream) != cudaSuccess) {
+        h->fail(VB200_ERR_CUDA, "profile_step: stream failed");
+        return -VB200_ERR_CUDA;
+    }
+    int cnt = 0;
+    for (auto &r : h->records) {
+        if (cnt >= max || !out) break;
+        vb200_kernel_record &o = out[cnt++];
+        memset(&o, 0, sizeof o);
+        strncpy(o.name, r.name.c_str(), sizeof(o.name) - 1);
+        cudaEventElapsedTime(&o.ms, r.e0, r.e1);
+        o.flops = r.flops;
+        o.bytes = r.bytes;
+    }
+    return cnt;
+}
+
+int volta_b200_dp_unique_id(uint8_t out[128]) { return DpComm::unique_id(out) ? VB200_ERR_NCCL : VB200_OK; }
+
+// ---- stand-alone kernel entry points ------------------------------------------------------
+int volta_b200_optimizer_apply(int32_t optimizer, float *p, float *s1, float *s2, const float *g, int64_t n,
+                               int64_t n_decay, float lr, float weight_decay, float momentum, uint64_t t,
+                               void *stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    StepScalars sc{};
+    sc.lr = lr; sc.beta1 = 0.9f; sc.beta2 = 0.999f; sc.eps = 1e-8f;
+    sc.weight_decay = weight_decay; sc.momentum = momentum;
+    sc.bc1 = 1.0f - powf(0.9f, (float)t);
+    sc.bc2 = 1.0f - powf(0.999f, (float)t);
+    StepScalars *d = nullptr;
+    if (cudaMalloc(&d, sizeof(StepScalars)) != cudaSuccess) return VB200_ERR_OOM;
+    cudaError_t e = launch_set_scalars(d, sc, s);
+    if (e == cudaSuccess) e = launch_optimizer(optimizer, p, s1 ? s1 : p, s2 ? s2 : p, g, n, n_decay, d, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    cudaFree(d);
+    return e == cudaSuccess ? VB200_OK : VB200_ERR_CUDA;
+}
+
+int volta_b200_gemm(int32_t layout, int32_t path, float *C, const float *A, const float *B, int64_t m, int64_t n,
+                    int64_t k, void *stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    Epilogue e{};
+    e.mode = EPI_STORE;
+    e.out0 = C;
+    e.ld = n;
+    cudaError_t err;
+    if (path == VB200_GEMM_TENSOR) {
+        if (!gemm_tc_supported(layout, A, B, m, n, k, e)) return VB200_ERR_UNSUPPORTED;
+        unsigned int *st = nullptr;
+        if (cudaMalloc(&st, sizeof(unsigned int)) != cudaSuccess) return VB200_ERR_OOM;
+        cudaMemsetAsync(st, 0, sizeof(unsigned int), s);
+        err = launch_gemm_tc(layout, A, B, m, n, k, e, st, s);
+        unsigned int hs = 0;
+        if (err == cudaSuccess) err = cudaMemcpyAsync(&hs, st, sizeof hs, cudaMemcpyDeviceToHost, s);
+        if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+        cudaFree(st);
+        if (err == cudaSuccess && hs != 0) return VB200_ERR_DEVICE_WAIT;
+    } else {
+        err = launch_gemm_ffma(layout, A, B, m, n, k, e, s);
+    }
+    return err == cudaSuccess ? VB200_OK : VB200_ERR_CUDA;
+}
+
+int64_t volta_b200_colsum_scratch_floats(int64_t rows, int64_t cols) {
+    if (rows <= 0 || cols <= 0) return 0;
+    return colsum_chunks(rows, cols) * cols;
+}
+
+int volta_b200_colsum(float *out, const float *in, int64_t rows, int64_t cols, float *scratch, void *stream) {
+    if (!out || !in || !scratch) return VB200_ERR_INVALID;
+    cudaError_t e = launch_colsum(out, in, rows, cols, scratch, (cudaStream_t)stream);
+    return e == cudaSuccess ? VB200_OK : VB200_ERR_CUDA;
+}
+
+}  // extern "C"

@@ -1,0 +1,92 @@
+"""Loads libvolta_b200.so and declares its C ABI (include/volta_b200.h) for ctypes."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+VB200_MAX_LAYERS = 32
+
+
+class VoltaB200Error(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__("libvolta_b200 error %d: %s" % (code, message))
+        self.code = code
+
+
+class Config(C.Structure):
+    _fields_ = [
+        ("n_sizes", C.c_int32), ("layers", C.c_int32 * VB200_MAX_LAYERS), ("activation", C.c_int32),
+        ("optimizer", C.c_int32), ("batch", C.c_int32), ("global_batch", C.c_int32), ("world_size", C.c_int32),
+        ("rank", C.c_int32), ("nccl_unique_id", C.c_uint8 * 128), ("momentum", C.c_float),
+        ("weight_decay", C.c_float), ("gemm_path", C.c_int32), ("use_graph", C.c_int32),
+        ("reserved", C.c_int32 * 8),
+    ]
+
+
+class KernelRecord(C.Structure):
+    _fields_ = [("name", C.c_char * 48), ("ms", C.c_float), ("flops", C.c_double), ("bytes", C.c_double)]
+
+
+# every symbol include/volta_b200.h declares
+EXPORTS = [
+    "volta_b200_create", "volta_b200_destroy", "volta_b200_step", "volta_b200_loss", "volta_b200_set_params",
+    "volta_b200_get_params", "volta_b200_get_grads", "volta_b200_state_floats", "volta_b200_save_state",
+    "volta_b200_load_state", "volta_b200_status", "volta_b200_last_error", "volta_b200_stream",
+    "volta_b200_synchronize", "volta_b200_arena_bytes", "volta_b200_plan", "volta_b200_kernels_per_step",
+    "volta_b200_profile_step", "volta_b200_dp_unique_id", "volta_b200_optimizer_apply", "volta_b200_gemm",
+    "volta_b200_colsum_scratch_floats", "volta_b200_colsum", "volta_b200_version",
+]
+
+_lib = None
+
+
+def library_path() -> str:
+    return os.environ.get("VOLTA_B200_LIB", os.path.join(HERE, "libvolta_b200.so"))
+
+
+def load_library():
+    """Load the compiled library; raises if it has not been built (no fallback exists)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    if not os.path.exists(path):
+        raise VoltaB200Error(-1, "%s is missing: build it with `python -m volta_b200.build` "
+                                 "(there is no CPU or PyTorch fallback)" % path)
+    lib = C.CDLL(path)
+    fp, vp, i32, i64 = C.POINTER(C.c_float), C.c_void_p, C.c_int32, C.c_int64
+    fpp = C.POINTER(fp)
+    sig = {
+        "volta_b200_create": (C.c_int, [C.POINTER(Config), C.POINTER(vp)]),
+        "volta_b200_destroy": (None, [vp]),
+        "volta_b200_step": (C.c_int, [vp, vp, vp, C.c_float]),
+        "volta_b200_loss": (C.c_float, [vp]),
+        "volta_b200_set_params": (C.c_int, [vp, i32, fp, fp]),
+        "volta_b200_get_params": (C.c_int, [vp, fpp, fpp]),
+        "volta_b200_get_grads": (C.c_int, [vp, fpp, fpp]),
+        "volta_b200_state_floats": (i64, [vp]),
+        "volta_b200_save_state": (C.c_int, [vp, fp, i64, C.POINTER(C.c_uint64)]),
+        "volta_b200_load_state": (C.c_int, [vp, fp, i64, C.c_uint64]),
+        "volta_b200_status": (C.c_int, [vp]),
+        "volta_b200_last_error": (C.c_char_p, [vp]),
+        "volta_b200_stream": (vp, [vp]),
+        "volta_b200_synchronize": (C.c_int, [vp]),
+        "volta_b200_arena_bytes": (i64, [vp]),
+        "volta_b200_kernels_per_step": (i32, [vp]),
+        "volta_b200_plan": (C.c_int, [C.POINTER(Config), C.POINTER(i64), C.POINTER(i64), C.c_char_p, i64]),
+        "volta_b200_profile_step": (C.c_int, [vp, vp, vp, C.c_float, C.POINTER(KernelRecord), i32]),
+        "volta_b200_dp_unique_id": (C.c_int, [C.POINTER(C.c_uint8 * 128)]),
+        "volta_b200_optimizer_apply": (C.c_int, [i32, vp, vp, vp, vp, i64, i64, C.c_float, C.c_float, C.c_float,
+                                                 C.c_uint64, vp]),
+        "volta_b200_gemm": (C.c_int, [i32, i32, vp, vp, vp, i64, i64, i64, vp]),
+        "volta_b200_colsum_scratch_floats": (i64, [i64, i64]),
+        "volta_b200_colsum": (C.c_int, [vp, vp, i64, i64, vp, vp]),
+        "volta_b200_version": (C.c_char_p, []),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
