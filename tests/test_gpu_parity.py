@@ -168,6 +168,37 @@ def test_reference_pytorch_fixtures_through_the_gpu_path(name, opt):
     g.free()
 
 
+def first_step_weight_tolerance(opt, w_ref, g_ref, lr):
+    """Allowed |w_gpu - w_oracle| per element after ONE step: 1e-5 of the tensor's largest
+    weight, plus - for Adam/AdamW only - what a gradient perturbation of 1e-5 of the
+    tensor's largest gradient does to the first Adam update u = lr*g/(|g|+eps).  That
+    update is sign-like: where |g| is below the fp32 noise floor of the gradient GEMM it
+    flips between -lr and +lr, so two correct fp32 summation orders (and the fp32 oracle
+    versus its own fp64 shadow, see test_adam_first_step_is_ill_conditioned_in_the_oracle_too)
+    differ there by up to 2*lr.  Everywhere else the extra term is negligible."""
+    tol = np.full(w_ref.shape, W_TOL * float(np.max(np.abs(w_ref))), np.float64)
+    if opt in ("adam", "adamw"):
+        g = g_ref.astype(np.float64)
+        d = W_TOL * float(np.max(np.abs(g)))
+        u = lambda v: lr * v / (np.abs(v) + 1e-8)
+        tol += np.maximum(np.abs(u(g + d) - u(g)), np.abs(u(g - d) - u(g)))
+    return tol
+
+
+def assert_first_step(g, o, opt, lr):
+    gdw, gdb = g.get_grads()
+    odw, odb = o.get_grads()
+    for a, b in zip(gdw + gdb, odw + odb):
+        assert rel_err(a, b) <= W_TOL, "gradients of the first step"
+    loose = 0
+    for a, b, gr in zip(sum(g.get_params(), []), sum(o.get_params(), []), odw + odb):
+        tol = first_step_weight_tolerance(opt, b, gr, lr)
+        assert np.all(np.abs(a.astype(np.float64) - b) <= tol), "weights after one step"
+        loose += int(np.sum(tol > 2 * W_TOL * float(np.max(np.abs(b)))))
+    # the conditioning allowance may touch only a vanishing share of the parameters
+    assert loose <= 1e-3 * sum(p.size for p in sum(o.get_params(), [])), loose
+
+
 def _config_run(cfg, B, steps, gemm_path="auto"):
     layers = list(cfg.layers)
     g, o = _pair(layers, cfg.activation, cfg.optimizer, B, gemm_path=gemm_path)
@@ -177,8 +208,7 @@ def _config_run(cfg, B, steps, gemm_path="auto"):
         g.step(x, y, cfg.lr)
         o.step(x, y, cfg.lr)
         if step == 0:
-            for a, b in zip(sum(g.get_params(), []), sum(o.get_params(), [])):
-                assert rel_err(a, b) <= W_TOL, "weights after one step"
+            assert_first_step(g, o, cfg.optimizer, cfg.lr)
     lg, lo = g.loss(), o.loss()
     assert abs(lg - lo) <= LOSS_TOL * abs(lo), "loss after %d steps: %g vs %g" % (steps, lg, lo)
     g.free()
