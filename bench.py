@@ -163,10 +163,15 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--gemm-path", default="auto", choices=["auto", "ffma", "tensor"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="override the workload's global batch (for small profiler captures; not a headline number)")
     args = ap.parse_args()
 
     from volta_b200 import CONFIGS
     cfg = CONFIGS[args.workload]
+    if args.batch:
+        import dataclasses
+        cfg = dataclasses.replace(cfg, batch=args.batch, note=(cfg.note + "; batch overridden to %d" % args.batch).strip("; "))
     steps = args.steps if args.steps is not None else (10 if cfg.batch > 4096 else cfg.steps)
     warmup = max(args.warmup, 0)
     rank = int(os.environ.get("RANK", "0"))

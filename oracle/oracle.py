@@ -26,6 +26,9 @@ def _lib(real: str):
         lib.oracle_free.argtypes = [C.c_void_p]
         lib.oracle_set_momentum.argtypes = [C.c_void_p, C.c_double]
         lib.oracle_set_decay_bias.argtypes = [C.c_void_p, C.c_int]
+        lib.oracle_set_global_batch.argtypes = [C.c_void_p, C.c_longlong]
+        lib.oracle_grad_step.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]
+        lib.oracle_update.argtypes = [C.c_void_p, C.c_float]
         lib.oracle_set_gemm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         lib.oracle_set_params.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float)]
         lib.oracle_get_params.argtypes = [C.c_void_p, C.POINTER(rp), C.POINTER(rp)]
@@ -122,6 +125,28 @@ class Oracle:
         y = np.ascontiguousarray(y, dtype=np.float32)
         assert x.size == self.batch * self.layers[0] and y.size == self.batch * self.layers[-1]
         self.lib.oracle_step(self.h, _fp(x), _fp(y), float(lr))
+
+    def set_global_batch(self, gb: int):
+        """This handle holds one shard of a global batch of gb rows (data parallel)."""
+        self.lib.oracle_set_global_batch(self.h, int(gb))
+
+    def grad_step(self, x: np.ndarray, y: np.ndarray):
+        """Forward + backward + gradients, no update."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        y = np.ascontiguousarray(y, dtype=np.float32)
+        self.lib.oracle_grad_step(self.h, _fp(x), _fp(y))
+
+    def update(self, lr: float):
+        self.lib.oracle_update(self.h, float(lr))
+
+    def grad_views(self):
+        """Writable numpy views of the gradients held in the handle (for an external all-reduce)."""
+        wo = (self._rp * self.n)()
+        bo = (self._rp * self.n)()
+        self.lib.oracle_get_grads(self.h, wo, bo)
+        ws = [np.ctypeslib.as_array(wo[i], shape=(self.layers[i], self.layers[i + 1])) for i in range(self.n)]
+        bs = [np.ctypeslib.as_array(bo[i], shape=(self.layers[i + 1],)) for i in range(self.n)]
+        return ws, bs
 
     def loss(self) -> float:
         return float(self.lib.oracle_loss(self.h))

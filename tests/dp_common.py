@@ -1,0 +1,84 @@
+"""Shared pieces of the data-parallel tests: the worker both the CPU (gloo + oracle) and the
+GPU (libvolta_b200 + NCCL) tests run in every rank."""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+LAYERS = [96, 160, 128, 1]
+GLOBAL_BATCH = 64
+STEPS = 4
+
+
+def inputs(cfg_act="silu"):
+    from volta_b200 import synth
+    x = synth.rows("uniform", 1234, 0, GLOBAL_BATCH, LAYERS[0])
+    y = synth.rows("normal", 4321, 0, GLOBAL_BATCH, LAYERS[-1])
+    ws, bs = synth.kaiming_uniform_weights(LAYERS, 42)
+    return x, y, ws, bs
+
+
+def oracle_shard_worker(rank, world, port, opt, real, out_dir):
+    """One CPU rank: oracle on its row shard, gradients summed over ranks with gloo in rank
+    order, identical update everywhere.  Writes its final parameters and loss trace."""
+    import torch
+    import torch.distributed as dist
+    from oracle.oracle import Oracle
+
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+    x, y, ws, bs = inputs()
+    B = GLOBAL_BATCH // world
+    xs, ys = x[rank * B:(rank + 1) * B], y[rank * B:(rank + 1) * B]
+    o = Oracle(LAYERS, "silu", opt, B, real=real)
+    o.set_global_batch(GLOBAL_BATCH)
+    for i, (w, b) in enumerate(zip(ws, bs)):
+        o.set_params(i, w, b)
+    losses = []
+    for _ in range(STEPS):
+        o.grad_step(xs, ys)
+        gw, gb = o.grad_views()
+        for g in gw + gb:
+            t = torch.from_numpy(g)
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        lt = torch.tensor([o.loss()], dtype=torch.float64)
+        dist.all_reduce(lt, op=dist.ReduceOp.SUM)
+        losses.append(float(lt.item()))
+        o.update(0.01)
+    pw, pb = o.get_params()
+    np.savez(os.path.join(out_dir, "rank%d.npz" % rank), losses=np.array(losses),
+             **{"w%d" % i: w for i, w in enumerate(pw)}, **{"b%d" % i: b for i, b in enumerate(pb)})
+    dist.destroy_process_group()
+
+
+def gpu_shard_worker(rank, world, port, opt, out_dir, repeat):
+    """One GPU rank: libvolta_b200 handle on its row shard; the unique id travels over gloo."""
+    import torch
+    import torch.distributed as dist
+    from volta_b200 import TrainHandle
+    from volta_b200.train import dp_unique_id
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+    x, y, ws, bs = inputs()
+    B = GLOBAL_BATCH // world
+    xs, ys = np.ascontiguousarray(x[rank * B:(rank + 1) * B]), np.ascontiguousarray(y[rank * B:(rank + 1) * B])
+    for rep in range(repeat):
+        box = [dp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        h = TrainHandle(LAYERS, "silu", opt, B, global_batch=GLOBAL_BATCH, world_size=world, rank=rank, unique_id=box[0])
+        for i, (w, b) in enumerate(zip(ws, bs)):
+            h.set_params(i, w, b)
+        losses = []
+        for _ in range(STEPS):
+            h.step(xs, ys, 0.01)
+            losses.append(h.loss())
+        pw, pb = h.get_params()
+        np.savez(os.path.join(out_dir, "rank%d_rep%d.npz" % (rank, rep)), losses=np.array(losses, dtype=np.float32),
+                 **{"w%d" % i: w for i, w in enumerate(pw)}, **{"b%d" % i: b for i, b in enumerate(pb)})
+        h.free()
+        dist.barrier()
+    dist.destroy_process_group()

@@ -1,0 +1,52 @@
+"""Data parallelism on real GPUs (needs >= 2): two ranks of libvolta_b200 with bucketed NCCL
+all-reduce against the single-process oracle on the full batch; replicas bit-identical; two
+runs bit-identical."""
+import socket
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from oracle.oracle import Oracle
+from tests import dp_common as dpc
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("opt", ["sgd_momentum", "adam"])
+def test_two_gpu_ranks_match_the_full_batch_oracle(opt):
+    world = 2
+    out = tempfile.mkdtemp()
+    mp.spawn(dpc.gpu_shard_worker, args=(world, _free_port(), opt, out, 2), nprocs=world, join=True)
+    x, y, ws, bs = dpc.inputs()
+    o = Oracle(dpc.LAYERS, "silu", opt, dpc.GLOBAL_BATCH)
+    for i, (w, b) in enumerate(zip(ws, bs)):
+        o.set_params(i, w, b)
+    losses = []
+    for _ in range(dpc.STEPS):
+        o.step(x, y, 0.01)
+        losses.append(o.loss())
+    pw, pb = o.get_params()
+    runs = [[np.load("%s/rank%d_rep%d.npz" % (out, r, rep)) for r in range(world)] for rep in range(2)]
+    for rep in runs:
+        for r in rep:
+            np.testing.assert_allclose(r["losses"], losses, rtol=1e-5)
+            for i in range(len(pw)):
+                assert np.max(np.abs(r["w%d" % i] - pw[i])) <= 1e-4 * np.max(np.abs(pw[i]))
+        for i in range(len(pw)):  # replicas bit-identical
+            assert np.array_equal(rep[0]["w%d" % i], rep[1]["w%d" % i])
+            assert np.array_equal(rep[0]["b%d" % i], rep[1]["b%d" % i])
+    for i in range(len(pw)):      # run-to-run bit-identical at a fixed GPU count
+        assert np.array_equal(runs[0][0]["w%d" % i], runs[1][0]["w%d" % i])
+    assert np.array_equal(runs[0][0]["losses"], runs[1][0]["losses"])

@@ -190,13 +190,15 @@ def assert_first_step(g, o, opt, lr):
     odw, odb = o.get_grads()
     for a, b in zip(gdw + gdb, odw + odb):
         assert rel_err(a, b) <= W_TOL, "gradients of the first step"
-    loose = 0
+    beyond = 0
     for a, b, gr in zip(sum(g.get_params(), []), sum(o.get_params(), []), odw + odb):
         tol = first_step_weight_tolerance(opt, b, gr, lr)
-        assert np.all(np.abs(a.astype(np.float64) - b) <= tol), "weights after one step"
-        loose += int(np.sum(tol > 2 * W_TOL * float(np.max(np.abs(b)))))
-    # the conditioning allowance may touch only a vanishing share of the parameters
-    assert loose <= 1e-3 * sum(p.size for p in sum(o.get_params(), [])), loose
+        diff = np.abs(a.astype(np.float64) - b)
+        assert np.all(diff <= tol), "weights after one step"
+        beyond += int(np.sum(diff > W_TOL * float(np.max(np.abs(b)))))
+    # only a vanishing share of the parameters may need the conditioning allowance at all
+    # (the fp32 oracle against its fp64 shadow needs it for ~3e-5 of them)
+    assert beyond <= 2e-4 * sum(p.size for p in sum(o.get_params(), [])), beyond
 
 
 def _config_run(cfg, B, steps, gemm_path="auto"):

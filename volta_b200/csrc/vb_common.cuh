@@ -153,7 +153,12 @@ cudaError_t launch_optimizer(int optimizer, float *p, float *s1, float *s2, cons
 cudaError_t launch_set_scalars(StepScalars *dst, StepScalars v, cudaStream_t s);
 
 long long colsum_chunks(long long rows, long long cols);
-cudaError_t launch_colsum(float *out, const float *in, long long rows, long long cols, float *scratch, cudaStream_t s);
+// out[j] = sum_rows in[row, j] * (row_weight ? row_weight[row] : 1), fixed order
+cudaError_t launch_colsum(float *out, const float *in, long long rows, long long cols, float *scratch, cudaStream_t s,
+                          const float *row_weight = nullptr);
+// out[row] = in[row, :] . w + bias[0]
+cudaError_t launch_rowdot(float *out, const float *in, const float *w, const float *bias, long long rows,
+                          long long cols, cudaStream_t s);
 
 long long loss_blocks(long long nt);
 // delta[k] = 2*(out[k]-y[k])/nt_global ; *loss_sum = sum_k (out[k]-y[k])^2 (fixed order)

@@ -149,7 +149,8 @@ long long colsum_chunks(long long rows, long long cols) {
 }
 
 __global__ void __launch_bounds__(32 * CS_TY) colsum_pass1(float *__restrict__ partial, const float *__restrict__ in,
-                                                           long long rows, long long cols, long long rows_per_chunk) {
+                                                           const float *__restrict__ wgt, long long rows,
+                                                           long long cols, long long rows_per_chunk) {
     __shared__ float4 sm[CS_TY][32];
     const int tx = threadIdx.x, ty = threadIdx.y;
     const long long c0 = (long long)blockIdx.x * CS_COLS + tx * 4;
@@ -162,15 +163,18 @@ __global__ void __launch_bounds__(32 * CS_TY) colsum_pass1(float *__restrict__ p
         if (c0 < cols)
             for (long long r = r0 + ty; r < r1; r += CS_TY) {
                 float4 v = __ldg(reinterpret_cast<const float4 *>(in + r * cols + c0));
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                const float w = wgt ? wgt[r] : 1.0f;
+                acc.x = fmaf(v.x, w, acc.x); acc.y = fmaf(v.y, w, acc.y);
+                acc.z = fmaf(v.z, w, acc.z); acc.w = fmaf(v.w, w, acc.w);
             }
     } else {
         for (long long r = r0 + ty; r < r1; r += CS_TY) {
             const float *row = in + r * cols;
-            if (c0 + 0 < cols) acc.x += row[c0 + 0];
-            if (c0 + 1 < cols) acc.y += row[c0 + 1];
-            if (c0 + 2 < cols) acc.z += row[c0 + 2];
-            if (c0 + 3 < cols) acc.w += row[c0 + 3];
+            const float w = wgt ? wgt[r] : 1.0f;
+            if (c0 + 0 < cols) acc.x = fmaf(row[c0 + 0], w, acc.x);
+            if (c0 + 1 < cols) acc.y = fmaf(row[c0 + 1], w, acc.y);
+            if (c0 + 2 < cols) acc.z = fmaf(row[c0 + 2], w, acc.z);
+            if (c0 + 3 < cols) acc.w = fmaf(row[c0 + 3], w, acc.w);
         }
     }
     sm[ty][tx] = acc;
@@ -200,15 +204,52 @@ __global__ void colsum_pass2(float *__restrict__ out, const float *__restrict__ 
 }
 
 cudaError_t launch_colsum(float *out, const float *in, long long rows, long long cols, float *scratch,
-                          cudaStream_t s) {
+                          cudaStream_t s, const float *row_weight) {
     if (rows <= 0 || cols <= 0) return cudaErrorInvalidValue;
     long long chunks = colsum_chunks(rows, cols);
     long long rpc = (rows + chunks - 1) / chunks;
     dim3 grid((unsigned)((cols + CS_COLS - 1) / CS_COLS), (unsigned)chunks), block(32, CS_TY);
-    colsum_pass1<<<grid, block, 0, s>>>(scratch, in, rows, cols, rpc);
+    colsum_pass1<<<grid, block, 0, s>>>(scratch, in, row_weight, rows, cols, rpc);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     colsum_pass2<<<(unsigned)((cols + 255) / 256), 256, 0, s>>>(out, scratch, chunks, cols);
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------
+// Output layer of width one: out[row] = in[row, :] . w + bias[0].  One warp per row, each
+// lane a fixed strided share of the columns, then a fixed shuffle tree.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) rowdot_kernel(float *__restrict__ out, const float *__restrict__ in,
+                                                     const float *__restrict__ w, const float *__restrict__ bias,
+                                                     long long rows, long long cols) {
+    const int lane = threadIdx.x & 31;
+    const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+    const bool vec = ((cols & 3) == 0) && (((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(w)) & 15) == 0);
+    for (long long row = (((long long)blockIdx.x * blockDim.x) + threadIdx.x) >> 5; row < rows; row += warps) {
+        const float *src = in + row * cols;
+        float acc = 0.0f;
+        if (vec) {
+            for (long long c = lane * 4; c < cols; c += 128) {
+                float4 a = __ldcs(reinterpret_cast<const float4 *>(src + c));
+                float4 b = __ldg(reinterpret_cast<const float4 *>(w + c));
+                acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+            }
+        } else {
+            for (long long c = lane; c < cols; c += 32) acc = fmaf(src[c], w[c], acc);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+        if (lane == 0) out[row] = acc + (bias ? bias[0] : 0.0f);
+    }
+}
+
+cudaError_t launch_rowdot(float *out, const float *in, const float *w, const float *bias, long long rows,
+                          long long cols, cudaStream_t s) {
+    if (rows <= 0 || cols <= 0) return cudaErrorInvalidValue;
+    long long want = (rows + 7) / 8, cap = (long long)sm_count() * 8;
+    int blocks = (int)(want > cap ? cap : want);
+    rowdot_kernel<<<blocks, 256, 0, s>>>(out, in, w, bias, rows, cols);
     return cudaGetLastError();
 }
 

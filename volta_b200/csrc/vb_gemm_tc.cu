@@ -14,9 +14,13 @@
 //                   layout the tensor core reads; operands stored with M or N contiguous
 //                   (W in the forward pass, both operands of dW) are transposed on the way, so
 //                   no matrix is ever transposed in global memory;
-//   MMA warp        one thread issues, per 8-deep k-step, A_lo.B_hi, A_hi.B_lo, A_hi.B_hi
-//                   (small terms first) into the same fp32 accumulator in TMEM, then commits the
-//                   stage back to the split warps;
+//   MMA warp        one thread issues, per 8-deep k-step, A_lo.B_hi, A_hi.B_lo and A_hi.B_hi into
+//                   fp32 accumulators in TMEM, then commits the stage back to the split warps.
+//                   The tensor core truncates (rounds toward zero) when it adds into an
+//                   accumulator, a bias that grows with the number of additions and with the
+//                   accumulator's magnitude; so the two cross terms have an accumulator of their
+//                   own and A_hi.B_hi rotates over three more, and the epilogue adds the four in
+//                   fp32 with round-to-nearest (measured: ~9x less error than one accumulator);
 // after the last k-block the split warps become the epilogue: tcgen05.ld the accumulator
 // (lane = row) and apply the fused epilogue (bias + activation, activation derivative, or a
 // plain store) straight to global memory.
@@ -42,7 +46,8 @@ constexpr int RAW_STAGE_BYTES = 2 * TILE_BYTES;
 constexpr int MMA_STAGE_BYTES = 4 * TILE_BYTES;
 constexpr int SMEM_TILES = RAW_STAGES * RAW_STAGE_BYTES + MMA_STAGES * MMA_STAGE_BYTES;
 constexpr int SMEM_BYTES = SMEM_TILES + 256 + 1024;  // + barriers + room to align the base to 1 KiB
-constexpr int TMEM_COLS = 128;
+constexpr int NUM_MAIN = 3;               // hi.hi accumulators, used round-robin by k-step
+constexpr int TMEM_COLS = 512;            // NUM_MAIN + 1 accumulators of BN fp32 columns (all of TMEM)
 constexpr int GROUP_M = 8;  // tiles are walked in bands of 8 tile rows so that a wave shares operands in L2
 
 // status codes (which wait gave up)
@@ -282,9 +287,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < BK / 8; ++j) {
                     const uint64_t adv = (uint64_t)(j * 32 >> 4);  // 8 tf32 = 32 bytes further along the swizzled row
-                    umma_tf32(tmem_base, a_lo + adv, b_hi + adv, (kb | j) != 0 ? 1u : 0u);
-                    umma_tf32(tmem_base, a_hi + adv, b_lo + adv, 1u);
-                    umma_tf32(tmem_base, a_hi + adv, b_hi + adv, 1u);
+                    const int ks = kb * (BK / 8) + j;
+                    // cross terms go to their own accumulator; hi.hi rotates over NUM_MAIN accumulators
+                    umma_tf32(tmem_base + NUM_MAIN * BN, a_lo + adv, b_hi + adv, ks != 0 ? 1u : 0u);
+                    umma_tf32(tmem_base + NUM_MAIN * BN, a_hi + adv, b_lo + adv, 1u);
+                    umma_tf32(tmem_base + (uint32_t)(ks % NUM_MAIN) * BN, a_hi + adv, b_hi + adv, ks >= NUM_MAIN ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&mma_empty[s]));
             }
@@ -324,7 +331,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int c = 0; c < 2; ++c) {
                 const int col0 = half * 64 + c * 32;
                 uint32_t v[32];
-                tmem_load_32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0, v);
+                {
+                    const uint32_t t = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0;
+                    uint32_t w[32];
+                    tmem_load_32(t + NUM_MAIN * BN, v);  // cross terms first
+#pragma unroll
+                    for (int a = 0; a < NUM_MAIN; ++a) {
+                        tmem_load_32(t + a * BN, w);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(w[j]));
+                    }
+                }
                 if (m < M) {
 #pragma unroll
                     for (int j = 0; j < 32; j += 4) {

@@ -171,6 +171,13 @@ int enqueue_step(vb200_handle *h, int slot) {
             e.out0 = h->act[i + 1];
             e.out1 = act_needs_pre(act) ? h->pre[i] : nullptr;
         }
+        if (i == n - 1 && c == 1) {
+            // width-one output layer: a row-dot, bandwidth-bound on act_i
+            snprintf(nm, sizeof nm, "fwd%d_rowdot_%lldx%lld", i, (long long)B, r);
+            Scope sc(h, nm, 2.0 * B * r, 4.0 * (B * r + r + B));
+            VB_CUDA(h, launch_rowdot(h->act[n], A(i), h->params + h->off_w[i], e.bias, B, r, s));
+            continue;
+        }
         snprintf(nm, sizeof nm, "fwd%d_gemm_nn_%lldx%lldx%lld", i, (long long)B, c, r);
         Scope sc(h, nm, 2.0 * B * r * c, 4.0 * (B * r + r * c + B * c * (e.out1 ? 2 : 1)));
         VB_CUDA(h, run_gemm(h, GEMM_NN, A(i), h->params + h->off_w[i], B, c, r, e));
@@ -186,7 +193,13 @@ int enqueue_step(vb200_handle *h, int slot) {
     // backward
     for (int i = n - 1; i >= 0; --i) {
         const long long r = L[i], c = L[i + 1];
-        {
+        if (c == 1) {
+            // dW of a width-one layer: column sums of act_i weighted by delta_i[row]
+            snprintf(nm, sizeof nm, "dW%d_wcolsum_%lldx%lld", i, (long long)B, r);
+            Scope sc(h, nm, 2.0 * B * r, 4.0 * (B * r + B + r));
+            h->kernels_per_step++;
+            VB_CUDA(h, launch_colsum(h->grads + h->off_w[i], A(i), B, r, h->colsum_scratch, s, h->delta[i]));
+        } else {
             Epilogue e{};
             e.mode = EPI_STORE;
             e.out0 = h->grads + h->off_w[i];
@@ -409,7 +422,10 @@ void make_plan(const vb200_config &c, ArenaPlan &pl, PlanIdx &ix, std::vector<in
     ix.sc = pl.add("scalars+status", 1024, 0, end, true);
     ix.mse = pl.add("mse_scratch", loss_blocks((long long)B * L[n]) * 4, 0, end, true);
     long long cs = 0;
-    for (int i = 0; i < n; ++i) cs = std::max(cs, colsum_chunks(B, L[i + 1]) * (long long)L[i + 1]);
+    for (int i = 0; i < n; ++i) {
+        cs = std::max(cs, colsum_chunks(B, L[i + 1]) * (long long)L[i + 1]);
+        if (L[i + 1] == 1) cs = std::max(cs, colsum_chunks(B, L[i]) * (long long)L[i]);  // weighted sums for dW
+    }
     ix.cs = pl.add("colsum_scratch", cs * 4, 0, end, true);
     for (int s = 0; s < 2; ++s) {
         ix.x[s] = pl.add(s ? "x_slot1" : "x_slot0", (int64_t)B * L[0] * 4, 0, end, true);
