@@ -29,6 +29,10 @@ def _lib(real: str):
         lib.oracle_set_global_batch.argtypes = [C.c_void_p, C.c_longlong]
         lib.oracle_grad_step.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]
         lib.oracle_update.argtypes = [C.c_void_p, C.c_float]
+        lib.oracle_get_state.argtypes = [C.c_void_p] + [C.POINTER(rp)] * 4
+        lib.oracle_get_adam_step.restype = C.c_uint64
+        lib.oracle_get_adam_step.argtypes = [C.c_void_p]
+        lib.oracle_set_adam_step.argtypes = [C.c_void_p, C.c_uint64]
         lib.oracle_set_gemm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         lib.oracle_set_params.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float)]
         lib.oracle_get_params.argtypes = [C.c_void_p, C.POINTER(rp), C.POINTER(rp)]
@@ -147,6 +151,19 @@ class Oracle:
         ws = [np.ctypeslib.as_array(wo[i], shape=(self.layers[i], self.layers[i + 1])) for i in range(self.n)]
         bs = [np.ctypeslib.as_array(bo[i], shape=(self.layers[i + 1],)) for i in range(self.n)]
         return ws, bs
+
+    def state(self):
+        """Copies of the optimizer state: (s1w, s1b, s2w, s2b) lists (None where unused) and the Adam step count."""
+        arrs = [(self._rp * self.n)() for _ in range(4)]
+        self.lib.oracle_get_state(self.h, *arrs)
+        out = []
+        for k, a in enumerate(arrs):
+            lst = []
+            for i in range(self.n):
+                shape = (self.layers[i], self.layers[i + 1]) if k % 2 == 0 else (self.layers[i + 1],)
+                lst.append(np.ctypeslib.as_array(a[i], shape=shape).copy() if a[i] else None)
+            out.append(lst)
+        return out[0], out[1], out[2], out[3], int(self.lib.oracle_get_adam_step(self.h))
 
     def loss(self) -> float:
         return float(self.lib.oracle_loss(self.h))

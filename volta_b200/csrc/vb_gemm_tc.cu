@@ -151,13 +151,14 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) 
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// x = hi + lo (+ an error below 2^-22 |x|): hi is x rounded to tf32 (10 explicit mantissa bits),
-// lo the rounded remainder.  Integer rounding on the bit pattern (add half an ulp, clear the low
-// 13 bits); the tensor core ignores those bits anyway.
+// x = hi + lo exactly: hi is x rounded to nearest tf32 (10 explicit mantissa bits; integer
+// rounding on the bit pattern: add half an ulp, clear the low 13 bits), lo = x - hi is exact in
+// fp32 and at most 2^-11 |x|.  The tensor core reads only the top 19 bits of each operand, so
+// lo is used truncated to tf32: an error below 2^-21 |x| whose sign follows lo's, i.e. random
+// with respect to x.  Three instructions per element.
 __device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
     hi = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
-    float l = x - hi;
-    lo = __uint_as_float((__float_as_uint(l) + 0x1000u) & 0xFFFFE000u);
+    lo = x - hi;
 }
 
 // Byte offset of element (row, 4*k4 .. 4*k4+3) inside a K-major 128-byte-swizzled tile.

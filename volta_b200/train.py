@@ -148,6 +148,34 @@ class TrainHandle:
         buf = np.ascontiguousarray(buf, dtype=np.float32)
         self._check(self.lib.volta_b200_load_state(self.h, buf.ctypes.data_as(C.POINTER(C.c_float)), buf.size, int(step)))
 
+    def state_offsets(self):
+        """Float offsets of every W_i and b_i inside one flat state/parameter region: all
+        weights first, then all biases, each tensor padded to a multiple of 64 floats."""
+        pad = lambda v: (v + 63) // 64 * 64
+        off, ow, ob = 0, [], []
+        for r, c in zip(self.layers[:-1], self.layers[1:]):
+            ow.append(off)
+            off += pad(r * c)
+        for c in self.layers[1:]:
+            ob.append(off)
+            off += pad(c)
+        return ow, ob, off
+
+    def load_state_tensors(self, s1w, s1b, s2w, s2b, step: int):
+        """Import per-layer optimizer state (lists of arrays; None where unused) and the step count."""
+        ow, ob, total = self.state_offsets()
+        n = int(self.lib.volta_b200_state_floats(self.h))
+        buf = np.zeros(max(n, 1), dtype=np.float32)
+        for base, (ws, bs) in ((0, (s1w, s1b)), (total, (s2w, s2b))):
+            if base >= n:
+                break
+            for i in range(self.n):
+                if ws[i] is not None:
+                    buf[base + ow[i]: base + ow[i] + ws[i].size] = np.asarray(ws[i], np.float32).ravel()
+                if bs[i] is not None:
+                    buf[base + ob[i]: base + ob[i] + bs[i].size] = np.asarray(bs[i], np.float32).ravel()
+        self.load_state(buf[:n], step)
+
     def synchronize(self):
         self._check(self.lib.volta_b200_synchronize(self.h))
 
