@@ -18,6 +18,10 @@ pytestmark = pytest.mark.gpu
 GOLD = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "mlp_parity.json")))
 W_TOL = 1e-5
 LOSS_TOL = 1e-3
+# Gradient error allowed relative to the gradient's scale (see gradient_scales).  The FFMA path
+# is held to the weight tolerance; the tensor path gets 1e-4 because the tensor core adds into
+# its accumulator with truncation, a bias of about K/24 * 2^-24 per GEMM (4e-5 at K = 16384).
+G_TOL = {"ffma": 1e-5, "auto": 1e-4}
 
 
 def rel_err(a, b):
@@ -182,34 +186,50 @@ def update_fn(opt, lr, s1, s2, t):
     return lambda g: lr * g
 
 
-def weight_tolerance(opt, lr, w_ref, g_ref, s1, s2, t):
+def gradient_scales(o):
+    """Per gradient tensor, the magnitude its rounding error is measured against: the largest
+    entry of |act_i|^T.|delta_i| (for dW_i) or of sum_rows |delta_i| (for db_i), from the
+    oracle's own activations and deltas.  Without cancellation this equals max|g|; where a
+    gradient is a small difference of large terms (the output bias close to convergence is
+    sum_b 2(out_b - y_b)/nt, nearly zero) only an error relative to the terms is meaningful."""
+    sw, sb = [], []
+    for i in range(o.n):
+        a, d = np.abs(o.get_act(i).astype(np.float64)), np.abs(o.get_delta(i).astype(np.float64))
+        sw.append(float(np.max(a.T @ d)))
+        sb.append(float(np.max(d.sum(axis=0))))
+    return sw + sb
+
+
+def weight_tolerance(opt, lr, w_ref, g_ref, g_scale, s1, s2, t, g_tol=W_TOL):
     """Allowed |w_gpu - w_oracle| per element after ONE step from identical state: 1e-5 of
-    the tensor's largest weight, plus what a gradient error of 1e-5 of the tensor's largest
-    gradient does to the update.  For SGD-type updates the second term is negligible.  Adam
-    and Adagrad divide by a running magnitude of the gradient itself, so where that magnitude
-    is at the fp32 noise floor of the gradient GEMM the update is sign-like and swings by up
-    to 2*lr between two correct summation orders - the fp32 oracle differs from its own fp64
-    shadow in exactly those elements (test_adam_first_step_is_ill_conditioned_in_the_oracle_too)."""
+    the tensor's largest weight, plus what a gradient error of 1e-5 of the gradient's scale
+    does to the update.  For SGD-type updates the second term is negligible.  Adam and Adagrad
+    divide by a running magnitude of the gradient itself, so where that magnitude is at the
+    fp32 noise floor of the gradient GEMM the update is sign-like and swings by up to 2*lr
+    between two correct summation orders - the fp32 oracle differs from its own fp64 shadow
+    in exactly those elements (test_adam_first_step_is_ill_conditioned_in_the_oracle_too)."""
     tol = np.full(w_ref.shape, W_TOL * float(np.max(np.abs(w_ref))), np.float64)
     g = g_ref.astype(np.float64)
-    d = W_TOL * float(np.max(np.abs(g)))
+    d = g_tol * g_scale
     z = np.zeros_like(g)
     u = update_fn(opt, lr, s1 if s1 is not None else z, s2 if s2 is not None else z, t)
     tol += np.maximum(np.abs(u(g + d) - u(g)), np.abs(u(g - d) - u(g)))
     return tol
 
 
-def assert_one_step_parity(g, o, opt, lr, state_before):
-    """Gradients within 1e-5 (relative to the tensor maximum); weights within weight_tolerance;
-    at most a vanishing share of the weights may need more than the plain 1e-5."""
+def assert_one_step_parity(g, o, opt, lr, state_before, g_tol=G_TOL["auto"]):
+    """Gradients within 1e-5 of their scale; weights within weight_tolerance; at most a
+    vanishing share of the weights may need more than the plain 1e-5."""
     s1w, s1b, s2w, s2b, t_prev = state_before
     gdw, gdb = g.get_grads()
     odw, odb = o.get_grads()
-    for a, b in zip(gdw + gdb, odw + odb):
-        assert rel_err(a, b) <= W_TOL, "gradients"
+    scales = gradient_scales(o)
+    for a, b, sc in zip(gdw + gdb, odw + odb, scales):
+        assert float(np.max(np.abs(a.astype(np.float64) - b))) <= g_tol * sc, "gradients"
     beyond = 0
-    for a, b, gr, s1, s2 in zip(sum(g.get_params(), []), sum(o.get_params(), []), odw + odb, s1w + s1b, s2w + s2b):
-        tol = weight_tolerance(opt, lr, b, gr, s1, s2, t_prev + 1)
+    for a, b, gr, sc, s1, s2 in zip(sum(g.get_params(), []), sum(o.get_params(), []), odw + odb, scales, s1w + s1b,
+                                    s2w + s2b):
+        tol = weight_tolerance(opt, lr, b, gr, sc, s1, s2, t_prev + 1, g_tol)
         diff = np.abs(a.astype(np.float64) - b)
         assert np.all(diff <= tol), "weights after one step"
         beyond += int(np.sum(diff > W_TOL * float(np.max(np.abs(b)))))
@@ -246,8 +266,12 @@ def _config_run(cfg, B, steps, gemm_path="auto", checkpoints=(0,)):
         o64.step(x, y, cfg.lr)
         if step in checkpoints:
             forced.step(x, y, cfg.lr)
-            assert abs(forced.loss() - o.loss()) <= 1e-5 * abs(o.loss()), "loss from identical weights"
-            assert_one_step_parity(forced, o, cfg.optimizer, cfg.lr, before)
+            # loss = mean((out - y)^2): an output error e moves it by about 2*rms(out - y)*e, and e
+            # is relative to the outputs, not to the (possibly tiny) residuals
+            out_max = float(np.max(np.abs(o.get_act(o.n))))
+            tol = G_TOL[gemm_path] * (abs(o.loss()) + 2.0 * abs(o.loss()) ** 0.5 * out_max)
+            assert abs(forced.loss() - o.loss()) <= tol, "loss from identical weights"
+            assert_one_step_parity(forced, o, cfg.optimizer, cfg.lr, before, G_TOL[gemm_path])
     lg, lo, l64 = g.loss(), o.loss(), o64.loss()
     # Free run: within 1e-3 of the fp32 oracle where the trajectory is well conditioned; where
     # fp32 itself cannot do that (Adam-type runs: the fp32 oracle drifts from its fp64 shadow by

@@ -156,9 +156,11 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) 
 // fp32 and at most 2^-11 |x|.  The tensor core reads only the top 19 bits of each operand, so
 // lo is used truncated to tf32: an error below 2^-21 |x| whose sign follows lo's, i.e. random
 // with respect to x.  Three instructions per element.
+template <bool LO_RN>
 __device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
     hi = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
     lo = x - hi;
+    if (LO_RN) lo = __uint_as_float((__float_as_uint(lo) + 0x1000u) & 0xFFFFE000u);
 }
 
 // Byte offset of element (row, 4*k4 .. 4*k4+3) inside a K-major 128-byte-swizzled tile.
@@ -166,7 +168,7 @@ __device__ __forceinline__ uint32_t swz_offset(int row, int k4) {
     return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((k4 ^ (row & 7)) << 4));
 }
 
-template <bool KMAJOR>
+template <bool KMAJOR, bool LO_RN>
 __device__ __forceinline__ void split_tile(const uint8_t *raw, uint8_t *hi_t, uint8_t *lo_t, int tid) {
 #pragma unroll
     for (int it = 0; it < 128 * BK / 4 / SPLIT_THREADS; ++it) {
@@ -185,16 +187,16 @@ __device__ __forceinline__ void split_tile(const uint8_t *raw, uint8_t *hi_t, ui
             off = swz_offset(mn, k4);
         }
         float4 h, l;
-        split_tf32(v.x, h.x, l.x);
-        split_tf32(v.y, h.y, l.y);
-        split_tf32(v.z, h.z, l.z);
-        split_tf32(v.w, h.w, l.w);
+        split_tf32<LO_RN>(v.x, h.x, l.x);
+        split_tf32<LO_RN>(v.y, h.y, l.y);
+        split_tf32<LO_RN>(v.z, h.z, l.z);
+        split_tf32<LO_RN>(v.w, h.w, l.w);
         *reinterpret_cast<float4 *>(hi_t + off) = h;
         *reinterpret_cast<float4 *>(lo_t + off) = l;
     }
 }
 
-template <bool A_KMAJOR, bool B_KMAJOR>
+template <bool A_KMAJOR, bool B_KMAJOR, bool LO_RN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, long long M,
                long long N, long long K, int tiles_m, int tiles_n, Epilogue epi, unsigned int *status) {
@@ -308,8 +310,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!mbar_wait(smem_u32(&mma_empty[s]), phs ^ 1u, abort_flag, status, ST_MMA_EMPTY)) { ok = false; break; }
             const uint8_t *raw = raw_base + r * RAW_STAGE_BYTES;
             uint8_t *st = mma_base + s * MMA_STAGE_BYTES;
-            split_tile<A_KMAJOR>(raw, st, st + TILE_BYTES, tid);
-            split_tile<B_KMAJOR>(raw + TILE_BYTES, st + 2 * TILE_BYTES, st + 3 * TILE_BYTES, tid);
+            split_tile<A_KMAJOR, LO_RN>(raw, st, st + TILE_BYTES, tid);
+            split_tile<B_KMAJOR, LO_RN>(raw + TILE_BYTES, st + 2 * TILE_BYTES, st + 3 * TILE_BYTES, tid);
             fence_async_smem();  // generic-proxy writes must be visible to the tensor core's reads
             __syncwarp();
             if (lane == 0) {
@@ -404,17 +406,34 @@ bool make_map(CUtensorMap *map, const float *base, long long inner, long long ou
     return r == CUDA_SUCCESS;
 }
 
-template <bool AK, bool BKM>
-cudaError_t launch_variant(const CUtensorMap &ma, const CUtensorMap &mb, long long m, long long n, long long k,
-                           int tiles_m, int tiles_n, const Epilogue &epi, unsigned int *status, cudaStream_t s) {
+int env_int(const char *name, int dflt) {
+    const char *e = getenv(name);
+    return e ? atoi(e) : dflt;
+}
+
+template <bool AK, bool BKM, bool LO_RN>
+cudaError_t launch_one(const CUtensorMap &ma, const CUtensorMap &mb, long long m, long long n, long long k,
+                       int tiles_m, int tiles_n, const Epilogue &epi, unsigned int *status, cudaStream_t s) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<AK, BKM>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<AK, BKM, LO_RN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             SMEM_BYTES);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    gemm_tc_kernel<AK, BKM><<<tiles_m * tiles_n, THREADS, SMEM_BYTES, s>>>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status);
+    gemm_tc_kernel<AK, BKM, LO_RN><<<tiles_m * tiles_n, THREADS, SMEM_BYTES, s>>>(ma, mb, m, n, k, tiles_m, tiles_n, epi,
+                                                                                 status);
     return cudaGetLastError();
+}
+
+template <bool AK, bool BKM>
+cudaError_t launch_variant(const CUtensorMap &ma, const CUtensorMap &mb, long long m, long long n, long long k,
+                           int tiles_m, int tiles_n, const Epilogue &epi, unsigned int *status, cudaStream_t s) {
+    // VOLTA_B200_TC_LO_RN=1 also rounds the low part to tf32 explicitly (two more instructions
+    // per element) instead of leaving its truncation to the tensor core.
+    static const bool lo_rn = env_int("VOLTA_B200_TC_LO_RN", 0) != 0;
+    if (lo_rn) return launch_one<AK, BKM, true>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s);
+    return launch_one<AK, BKM, false>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s);
 }
 
 long long min_flops_for_tc() {
