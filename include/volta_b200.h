@@ -65,7 +65,8 @@ typedef struct vb200_config {
     float weight_decay;                /* AdamW; 0 = 0.01 */
     int32_t gemm_path;                 /* VB200_GEMM_* */
     int32_t use_graph;                 /* 0 = default (captured CUDA graph), 1 = graph, 2 = plain launches */
-    int32_t reserved[8];
+    int32_t reserved[8];               /* reserved[0] = 1: build the data-parallel path (communicator, bucketed
+                                          all-reduce) even for world_size 1, so it can be exercised on one GPU */
 } vb200_config;
 
 typedef struct vb200_handle vb200_handle;

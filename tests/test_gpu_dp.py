@@ -23,6 +23,29 @@ def _free_port():
     return p
 
 
+def test_data_parallel_path_on_a_single_rank_matches_the_plain_path():
+    """The whole data-parallel machinery (NCCL communicator, per-layer buckets reduced on a
+    side stream inside the captured graph, loss travelling in the bias bucket) with one rank:
+    a sum over one rank changes nothing, so results must equal the plain handle bit for bit."""
+    from volta_b200 import TrainHandle
+    from volta_b200.train import dp_unique_id
+    x, y, ws, bs = dpc.inputs()
+    outs = []
+    for dp in (False, True):
+        h = TrainHandle(dpc.LAYERS, "silu", "adam", dpc.GLOBAL_BATCH, force_dp=dp, unique_id=dp_unique_id() if dp else None)
+        for i, (w, b) in enumerate(zip(ws, bs)):
+            h.set_params(i, w, b)
+        losses = []
+        for _ in range(dpc.STEPS):
+            h.step(x, y, 0.01)
+            losses.append(np.float32(h.loss()))
+        outs.append((losses, sum(h.get_params(), [])))
+        h.free()
+    assert outs[0][0] == outs[1][0]
+    for a, b in zip(outs[0][1], outs[1][1]):
+        assert np.array_equal(a, b)
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("opt", ["sgd_momentum", "adam"])
 def test_two_gpu_ranks_match_the_full_batch_oracle(opt):

@@ -519,13 +519,18 @@ int build(vb200_handle *h) {
     VB_CUDA(h, cudaMemcpyAsync(h->params, h->mirror_params, (size_t)P * 4, cudaMemcpyHostToDevice, h->stream));
     VB_CUDA(h, cudaStreamSynchronize(h->stream));
 
-    if (h->world > 1) {
+    if (h->world > 1 || c.reserved[0] == 1) {
         VB_CUDA(h, cudaStreamCreateWithFlags(&h->comm_stream, cudaStreamNonBlocking));
         VB_CUDA(h, cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming));
         h->ev_bucket.resize(n + 1);
         for (auto &ev : h->ev_bucket) VB_CUDA(h, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
         h->dp = new DpComm();
         if (h->dp->init(c.nccl_unique_id, h->world, h->rank)) return h->fail(VB200_ERR_NCCL, h->dp->error());
+        // NCCL sets up its channels and peer connections on the first collective (allocations and
+        // a handshake between the ranks); that must not happen inside a stream capture.  Run one
+        // plain all-reduce first (on the loss slot, which is zero here and stays zero).
+        if (h->dp->all_reduce_sum(h->loss_sum, 64, h->comm_stream)) return h->fail(VB200_ERR_NCCL, h->dp->error());
+        VB_CUDA(h, cudaStreamSynchronize(h->comm_stream));
     }
     if (h->use_graph) {
         int rc = capture_graphs(h);

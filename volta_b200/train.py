@@ -51,7 +51,8 @@ class TrainHandle:
     """volta_train_init(batch) for a given topology; methods mirror the other five entry points."""
 
     def __init__(self, layers, activation="relu", optimizer="sgd", batch=1, *, global_batch=0, world_size=1, rank=0,
-                 unique_id: bytes | None = None, momentum=0.0, weight_decay=0.0, gemm_path="auto", use_graph=True):
+                 unique_id: bytes | None = None, momentum=0.0, weight_decay=0.0, gemm_path="auto", use_graph=True,
+                 force_dp=False):
         act = activation.lower()
         opt = optimizer.lower()
         if act not in ACTIVATIONS:
@@ -74,7 +75,8 @@ class TrainHandle:
         cfg.global_batch = int(global_batch)
         cfg.world_size = int(world_size)
         cfg.rank = int(rank)
-        if world_size > 1:
+        if world_size > 1 or force_dp:
+            cfg.reserved[0] = 1 if force_dp else 0
             if unique_id is None or len(unique_id) != 128:
                 raise VoltaB200Error(1, "world_size > 1 needs the 128-byte unique id")
             for i, b in enumerate(unique_id):
