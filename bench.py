@@ -43,6 +43,27 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per batch row of one launch, from
+# the ncu capture summarised in profiles/gemm_tc_c4_batch8192.md (taken at batch 8192; traffic of
+# these GEMMs grows in proportion to the batch, so a full launch is rows x this figure).
+NCU_TRAFFIC_PER_ROW = {
+    "fwd_gemm_nn_Bx4096x4096": (742.602496e6 + 247.932672e6) / 8192,
+    "fwd_gemm_nn_Bx1024x4096": (203.244288e6 + 44.418816e6) / 8192,
+    "dW_gemm_tn_4096x1024xB": (233.943040e6 + 14.075648e6) / 8192,
+}
+
+
+def ncu_traffic_bytes(kernel_name: str, rows: int):
+    import re
+    m = re.match(r"(fwd|dW|dX)\d+_gemm_(nn|nt|tn)_(\d+)x(\d+)x(\d+)", kernel_name)
+    if not m:
+        return None
+    fam, lay, a, b, c = m.group(1), m.group(2), int(m.group(3)), int(m.group(4)), int(m.group(5))
+    key = "%s_gemm_%s_Bx%dx%d" % (fam, lay, b, c) if fam != "dW" else "%s_gemm_%s_%dx%dxB" % (fam, lay, a, b)
+    per_row = NCU_TRAFFIC_PER_ROW.get(key)
+    return per_row * rows if per_row else None
+
+
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons of one GPU every 200 ms while running."""
 
@@ -315,7 +336,7 @@ def main():
             peak = peaks["bf16_tflops_sustained"] / 6.0
             ach = tv[1] / tv[0] / 1e9
             roofline = {"kernel": top, "bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
-                        "frac": ach / peak, "traffic": None,
+                        "frac": ach / peak, "traffic": ncu_traffic_bytes(top, B),
                         "peak_basis": "%s bf16 sustained %.1f TFLOP/s / 6 (TF32 runs at half the bf16 rate and a "
                                       "3xTF32 product issues three MMAs); achieved counts logical fp32 flops" % (
                                           peaks["source"], peaks["bf16_tflops_sustained"])}
@@ -358,4 +379,18 @@ def main():
 
 
 if __name__ == "__main__":
+    # Libraries loaded along the way (NCCL prints its version banner) write to stdout; the
+    # contract is ONE JSON line there.  Point fd 1 at stderr while running and print the line
+    # to the real stdout.
+    sys.stdout.flush()
+    _real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    _out = os.fdopen(_real_stdout, "w")
+    _print = print
+
+    def print(*a, **k):  # noqa: A001  (only the JSON line goes through here)
+        k.setdefault("file", _out)
+        _print(*a, **k)
+        _out.flush()
+
     main()

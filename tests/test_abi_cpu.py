@@ -103,3 +103,32 @@ def test_create_fails_loudly_without_a_gpu():
     with pytest.raises(VoltaB200Error) as e:
         TrainHandle([4, 4, 1], "relu", "sgd", 2)
     assert "no CPU fallback" in str(e.value)
+
+
+def _train_symbols():
+    text = open(os.path.join(ROOT, "include", "volta_train.h")).read()
+    return sorted(set(re.findall(r"\b(volta_train_[a-z_]+)\s*\(", text)))
+
+
+def test_codegen_emits_a_library_with_the_reference_symbols(tmp_path):
+    from volta_b200 import codegen
+    out = codegen.compile_model([512, 1024, 1024, 512, 256, 1], "relu", "adam", str(tmp_path / "m.train_cuda.so"))
+    lib = C.CDLL(out)
+    syms = _train_symbols()
+    assert syms == ["volta_train_free", "volta_train_get_params", "volta_train_init", "volta_train_loss",
+                    "volta_train_set_params", "volta_train_step"]
+    for s in syms:
+        assert hasattr(lib, s)
+    src = open(out + ".shim.c").read()
+    assert "512, 1024, 1024, 512, 256, 1" in src
+
+
+def test_codegen_rejects_what_the_reference_rejects(tmp_path):
+    # tests/cli_smoke.rs:207-379: compile-train refuses RMSprop on the Rust path and non-MLP input
+    from volta_b200 import codegen
+    with pytest.raises(codegen.CodegenError, match="does not support optimizer"):
+        codegen.compile_model([4, 4, 1], "relu", "rmsprop", str(tmp_path / "a.so"))
+    with pytest.raises(codegen.CodegenError, match="need >= 2 layer sizes"):
+        codegen.compile_model([4], "relu", "sgd", str(tmp_path / "b.so"))
+    with pytest.raises(codegen.CodegenError, match="does not support activation"):
+        codegen.compile_model([4, 4, 1], "softmax", "sgd", str(tmp_path / "c.so"))

@@ -418,3 +418,34 @@ def test_errors_are_reported_not_raised_as_faults():
         g.set_params(0, np.zeros(3, np.float32), np.zeros(4, np.float32))
     g.free()
     g.free()  # double free is a no-op
+
+
+def test_generated_per_model_library_runs_the_reference_abi(tmp_path):
+    """volta_train_init/_set_params/_step/_loss/_get_params/_free of an emitted library, called
+    the way a host harness calls a Volta training DLL, against the oracle."""
+    from volta_b200 import codegen
+    layers, B = [48, 64, 1], 16
+    lib = C.CDLL(codegen.compile_model(layers, "relu", "sgd", str(tmp_path / "m.train_cuda.so")))
+    fp = C.POINTER(C.c_float)
+    lib.volta_train_init.restype = C.c_void_p
+    lib.volta_train_init.argtypes = [C.c_int32]
+    lib.volta_train_step.argtypes = [C.c_void_p, fp, fp, C.c_float]
+    lib.volta_train_loss.restype = C.c_float
+    lib.volta_train_loss.argtypes = [C.c_void_p]
+    lib.volta_train_get_params.argtypes = [C.c_void_p, C.POINTER(fp), C.POINTER(fp)]
+    lib.volta_train_free.argtypes = [C.c_void_p]
+    h = lib.volta_train_init(B)
+    assert h
+    o = Oracle(layers, "relu", "sgd", B)   # both start from the LCG-Xavier default
+    x = synth.rows("normal", 5, 0, B, layers[0])
+    y = synth.rows("normal", 6, 0, B, 1)
+    for _ in range(3):
+        lib.volta_train_step(h, x.ctypes.data_as(fp), y.ctypes.data_as(fp), 0.05)
+        o.step(x, y, 0.05)
+        assert abs(lib.volta_train_loss(h) - o.loss()) <= 1e-5 * abs(o.loss())
+    wo, bo = (fp * 2)(), (fp * 2)()
+    lib.volta_train_get_params(h, wo, bo)
+    w0 = np.ctypeslib.as_array(wo[0], shape=(48, 64))
+    assert rel_err(w0, o.get_params()[0][0]) <= W_TOL
+    lib.volta_train_free(h)
+    lib.volta_train_free(None)

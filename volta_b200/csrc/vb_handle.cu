@@ -353,12 +353,18 @@ void destroy(vb200_handle *h) {
     if (h->stream) cudaStreamSynchronize(h->stream);
     if (h->copy_stream) cudaStreamSynchronize(h->copy_stream);
     if (h->comm_stream) cudaStreamSynchronize(h->comm_stream);
+    // The captured graphs hold references on the communicator (NCCL waits for them in its
+    // destroy call), so they must go first.
+    for (int s = 0; s < 2; ++s)
+        if (h->graph[s]) {
+            cudaGraphExecDestroy(h->graph[s]);
+            h->graph[s] = nullptr;
+        }
     if (h->dp) {
         delete h->dp;
         h->dp = nullptr;
     }
     for (int s = 0; s < 2; ++s) {
-        if (h->graph[s]) cudaGraphExecDestroy(h->graph[s]);
         if (h->ev_copied[s]) cudaEventDestroy(h->ev_copied[s]);
         if (h->ev_slot_free[s]) cudaEventDestroy(h->ev_slot_free[s]);
     }
