@@ -44,7 +44,7 @@ enum { VB200_GEMM_AUTO = 0, VB200_GEMM_FFMA = 1, VB200_GEMM_TENSOR = 2 };
  * (void functions, mlp_train_rust_codegen.rs:670-699); the replacement never traps and
  * reports through these codes and volta_b200_last_error(). */
 enum { VB200_OK = 0, VB200_ERR_INVALID = 1, VB200_ERR_CUDA = 2, VB200_ERR_OOM = 3, VB200_ERR_NCCL = 4,
-       VB200_ERR_DEVICE_WAIT = 5, VB200_ERR_UNSUPPORTED = 6 };
+       VB200_ERR_DEVICE_WAIT = 5, VB200_ERR_UNSUPPORTED = 6, VB200_ERR_TOO_LARGE = 7 };
 
 /* Replaces MlpTopology (mlp_train_rust_codegen.rs:28-39) plus the `batch` argument of
  * volta_train_init.  Hyper-parameters other than lr are fixed in the reference's
@@ -158,6 +158,21 @@ int volta_b200_gemm(int32_t layout, int32_t path, float *C, const float *A, cons
  * volta_b200_colsum_scratch_floats(rows, cols) floats. */
 int64_t volta_b200_colsum_scratch_floats(int64_t rows, int64_t cols);
 int volta_b200_colsum(float *out, const float *in, int64_t rows, int64_t cols, float *scratch, void *stream);
+
+/* Column sums with NO allocation anywhere (no counterpart in the reference, which allocates
+ * freely on the host): same result as volta_b200_colsum, bit for bit, but the scratch partials
+ * live in a 4 MiB buffer built into the library image (1 Mi floats per GPU that loads the library,
+ * held until process exit).  For callers that may not touch the CUDA allocator where they need a
+ * bias gradient: latency-critical host threads that cannot take cudaMalloc's implicit
+ * synchronisation, processes that have given all device memory to a pool of their own, plug-ins
+ * whose host forbids allocation after start-up.  `out` [cols] and `in` [rows x cols] are the
+ * caller's device buffers.  Inputs needing more than 1 Mi scratch floats
+ * (volta_b200_colsum_scratch_floats says how many) are refused with VB200_ERR_TOO_LARGE and a
+ * message on stderr.  The first call on each device looks up the buffer's device address; make
+ * that call outside any stream capture.  All calls share the one buffer, which keeps whatever the
+ * last call left (nothing in it needs to start at zero): two calls whose kernels can overlap on
+ * the GPU - different streams without an ordering between them - race on it. */
+int volta_b200_colsum_noalloc(float *out, const float *in, int64_t rows, int64_t cols, void *stream);
 
 const char *volta_b200_version(void);
 

@@ -35,7 +35,7 @@ EXPORTS = [
     "volta_b200_load_state", "volta_b200_status", "volta_b200_last_error", "volta_b200_stream",
     "volta_b200_synchronize", "volta_b200_arena_bytes", "volta_b200_plan", "volta_b200_kernels_per_step",
     "volta_b200_profile_step", "volta_b200_dp_unique_id", "volta_b200_optimizer_apply", "volta_b200_gemm",
-    "volta_b200_colsum_scratch_floats", "volta_b200_colsum", "volta_b200_version",
+    "volta_b200_colsum_scratch_floats", "volta_b200_colsum", "volta_b200_colsum_noalloc", "volta_b200_version",
 ]
 
 _lib = None
@@ -82,6 +82,7 @@ def load_library():
         "volta_b200_gemm": (C.c_int, [i32, i32, vp, vp, vp, i64, i64, i64, vp]),
         "volta_b200_colsum_scratch_floats": (i64, [i64, i64]),
         "volta_b200_colsum": (C.c_int, [vp, vp, i64, i64, vp, vp]),
+        "volta_b200_colsum_noalloc": (C.c_int, [vp, vp, i64, i64, vp]),
         "volta_b200_version": (C.c_char_p, []),
     }
     for name, (res, args) in sig.items():
