@@ -145,6 +145,8 @@ cudaError_t launch_gemm_ffma(int layout, const float *A, const float *B, long lo
 // Returns cudaErrorNotSupported when the shape/alignment cannot take the tensor path.
 cudaError_t launch_gemm_tc(int layout, const float *A, const float *B, long long m, long long n, long long k,
                            const Epilogue &epi, unsigned int *status_word, cudaStream_t s);
+cudaError_t launch_gemm_tc2(int layout, const float *A, const float *B, long long m, long long n, long long k,
+                            const Epilogue &epi, unsigned int *status_word, cudaStream_t s);
 bool gemm_tc_supported(int layout, const float *A, const float *B, long long m, long long n, long long k,
                        const Epilogue &epi);
 

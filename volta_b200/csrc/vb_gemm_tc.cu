@@ -466,6 +466,8 @@ bool gemm_tc_supported(int layout, const float *A, const float *B, long long m, 
 cudaError_t launch_gemm_tc(int layout, const float *A, const float *B, long long m, long long n, long long k,
                            const Epilogue &epi, unsigned int *status, cudaStream_t s) {
     if (!gemm_tc_supported(layout, A, B, m, n, k, epi)) return cudaErrorNotSupported;
+    static const int version = env_int("VOLTA_B200_TC_VERSION", 2);
+    if (version == 2) return launch_gemm_tc2(layout, A, B, m, n, k, epi, status, s);
     const bool a_kmajor = (layout != GEMM_TN), b_kmajor = (layout == GEMM_NT);
     CUtensorMap ma, mb;
     bool ok = a_kmajor ? make_map(&ma, A, k, m, BK, BM, true) : make_map(&ma, A, m, k, BM, BK, false);
