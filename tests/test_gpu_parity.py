@@ -88,7 +88,8 @@ def test_colsum_matches_oracle_order_free_sum(rows, cols):
     assert torch.equal(first, out)
 
 
-GEMM_SHAPES = [(1, 1, 1), (64, 1, 256), (64, 512, 256), (33, 65, 17), (128, 128, 64), (200, 72, 300), (256, 256, 1024)]
+GEMM_SHAPES = [(1, 1, 1), (64, 1, 256), (64, 512, 256), (33, 65, 17), (128, 128, 64), (200, 72, 300), (256, 256, 1024),
+               (64, 512, 2048), (64, 1024, 1000), (70, 130, 333)]   # the last three take the split-K route
 
 
 @pytest.mark.parametrize("layout", [0, 1, 2])

@@ -140,8 +140,14 @@ struct StepScalars {
 // ---------------------------------------------------------------------------------------
 // Kernel launchers (defined in the .cu files of this directory).
 // ---------------------------------------------------------------------------------------
+// `scratch` (ffma_scratch_floats(m, n, k) floats, may be null) enables deterministic split-K for
+// shapes whose output gives too few tiles to occupy the GPU.
 cudaError_t launch_gemm_ffma(int layout, const float *A, const float *B, long long m, long long n, long long k,
-                             const Epilogue &epi, cudaStream_t s);
+                             const Epilogue &epi, cudaStream_t s, float *scratch = nullptr);
+int ffma_splits(long long m, long long n, long long k);
+long long ffma_scratch_floats(long long m, long long n, long long k);
+// Shape heuristic: true when the tensor-core kernel is expected to beat the FFMA path.
+bool gemm_prefers_tc(long long m, long long n, long long k);
 // Returns cudaErrorNotSupported when the shape/alignment cannot take the tensor path.
 cudaError_t launch_gemm_tc(int layout, const float *A, const float *B, long long m, long long n, long long k,
                            const Epilogue &epi, unsigned int *status_word, cudaStream_t s);

@@ -15,7 +15,8 @@ namespace vb {
 template <int BM, int BN, int BK, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_ffma_kernel(const float *__restrict__ A, const float *__restrict__ B, long long M, long long N, long long K,
-                 long long a_sm, long long a_sk, long long b_sk, long long b_sn, Epilogue epi) {
+                 long long a_sm, long long a_sk, long long b_sk, long long b_sn, Epilogue epi, long long k_len,
+                 float *__restrict__ partial) {
     constexpr int THREADS = (BM / TM) * (BN / TN);
     constexpr int PAD = 4;
     __shared__ __align__(16) float As[2][BK][BM + PAD];
@@ -31,6 +32,8 @@ gemm_ffma_kernel(const float *__restrict__ A, const float *__restrict__ B, long 
 #pragma unroll
         for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
 
+    const long long k_lo = (long long)blockIdx.z * k_len;
+    const long long k_hi = (k_lo + k_len < K) ? (k_lo + k_len) : K;
     constexpr int A_PER = BM * BK / THREADS, B_PER = BN * BK / THREADS;
     float ra[A_PER], rb[B_PER];
     const bool a_kmajor = (a_sk == 1), b_kmajor = (b_sk == 1);
@@ -42,7 +45,7 @@ gemm_ffma_kernel(const float *__restrict__ A, const float *__restrict__ B, long 
             int kk = a_kmajor ? (e % BK) : (e / BM);
             int mm = a_kmajor ? (e / BK) : (e % BM);
             long long gm = m0 + mm, gk = k0 + kk;
-            ra[j] = (gm < M && gk < K) ? __ldg(A + gm * a_sm + gk * a_sk) : 0.0f;
+            ra[j] = (gm < M && gk < k_hi) ? __ldg(A + gm * a_sm + gk * a_sk) : 0.0f;
         }
 #pragma unroll
         for (int j = 0; j < B_PER; ++j) {
@@ -50,7 +53,7 @@ gemm_ffma_kernel(const float *__restrict__ A, const float *__restrict__ B, long 
             int kk = b_kmajor ? (e % BK) : (e / BN);
             int nn = b_kmajor ? (e / BK) : (e % BN);
             long long gn = n0 + nn, gk = k0 + kk;
-            rb[j] = (gn < N && gk < K) ? __ldg(B + gk * b_sk + gn * b_sn) : 0.0f;
+            rb[j] = (gn < N && gk < k_hi) ? __ldg(B + gk * b_sk + gn * b_sn) : 0.0f;
         }
     };
     auto store_tiles = [&](int buf) {
@@ -70,13 +73,14 @@ gemm_ffma_kernel(const float *__restrict__ A, const float *__restrict__ B, long 
         }
     };
 
-    const long long ktiles = (K + BK - 1) / BK;
-    load_tiles(0);
+    // split-K: this CTA sums k in [k_lo, k_hi); with one split that is all of K
+    const long long ktiles = (k_hi - k_lo + BK - 1) / BK;
+    load_tiles(k_lo);
     store_tiles(0);
     __syncthreads();
     for (long long kt = 0; kt < ktiles; ++kt) {
         const int buf = (int)(kt & 1);
-        if (kt + 1 < ktiles) load_tiles((kt + 1) * BK);
+        if (kt + 1 < ktiles) load_tiles(k_lo + (kt + 1) * BK);
 #pragma unroll
         for (int kk = 0; kk < BK; ++kk) {
             float a[TM], b[TN];
@@ -101,6 +105,21 @@ gemm_ffma_kernel(const float *__restrict__ A, const float *__restrict__ B, long 
         }
     }
 
+    if (partial) {
+        // split-K: raw sums go to this split's slab; a second kernel adds the slabs in order
+        float *dst = partial + (long long)blockIdx.z * M * N;
+#pragma unroll
+        for (int i = 0; i < TM; ++i) {
+            long long gm = m0 + ty * TM + i;
+            if (gm >= M) continue;
+#pragma unroll
+            for (int j = 0; j < TN; ++j) {
+                long long gn = n0 + tx * TN + j;
+                if (gn < N) dst[gm * N + gn] = acc[i][j];
+            }
+        }
+        return;
+    }
     const bool vec_ok = ((epi.ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(epi.out0) & 15) == 0) &&
                         (!epi.out1 || (reinterpret_cast<uintptr_t>(epi.out1) & 15) == 0) &&
                         (!epi.saved || (reinterpret_cast<uintptr_t>(epi.saved) & 15) == 0) &&
@@ -123,8 +142,53 @@ gemm_ffma_kernel(const float *__restrict__ A, const float *__restrict__ B, long 
     }
 }
 
+// Adds the split-K slabs in split order and applies the epilogue.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ partial, long long M, long long N,
+                                                            int splits, Epilogue epi) {
+    const long long total = M * N;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        float v = partial[idx];
+        for (int z = 1; z < splits; ++z) v += partial[(long long)z * total + idx];
+        epi.apply(idx / N, idx % N, v);
+    }
+}
+
+// How many K splits the FFMA path uses for a shape: enough CTAs to occupy the GPU when the
+// output alone gives too few tiles (the batch-64 configurations), never fewer than 64 k per
+// split.  A function of the shape only, so results are reproducible.
+int ffma_splits(long long m, long long n, long long k) {
+    const long long tiles = ((m + 63) / 64) * ((n + 63) / 64);
+    if (tiles >= 96 || k < 128) return 1;
+    long long want = (2 * 148 + tiles - 1) / tiles;
+    long long max_by_k = k / 64;
+    long long s = want < max_by_k ? want : max_by_k;
+    if (s > 32) s = 32;
+    return (int)(s < 1 ? 1 : s);
+}
+
+// Rough launch-time estimates (seconds) of the two GEMM paths, from measurements on B200: the
+// tensor kernel pays ~8 us of fixed cost (tensor maps, TMEM, pipeline fill, epilogue) plus ~0.9 us
+// per 32-deep k-block per wave of 148 tiles; the FFMA path pays ~3 us plus its flops at ~20 TFLOP/s
+// scaled by how much of the GPU its CTAs cover.  Used only to route small shapes; a function of the
+// shape alone.
+bool gemm_prefers_tc(long long m, long long n, long long k) {
+    const double flops = 2.0 * (double)m * (double)n * (double)k;
+    const long long tiles128 = ((m + 127) / 128) * ((n + 127) / 128);
+    const double tc = 8e-6 + (double)((tiles128 + 147) / 148) * (double)((k + 31) / 32) * 0.9e-6;
+    const long long ctas = ((m + 63) / 64) * ((n + 63) / 64) * ffma_splits(m, n, k);
+    const double cover = ctas >= 148 ? 1.0 : (double)ctas / 148.0;
+    const double ffma = 3e-6 + flops / (20e12 * cover);
+    return tc < ffma;
+}
+
+long long ffma_scratch_floats(long long m, long long n, long long k) {
+    int s = ffma_splits(m, n, k);
+    return s > 1 ? (long long)s * m * n : 0;
+}
+
 cudaError_t launch_gemm_ffma(int layout, const float *A, const float *B, long long m, long long n, long long k,
-                             const Epilogue &epi, cudaStream_t s) {
+                             const Epilogue &epi, cudaStream_t s, float *scratch) {
     if (m <= 0 || n <= 0 || k <= 0) return cudaErrorInvalidValue;
     long long a_sm, a_sk, b_sk, b_sn;
     switch (layout) {
@@ -133,17 +197,29 @@ cudaError_t launch_gemm_ffma(int layout, const float *A, const float *B, long lo
     case GEMM_TN: a_sm = 1; a_sk = m; b_sk = n; b_sn = 1; break;
     default: return cudaErrorInvalidValue;
     }
-    // Small outputs get small tiles so that more SMs take part (the B = 64 configurations
-    // are latency-bound); the choice depends on the shape only.
+    const int splits = scratch ? ffma_splits(m, n, k) : 1;
+    if (splits > 1) {
+        const long long k_len = ((k + splits - 1) / splits + 15) / 16 * 16;
+        const int zs = (int)((k + k_len - 1) / k_len);
+        dim3 grid((unsigned)((n + 63) / 64), (unsigned)((m + 63) / 64), (unsigned)zs);
+        gemm_ffma_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, s>>>(A, B, m, n, k, a_sm, a_sk, b_sk, b_sn, epi, k_len, scratch);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        long long total = m * n;
+        int blocks = (int)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184);
+        splitk_reduce_kernel<<<blocks, 256, 0, s>>>(scratch, m, n, zs, epi);
+        return cudaGetLastError();
+    }
+    // Small outputs get small tiles so that more SMs take part; the choice depends on the shape only.
     long long tiles64 = ((m + 63) / 64) * ((n + 63) / 64);
     if (tiles64 >= 96 || (m >= 64 && n >= 64 && tiles64 >= 48)) {
         dim3 grid((unsigned)((n + 63) / 64), (unsigned)((m + 63) / 64));
         if (grid.y > 65535) return cudaErrorInvalidConfiguration;
-        gemm_ffma_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, s>>>(A, B, m, n, k, a_sm, a_sk, b_sk, b_sn, epi);
+        gemm_ffma_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, s>>>(A, B, m, n, k, a_sm, a_sk, b_sk, b_sn, epi, k, nullptr);
     } else {
         dim3 grid((unsigned)((n + 31) / 32), (unsigned)((m + 31) / 32));
         if (grid.y > 65535) return cudaErrorInvalidConfiguration;
-        gemm_ffma_kernel<32, 32, 16, 4, 4><<<grid, 64, 0, s>>>(A, B, m, n, k, a_sm, a_sk, b_sk, b_sn, epi);
+        gemm_ffma_kernel<32, 32, 16, 4, 4><<<grid, 64, 0, s>>>(A, B, m, n, k, a_sm, a_sk, b_sk, b_sn, epi, k, nullptr);
     }
     return cudaGetLastError();
 }

@@ -60,7 +60,7 @@ struct vb200_handle {
     float *loss_sum = nullptr;  // lives right behind the gradients so that it joins the bias bucket
     StepScalars *scalars = nullptr;
     unsigned int *status_word = nullptr;
-    float *mse_scratch = nullptr, *colsum_scratch = nullptr;
+    float *mse_scratch = nullptr, *colsum_scratch = nullptr, *gemm_scratch = nullptr;
     float *xin[2] = {nullptr, nullptr}, *yin[2] = {nullptr, nullptr};
     std::vector<float *> act, pre, delta;  // act[0] unused (slot dependent)
 
@@ -141,9 +141,11 @@ struct Scope {
 
 cudaError_t run_gemm(vb200_handle *h, int layout, const float *A, const float *Bm, long long m, long long n,
                      long long k, const Epilogue &epi) {
-    if (h->cfg.gemm_path != VB200_GEMM_FFMA && gemm_tc_supported(layout, A, Bm, m, n, k, epi))
+    const int path = h->cfg.gemm_path;
+    if (path != VB200_GEMM_FFMA && gemm_tc_supported(layout, A, Bm, m, n, k, epi) &&
+        (path == VB200_GEMM_TENSOR || gemm_prefers_tc(m, n, k)))
         return launch_gemm_tc(layout, A, Bm, m, n, k, epi, h->status_word, h->stream);
-    return launch_gemm_ffma(layout, A, Bm, m, n, k, epi, h->stream);
+    return launch_gemm_ffma(layout, A, Bm, m, n, k, epi, h->stream, h->gemm_scratch);
 }
 
 // Enqueue one whole step on h->stream reading inputs from `slot`.
@@ -397,7 +399,7 @@ int validate(const vb200_config *c, std::string *why) {
 }
 
 struct PlanIdx {
-    int params, grads, s1, s2, sc, mse, cs, x[2], y[2];
+    int params, grads, s1, s2, sc, mse, cs, gs, x[2], y[2];
     std::vector<int> act, pre, delta;
 };
 
@@ -433,6 +435,14 @@ void make_plan(const vb200_config &c, ArenaPlan &pl, PlanIdx &ix, std::vector<in
         if (L[i + 1] == 1) cs = std::max(cs, colsum_chunks(B, L[i]) * (long long)L[i]);  // weighted sums for dW
     }
     ix.cs = pl.add("colsum_scratch", cs * 4, 0, end, true);
+    long long gs = 0;  // split-K slabs of the FFMA path: the largest need over the step's GEMMs
+    for (int i = 0; i < n; ++i) {
+        const long long r = L[i], cc = L[i + 1];
+        gs = std::max(gs, ffma_scratch_floats(B, cc, r));            // forward
+        gs = std::max(gs, ffma_scratch_floats(r, cc, B));            // dW
+        if (i > 0) gs = std::max(gs, ffma_scratch_floats(B, r, cc)); // dX
+    }
+    ix.gs = pl.add("gemm_splitk_scratch", gs * 4, 0, end, true);
     for (int s = 0; s < 2; ++s) {
         ix.x[s] = pl.add(s ? "x_slot1" : "x_slot0", (int64_t)B * L[0] * 4, 0, end, true);
         ix.y[s] = pl.add(s ? "y_slot1" : "y_slot0", (int64_t)B * L[n] * 4, 0, end, true);
@@ -497,6 +507,7 @@ int build(vb200_handle *h) {
     h->status_word = reinterpret_cast<unsigned int *>(reinterpret_cast<char *>(at(i_sc)) + 512);
     h->mse_scratch = at(i_mse);
     h->colsum_scratch = at(i_cs);
+    h->gemm_scratch = at(ix.gs);
     for (int s = 0; s < 2; ++s) { h->xin[s] = at(i_x[s]); h->yin[s] = at(i_y[s]); }
     h->act.assign(n + 1, nullptr);
     h->pre.assign(n, nullptr);
@@ -812,7 +823,15 @@ int volta_b200_gemm(int32_t layout, int32_t path, float *C, const float *A, cons
         cudaFree(st);
         if (err == cudaSuccess && hs != 0) return VB200_ERR_DEVICE_WAIT;
     } else {
-        err = launch_gemm_ffma(layout, A, B, m, n, k, e, s);
+        // same split-K decision as inside a training step, with scratch of this call's own
+        float *scratch = nullptr;
+        const long long need = ffma_scratch_floats(m, n, k);
+        if (need > 0 && cudaMalloc(&scratch, (size_t)need * 4) != cudaSuccess) return VB200_ERR_OOM;
+        err = launch_gemm_ffma(layout, A, B, m, n, k, e, s, scratch);
+        if (scratch) {
+            if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+            cudaFree(scratch);
+        }
     }
     return err == cudaSuccess ? VB200_OK : VB200_ERR_CUDA;
 }
