@@ -182,7 +182,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="c4")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--gemm-path", default="auto", choices=["auto", "ffma", "tensor"])
+    ap.add_argument("--gemm-path", default="auto", choices=["auto", "ffma", "tensor", "tensor_pair"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=None,
                     help="override the workload's global batch (for small profiler captures; not a headline number)")

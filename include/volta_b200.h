@@ -37,8 +37,10 @@ enum { VB200_ACT_RELU = 0, VB200_ACT_SIGMOID = 1, VB200_ACT_TANH = 2, VB200_ACT_
 enum { VB200_OPT_SGD = 0, VB200_OPT_ADAM = 1, VB200_OPT_ADAMW = 2, VB200_OPT_ADAGRAD = 3,
        VB200_OPT_SGD_MOMENTUM = 4 };
 
-/* GEMM path selection. AUTO picks the tcgen05 kernel for shapes it supports. */
-enum { VB200_GEMM_AUTO = 0, VB200_GEMM_FFMA = 1, VB200_GEMM_TENSOR = 2 };
+/* GEMM path selection. AUTO routes each GEMM by shape (tcgen05 kernel for large ones, FFMA with
+ * split-K for small ones).  TENSOR_PAIR is the experimental CTA-pair (cta_group::2) tcgen05 kernel
+ * for outputs of at least 256 x 256; other shapes fall back to TENSOR. */
+enum { VB200_GEMM_AUTO = 0, VB200_GEMM_FFMA = 1, VB200_GEMM_TENSOR = 2, VB200_GEMM_TENSOR_PAIR = 3 };
 
 /* Error codes (0 = success). The reference reports no errors on this path
  * (void functions, mlp_train_rust_codegen.rs:670-699); the replacement never traps and

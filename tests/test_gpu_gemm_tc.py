@@ -10,7 +10,7 @@ from volta_b200 import load_library
 pytestmark = pytest.mark.gpu
 
 NN, NT, TN = 0, 1, 2
-FFMA, TENSOR = 1, 2
+FFMA, TENSOR, PAIR = 1, 2, 3
 
 
 def _run(layout, path, A, B):
@@ -80,3 +80,27 @@ def test_unsupported_shape_is_refused_not_faulted():
     B = np.ones((6, 6), np.float32)
     rc, _ = _run(NN, TENSOR, A, B)
     assert rc == 6  # VB200_ERR_UNSUPPORTED
+
+
+PAIR_SHAPES = [(256, 256, 32), (256, 512, 256), (512, 256, 4096), (1000, 520, 260), (384, 640, 96), (2048, 2048, 512)]
+
+
+@pytest.mark.parametrize("layout", [NT, NN, TN])
+@pytest.mark.parametrize("m,n,k", PAIR_SHAPES)
+def test_cta_pair_gemm_exact_on_integers_and_close_on_reals(layout, m, n, k):
+    """The cta_group::2 kernel (two CTAs per 256 x 256 tile) against fp64 and the single-CTA kernel."""
+    rs = np.random.RandomState(5 * m + n + k + layout)
+    A = rs.randint(-4, 5, size=(m, k)).astype(np.float32)
+    B = rs.randint(-4, 5, size=(k, n)).astype(np.float32)
+    rc, got = _run(layout, PAIR, A, B)
+    assert rc == 0
+    ref = (A.astype(np.float64) @ B.astype(np.float64)).astype(np.float32)
+    bad = np.argwhere(got != ref)
+    assert bad.size == 0, "first mismatches (row, col): %s of %d" % (bad[:8].tolist(), len(bad))
+    A = rs.randn(m, k).astype(np.float32)
+    B = rs.randn(k, n).astype(np.float32)
+    rc, got = _run(layout, PAIR, A, B)
+    assert rc == 0
+    ref = A.astype(np.float64) @ B.astype(np.float64)
+    bound = np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64)
+    assert float((np.abs(got - ref) / (bound + 1e-30)).max()) <= 2.0e-6

@@ -153,6 +153,9 @@ cudaError_t launch_gemm_tc(int layout, const float *A, const float *B, long long
                            const Epilogue &epi, unsigned int *status_word, cudaStream_t s);
 cudaError_t launch_gemm_tc2(int layout, const float *A, const float *B, long long m, long long n, long long k,
                             const Epilogue &epi, unsigned int *status_word, cudaStream_t s);
+cudaError_t launch_gemm_tc3(int layout, const float *A, const float *B, long long m, long long n, long long k,
+                            const Epilogue &epi, unsigned int *status_word, cudaStream_t s);
+void gemm_tc_select_pair(bool on);
 bool gemm_tc_supported(int layout, const float *A, const float *B, long long m, long long n, long long k,
                        const Epilogue &epi);
 

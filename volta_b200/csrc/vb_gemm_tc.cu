@@ -447,6 +447,10 @@ long long min_flops_for_tc() {
 
 }  // namespace
 
+// set by callers that explicitly select the CTA-pair kernel (VB200_GEMM_TENSOR_PAIR)
+thread_local bool g_force_pair = false;
+void gemm_tc_select_pair(bool on) { g_force_pair = on; }
+
 bool gemm_tc_supported(int layout, const float *A, const float *B, long long m, long long n, long long k,
                        const Epilogue &epi) {
     if (m <= 0 || n <= 0 || k <= 0) return false;
@@ -467,7 +471,8 @@ cudaError_t launch_gemm_tc(int layout, const float *A, const float *B, long long
                            const Epilogue &epi, unsigned int *status, cudaStream_t s) {
     if (!gemm_tc_supported(layout, A, B, m, n, k, epi)) return cudaErrorNotSupported;
     static const int version = env_int("VOLTA_B200_TC_VERSION", 2);
-    if (version == 2) return launch_gemm_tc2(layout, A, B, m, n, k, epi, status, s);
+    if ((version == 3 || g_force_pair) && m >= 256 && n >= 256) return launch_gemm_tc3(layout, A, B, m, n, k, epi, status, s);
+    if (version >= 2) return launch_gemm_tc2(layout, A, B, m, n, k, epi, status, s);
     const bool a_kmajor = (layout != GEMM_TN), b_kmajor = (layout == GEMM_NT);
     CUtensorMap ma, mb;
     bool ok = a_kmajor ? make_map(&ma, A, k, m, BK, BM, true) : make_map(&ma, A, m, k, BM, BK, false);

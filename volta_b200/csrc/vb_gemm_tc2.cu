@@ -7,7 +7,10 @@
 //    split warps compute just lo = tf32_rn(x - trunc_tf32(x)) and store it once, position by
 //    position, for every operand layout: operands whose contiguous dimension is M or N are loaded
 //    with the 128-byte/32-byte-atom swizzle and consumed through MN-major descriptors, so nothing is
-//    transposed in shared memory either.  One unified 3-stage ring [raw A | raw B | lo A | lo B].
+//    transposed in shared memory either.  Two rings: raw tiles (4 slots, alive from the TMA load
+//    until the MMAs that read them retire) and low parts (2 slots, alive from the split to the
+//    same MMAs); a per-CTA timeline showed the pipeline bound by the ~1.5 us load latency, so the
+//    bytes go where they buy loads in flight.
 //  * The tensor core adds into its accumulator with truncation, an error that grows with the
 //    number of additions.  The accumulators are therefore drained every 4 k-blocks: two
 //    accumulator sets (hi.hi and cross terms each) alternate in TMEM, and while the MMAs fill one
@@ -22,20 +25,26 @@
 #include "vb_common.cuh"
 
 namespace vb {
+#ifdef VB_TRACE
+__device__ unsigned long long *g_trace = nullptr;  // [role][kb] timestamps of CTA 0, experiments only
+#define TRACE(role, kb) do { if (blockIdx.x == 0 && g_trace && (kb) < 256) g_trace[(role) * 256 + (kb)] = global_ns_(); } while (0)
+__device__ __forceinline__ unsigned long long global_ns_() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#else
+#define TRACE(role, kb) do {} while (0)
+#endif
 namespace {
 
 constexpr int BM = 128, BN = 128, BK = 32;
-constexpr int STAGES = 3;
+constexpr int RAW_STAGES = 4, LO_STAGES = 2;   // raw tiles live from load to MMA, low parts only from split to MMA
 constexpr int SPLIT_WARPS = 8, SPLIT_THREADS = SPLIT_WARPS * 32;
 constexpr int TMA_WARP = SPLIT_WARPS, MMA_WARP = SPLIT_WARPS + 1;
 constexpr int THREADS = (SPLIT_WARPS + 2) * 32;
 constexpr int TILE_BYTES = 128 * BK * 4;        // 16 KiB
-constexpr int STAGE_BYTES = 4 * TILE_BYTES;     // raw A, raw B, lo A, lo B
-constexpr int SMEM_TILES = STAGES * STAGE_BYTES;
+constexpr int RING_BYTES = 2 * TILE_BYTES;      // one ring slot: an A tile and a B tile
+constexpr int SMEM_TILES = (RAW_STAGES + LO_STAGES) * RING_BYTES;
 constexpr int SMEM_BYTES = SMEM_TILES + 256 + 1024;
 constexpr int TMEM_COLS = 512;                  // 2 sets x (hi.hi + cross) x 128 columns
 constexpr int CHUNK = 4;                        // k-blocks per accumulator drain
-constexpr int DRAIN_LAG = 2;                    // drain chunk c-1 when about to split k-block c*CHUNK + LAG
 constexpr int GROUP_M = 8;
 
 constexpr unsigned ST_STAGE_FREE = 1u, ST_RAW_FULL = 2u, ST_LO_FULL = 8u, ST_ACC_FULL = 16u, ST_ACC_EMPTY = 32u;
@@ -153,15 +162,17 @@ __device__ __forceinline__ void split_tile(const uint8_t *raw, uint8_t *lo_t, in
 template <bool A_KMAJOR, bool B_KMAJOR>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, long long M,
-                long long N, long long K, int tiles_m, int tiles_n, Epilogue epi, unsigned int *status, int dbg, int nstages, int stage_bytes) {
+                long long N, long long K, int tiles_m, int tiles_n, Epilogue epi, unsigned int *status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + SMEM_TILES);
-    uint64_t *raw_full = bars, *lo_full = bars + 8, *stage_free = bars + 16, *acc_full = bars + 24, *acc_empty = bars + 26;
+    uint64_t *raw_full = bars, *lo_full = bars + 8, *mma_done = bars + 16, *acc_full = bars + 24, *acc_empty = bars + 26;
+    uint8_t *lo_ring = smem + RAW_STAGES * RING_BYTES;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 28);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) TRACE(5, 0);
     int tm, tn;
     {
         const int t = blockIdx.x;
@@ -180,7 +191,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int i = 0; i < 8; ++i) {
             mbar_init(smem_u32(&raw_full[i]), 1);
             mbar_init(smem_u32(&lo_full[i]), SPLIT_WARPS);
-            mbar_init(smem_u32(&stage_free[i]), 1);
+            mbar_init(smem_u32(&mma_done[i]), 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&acc_full[i]), 1);
@@ -199,17 +210,21 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (tid == 0) TRACE(5, 1);
 
     if (warp == TMA_WARP) {
         if (lane == 0) {
             int issued = 0;
             for (int kb = 0; kb < kblocks; ++kb) {
-                const int s = kb % nstages;
-                const uint32_t ph = (uint32_t)((kb / nstages) & 1);
-                if (!mbar_wait(smem_u32(&stage_free[s]), ph ^ 1u, abort_flag, status, ST_STAGE_FREE)) break;
+                const int s = kb % RAW_STAGES;
+                const uint32_t ph = (uint32_t)((kb / RAW_STAGES) & 1);
+                // slot s was last read by the MMAs of k-block kb - RAW_STAGES
+                if (!mbar_wait(smem_u32(&mma_done[s]), ph ^ 1u, abort_flag, status, ST_STAGE_FREE)) break;
+                TRACE(4, kb);  // slot seen free by the producer
+                TRACE(0, kb);  // TMA issue
                 const uint32_t full = smem_u32(&raw_full[s]);
                 mbar_expect_tx(full, 2 * TILE_BYTES);
-                const uint32_t dst = smem_u32(smem + s * stage_bytes);
+                const uint32_t dst = smem_u32(smem + s * RING_BYTES);
                 const int k0 = kb * BK;
                 if (A_KMAJOR) {
                     tma_load_2d(dst, &map_a, full, k0, (int)m0);
@@ -226,9 +241,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 issued = kb + 1;
             }
             if (*abort_flag) {
-                for (int kb = max(0, issued - nstages); kb < issued; ++kb) {
-                    const uint32_t bar = smem_u32(&raw_full[kb % nstages]);
-                    const uint32_t ph = (uint32_t)((kb / nstages) & 1);
+                for (int kb = max(0, issued - RAW_STAGES); kb < issued; ++kb) {
+                    const uint32_t bar = smem_u32(&raw_full[kb % RAW_STAGES]);
+                    const uint32_t ph = (uint32_t)((kb / RAW_STAGES) & 1);
                     for (int spin = 0; spin < (1 << 20) && !mbar_try(bar, ph); ++spin) {}
                 }
             }
@@ -240,7 +255,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             bool ok = true;
             for (int c = 0; c < nchunks && ok; ++c) {
                 const int set = c & 1;
-                if (!(dbg & 4) && !mbar_wait(smem_u32(&acc_empty[set]), (uint32_t)(((c >> 1) & 1) ^ 1), abort_flag, status, ST_ACC_EMPTY)) {
+                if (!mbar_wait(smem_u32(&acc_empty[set]), (uint32_t)(((c >> 1) & 1) ^ 1), abort_flag, status, ST_ACC_EMPTY)) {
                     ok = false;
                     break;
                 }
@@ -248,29 +263,28 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const uint32_t acc_main = tmem_base + (uint32_t)set * 256u, acc_cross = acc_main + 128u;
                 const int kb_end = min(kblocks, (c + 1) * CHUNK);
                 for (int kb = c * CHUNK; kb < kb_end; ++kb) {
-                    const int s = kb % nstages;
-                    if (!mbar_wait(smem_u32(&lo_full[s]), (uint32_t)((kb / nstages) & 1), abort_flag, status, ST_LO_FULL)) {
+                    const int s = kb % RAW_STAGES, l = kb % LO_STAGES;
+                    if (!mbar_wait(smem_u32(&lo_full[l]), (uint32_t)((kb / LO_STAGES) & 1), abort_flag, status, ST_LO_FULL)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t st = smem_u32(smem + s * stage_bytes);
+                    TRACE(3, kb);  // MMA start
+                    const uint32_t st = smem_u32(smem + s * RING_BYTES), sl = smem_u32(lo_ring + l * RING_BYTES);
 #pragma unroll
                     for (int j = 0; j < BK / 8; ++j) {
                         const uint32_t a_off = A_KMAJOR ? (uint32_t)j * 32u : (uint32_t)j * 1024u;
                         const uint32_t b_off = B_KMAJOR ? (uint32_t)j * 32u : (uint32_t)j * 1024u;
                         const uint64_t a_hi = A_KMAJOR ? desc_kmajor(st + a_off) : desc_mnmajor(st + a_off);
-                        const uint64_t a_lo = A_KMAJOR ? desc_kmajor(st + 2 * TILE_BYTES + a_off) : desc_mnmajor(st + 2 * TILE_BYTES + a_off);
+                        const uint64_t a_lo = A_KMAJOR ? desc_kmajor(sl + a_off) : desc_mnmajor(sl + a_off);
                         const uint64_t b_hi = B_KMAJOR ? desc_kmajor(st + TILE_BYTES + b_off) : desc_mnmajor(st + TILE_BYTES + b_off);
-                        const uint64_t b_lo = B_KMAJOR ? desc_kmajor(st + 3 * TILE_BYTES + b_off) : desc_mnmajor(st + 3 * TILE_BYTES + b_off);
+                        const uint64_t b_lo = B_KMAJOR ? desc_kmajor(sl + TILE_BYTES + b_off) : desc_mnmajor(sl + TILE_BYTES + b_off);
                         const uint32_t first = (kb == c * CHUNK && j == 0) ? 0u : 1u;
-                        if (!(dbg & 2)) {
-                            umma_tf32(acc_cross, a_lo, b_hi, idesc, first);
-                            umma_tf32(acc_cross, a_hi, b_lo, idesc, 1u);
-                        }
+                        umma_tf32(acc_cross, a_lo, b_hi, idesc, first);
+                        umma_tf32(acc_cross, a_hi, b_lo, idesc, 1u);
                         umma_tf32(acc_main, a_hi, b_hi, idesc, first);
                     }
-                    umma_commit(smem_u32(&stage_free[s]));
+                    umma_commit(smem_u32(&mma_done[s]));  // frees raw slot s and low-part slot l
                 }
                 umma_commit(smem_u32(&acc_full[set]));
             }
@@ -302,28 +316,43 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             return true;
         };
         for (int kb = 0; kb < kblocks; ++kb) {
-            if (kb >= CHUNK && (kb % CHUNK) == DRAIN_LAG && !(dbg & 4)) {
-                if (!drain(next_drain)) { ok = false; break; }
-                ++next_drain;
+            const int s = kb % RAW_STAGES, l = kb % LO_STAGES;
+            // the low-part slot was last read by the MMAs of k-block kb - LO_STAGES
+            if (kb >= LO_STAGES) {
+                const int j = kb - LO_STAGES;
+                if (!mbar_wait(smem_u32(&mma_done[j % RAW_STAGES]), (uint32_t)((j / RAW_STAGES) & 1), abort_flag, status,
+                               ST_STAGE_FREE)) {
+                    ok = false;
+                    break;
+                }
+                // ... so every chunk ending at or before k-block j is complete: drain it now, while the
+                // MMAs fill the other accumulator set
+                while (next_drain < nchunks && (next_drain + 1) * CHUNK - 1 <= j) {
+                    if (!drain(next_drain)) { ok = false; break; }
+                    ++next_drain;
+                }
+                if (!ok) break;
             }
-            const int s = kb % nstages;
-            if (!mbar_wait(smem_u32(&raw_full[s]), (uint32_t)((kb / nstages) & 1), abort_flag, status, ST_RAW_FULL)) {
+            if (!mbar_wait(smem_u32(&raw_full[s]), (uint32_t)((kb / RAW_STAGES) & 1), abort_flag, status, ST_RAW_FULL)) {
                 ok = false;
                 break;
             }
-            uint8_t *st = smem + s * stage_bytes;
-            if (!(dbg & 1)) {
-                split_tile(st, st + 2 * TILE_BYTES, tid);
-                split_tile(st + TILE_BYTES, st + 3 * TILE_BYTES, tid);
-            }
+            if (tid == 0) TRACE(1, kb);  // raw tile seen by the split warps
+            const uint8_t *st = smem + s * RING_BYTES;
+            uint8_t *dl = lo_ring + l * RING_BYTES;
+            split_tile(st, dl, tid);
+            split_tile(st + TILE_BYTES, dl + TILE_BYTES, tid);
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&lo_full[s]));
+            if (lane == 0) mbar_arrive(smem_u32(&lo_full[l]));
+            if (tid == 0) TRACE(2, kb);  // split done
         }
-        while (ok && next_drain < nchunks && !(dbg & 4)) {
+        if (tid == 0) TRACE(5, 2);
+        while (ok && next_drain < nchunks) {
             ok = drain(next_drain);
             ++next_drain;
         }
+        if (tid == 0) TRACE(5, 3);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             const long long m = m0 + q * 32 + lane;
@@ -346,8 +375,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
         }
     }
+    if (tid == 0) TRACE(5, 4);
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) TRACE(5, 5);
     if (warp == MMA_WARP) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
@@ -396,12 +427,15 @@ cudaError_t launch2(const CUtensorMap &ma, const CUtensorMap &mb, long long m, l
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    static const int dbg = getenv("VOLTA_B200_TC_DBG") ? atoi(getenv("VOLTA_B200_TC_DBG")) : 0;  // timing experiments only
-    gemm_tc2_kernel<AK, BKM><<<tiles_m * tiles_n, THREADS, SMEM_BYTES, s>>>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, dbg, (dbg & 8) ? 6 : STAGES, (dbg & 8) ? 2 * TILE_BYTES : STAGE_BYTES);
+    gemm_tc2_kernel<AK, BKM><<<tiles_m * tiles_n, THREADS, SMEM_BYTES, s>>>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status);
     return cudaGetLastError();
 }
 
 }  // namespace
+
+#ifdef VB_TRACE
+extern "C" void vb_trace_set(unsigned long long *p) { cudaMemcpyToSymbol(g_trace, &p, sizeof p); }
+#endif
 
 cudaError_t launch_gemm_tc2(int layout, const float *A, const float *B, long long m, long long n, long long k,
                             const Epilogue &epi, unsigned int *status, cudaStream_t s) {

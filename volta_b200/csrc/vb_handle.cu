@@ -143,8 +143,12 @@ cudaError_t run_gemm(vb200_handle *h, int layout, const float *A, const float *B
                      long long k, const Epilogue &epi) {
     const int path = h->cfg.gemm_path;
     if (path != VB200_GEMM_FFMA && gemm_tc_supported(layout, A, Bm, m, n, k, epi) &&
-        (path == VB200_GEMM_TENSOR || gemm_prefers_tc(m, n, k)))
-        return launch_gemm_tc(layout, A, Bm, m, n, k, epi, h->status_word, h->stream);
+        (path == VB200_GEMM_TENSOR || path == VB200_GEMM_TENSOR_PAIR || gemm_prefers_tc(m, n, k))) {
+        gemm_tc_select_pair(path == VB200_GEMM_TENSOR_PAIR);
+        cudaError_t e = launch_gemm_tc(layout, A, Bm, m, n, k, epi, h->status_word, h->stream);
+        gemm_tc_select_pair(false);
+        return e;
+    }
     return launch_gemm_ffma(layout, A, Bm, m, n, k, epi, h->stream, h->gemm_scratch);
 }
 
@@ -394,7 +398,7 @@ int validate(const vb200_config *c, std::string *why) {
     int world = c->world_size > 1 ? c->world_size : 1;
     if (c->rank < 0 || c->rank >= world) { *why = "rank out of range"; return VB200_ERR_INVALID; }
     if (c->global_batch != 0 && c->global_batch < c->batch) { *why = "global_batch smaller than batch"; return VB200_ERR_INVALID; }
-    if (c->gemm_path < VB200_GEMM_AUTO || c->gemm_path > VB200_GEMM_TENSOR) { *why = "unknown gemm_path"; return VB200_ERR_INVALID; }
+    if (c->gemm_path < VB200_GEMM_AUTO || c->gemm_path > VB200_GEMM_TENSOR_PAIR) { *why = "unknown gemm_path"; return VB200_ERR_INVALID; }
     return VB200_OK;
 }
 
@@ -811,12 +815,14 @@ int volta_b200_gemm(int32_t layout, int32_t path, float *C, const float *A, cons
     e.out0 = C;
     e.ld = n;
     cudaError_t err;
-    if (path == VB200_GEMM_TENSOR) {
+    if (path == VB200_GEMM_TENSOR || path == VB200_GEMM_TENSOR_PAIR) {
         if (!gemm_tc_supported(layout, A, B, m, n, k, e)) return VB200_ERR_UNSUPPORTED;
+        gemm_tc_select_pair(path == VB200_GEMM_TENSOR_PAIR);
         unsigned int *st = nullptr;
         if (cudaMalloc(&st, sizeof(unsigned int)) != cudaSuccess) return VB200_ERR_OOM;
         cudaMemsetAsync(st, 0, sizeof(unsigned int), s);
         err = launch_gemm_tc(layout, A, B, m, n, k, e, st, s);
+        gemm_tc_select_pair(false);
         unsigned int hs = 0;
         if (err == cudaSuccess) err = cudaMemcpyAsync(&hs, st, sizeof hs, cudaMemcpyDeviceToHost, s);
         if (err == cudaSuccess) err = cudaStreamSynchronize(s);

@@ -17,7 +17,7 @@ from .lib import Config, KernelRecord, VoltaB200Error, load_library
 
 ACTIVATIONS = {"relu": 0, "sigmoid": 1, "tanh": 2, "leaky_relu": 3, "leakyrelu": 3, "silu": 4, "gelu": 5, "": 0}
 OPTIMIZERS = {"sgd": 0, "adam": 1, "adamw": 2, "adagrad": 3, "sgd_momentum": 4}
-GEMM_PATHS = {"auto": 0, "ffma": 1, "tensor": 2}
+GEMM_PATHS = {"auto": 0, "ffma": 1, "tensor": 2, "tensor_pair": 3}
 
 
 def _ptr(a):
