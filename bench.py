@@ -236,7 +236,7 @@ def main():
     layers = list(cfg.layers)
 
     h = TrainHandle(layers, cfg.activation, cfg.optimizer, B, global_batch=cfg.batch, world_size=world, rank=rank,
-                    unique_id=uid, gemm_path=args.gemm_path)
+                    unique_id=uid, gemm_path=args.gemm_path, fuse_sgd=(cfg.optimizer == "sgd" and world == 1))
     ws, bs = synth.kaiming_uniform_weights(layers, 42)
     for i, (w, b) in enumerate(zip(ws, bs)):
         h.set_params(i, w, b)

@@ -68,7 +68,10 @@ typedef struct vb200_config {
     int32_t gemm_path;                 /* VB200_GEMM_* */
     int32_t use_graph;                 /* 0 = default (captured CUDA graph), 1 = graph, 2 = plain launches */
     int32_t reserved[8];               /* reserved[0] = 1: build the data-parallel path (communicator, bucketed
-                                          all-reduce) even for world_size 1, so it can be exercised on one GPU */
+                                          all-reduce) even for world_size 1, so it can be exercised on one GPU;
+                                          reserved[1] = 1: plain SGD on one GPU folds the update into the dW GEMM
+                                          epilogue (the reference's sgd_fused_tn); gradients of those layers are
+                                          then never materialised and volta_b200_get_grads does not return them */
 } vb200_config;
 
 typedef struct vb200_handle vb200_handle;
@@ -101,6 +104,13 @@ int volta_b200_set_params(vb200_handle *h, int32_t li, const float *w, const flo
  * the handle; the mirror is refreshed by this call (device -> host copy + wait) and
  * stays valid until destroy. */
 int volta_b200_get_params(vb200_handle *h, float **wo, float **bo);
+
+/* Forward pass only, with the handle's current weights: the GPU counterpart of the reference's
+ * inference entry point volta_infer(in, in_n, out, out_n) (src/engine/ir/codegen/inner.rs:194-198),
+ * which is compiled for batch 1 with the weights embedded.  Here in_n / L0 rows (at most the
+ * handle's batch) go through the same fused GEMM + bias + activation kernels as training;
+ * `in` and `out` may be host or device pointers; out_n must equal rows * Ln.  Call between steps. */
+int volta_b200_infer(vb200_handle *h, const float *in, int64_t in_n, float *out, int64_t out_n);
 
 /* Test/diagnostic extensions (no counterpart in the reference): gradients of the
  * last step (same mirror convention), optimizer-state export/import for checkpoints

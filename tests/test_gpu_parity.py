@@ -454,3 +454,55 @@ def test_generated_per_model_library_runs_the_reference_abi(tmp_path):
     assert rel_err(w0, o.get_params()[0][0]) <= W_TOL
     lib.volta_train_free(h)
     lib.volta_train_free(None)
+
+
+@pytest.mark.parametrize("act", ["relu", "gelu", "sigmoid"])
+def test_infer_matches_the_oracle_forward(act):
+    """volta_b200_infer (the reference's volta_infer on GPU, src/engine/ir/codegen/inner.rs:183-406):
+    outputs of a forward pass with the current weights, for a full batch, one row and a ragged count."""
+    layers, B = [40, 96, 64, 3], 32
+    g, o = _pair(layers, act, "sgd", B)
+    x = synth.rows("normal", 9, 0, B, layers[0])
+    y = synth.rows("normal", 10, 0, B, layers[-1])
+    for _ in range(2):          # move off the initial weights first
+        g.step(x, y, 0.05)
+        o.step(x, y, 0.05)
+    o.step(x, y, 0.0)           # lr 0: a pure forward of the oracle on x
+    ref = o.get_act(o.n)
+    for rows in (B, 1, 7):
+        out = g.infer(np.ascontiguousarray(x[:rows]))
+        assert out.shape == (rows, layers[-1])
+        assert rel_err(out, ref[:rows]) <= W_TOL
+    with pytest.raises(VoltaB200Error):
+        g.infer(np.zeros((B + 1, layers[0]), np.float32))
+    g.step(x, y, 0.05)          # training goes on unharmed
+    o.step(x, y, 0.05)
+    assert abs(g.loss() - o.loss()) <= 1e-5 * abs(o.loss())
+    g.free()
+
+
+@pytest.mark.parametrize("layers,B", [([256, 512, 512, 256, 1], 64), ([96, 260, 8], 300)])
+def test_sgd_folded_into_the_dw_gemm_matches_the_separate_update(layers, B):
+    """fuse_sgd: W -= lr * act^T.delta inside the dW epilogue (the reference's sgd_fused_tn,
+    mlp_train_rust_codegen.rs:321-324, 988).  Same arithmetic per element as GEMM + optimizer
+    kernel, so the two handles must agree bit for bit, and both with the oracle."""
+    x = synth.rows("normal", 21, 0, B, layers[0])
+    y = synth.rows("normal", 22, 0, B, layers[-1])
+    ws, bs = synth.kaiming_uniform_weights(layers, 42)
+    hs = [TrainHandle(layers, "relu", "sgd", B, fuse_sgd=f) for f in (False, True)]
+    o = Oracle(layers, "relu", "sgd", B)
+    for i, (w, b) in enumerate(zip(ws, bs)):
+        o.set_params(i, w, b)
+        for h in hs:
+            h.set_params(i, w, b)
+    for _ in range(5):
+        for h in hs:
+            h.step(x, y, 0.01)
+        o.step(x, y, 0.01)
+    assert np.float32(hs[0].loss()).view(np.uint32) == np.float32(hs[1].loss()).view(np.uint32)
+    for a, b, c in zip(sum(hs[0].get_params(), []), sum(hs[1].get_params(), []), sum(o.get_params(), [])):
+        assert np.array_equal(a, b)
+        assert rel_err(b, c) <= W_TOL
+    assert hs[1].kernels_per_step <= hs[0].kernels_per_step + 1
+    for h in hs:
+        h.free()

@@ -63,6 +63,8 @@ enum EpiMode {
     EPI_BIAS_ACT = 1,  // z = acc + bias[n]; out1[m,n] = z (if out1); out0[m,n] = f(z)   (forward, hidden)
     EPI_BIAS = 2,      // out0[m,n] = acc + bias[n]                         (forward, last layer)
     EPI_DACT = 3,      // out0[m,n] = acc * f'(saved[m,n])                  (dX + activation backward)
+    EPI_SGD = 4,       // out0[m,n] = out0[m,n] - lr * acc                  (dW folded into the SGD update,
+                       //   the reference's sgd_fused_tn, mlp_train_rust_codegen.rs:321-324, 988)
 };
 
 struct Epilogue {
@@ -72,6 +74,7 @@ struct Epilogue {
     float *out1;        // optional second output (pre-activation), same ld
     const float *bias;  // [n]
     const float *saved; // [m x n], same ld
+    const float *lr;    // EPI_SGD: device pointer to this step's learning rate
     long long ld;
 
     __device__ __forceinline__ void apply(long long m, long long n, float acc) const {
@@ -86,6 +89,7 @@ struct Epilogue {
         }
         case EPI_BIAS: out0[idx] = acc + bias[n]; break;
         case EPI_DACT: out0[idx] = acc * act_backward(act, saved[idx]); break;
+        case EPI_SGD: out0[idx] = __fsub_rn(out0[idx], __fmul_rn(*lr, acc)); break;
         }
     }
     // Same for four consecutive columns n..n+3 (idx 16-byte aligned, all in range).
@@ -111,6 +115,14 @@ struct Epilogue {
             *reinterpret_cast<float4 *>(out0 + idx) =
                 make_float4(acc.x * act_backward(act, s.x), acc.y * act_backward(act, s.y),
                             acc.z * act_backward(act, s.z), acc.w * act_backward(act, s.w));
+            break;
+        }
+        case EPI_SGD: {
+            const float l = *lr;
+            float4 w = *reinterpret_cast<const float4 *>(out0 + idx);
+            *reinterpret_cast<float4 *>(out0 + idx) =
+                make_float4(__fsub_rn(w.x, __fmul_rn(l, acc.x)), __fsub_rn(w.y, __fmul_rn(l, acc.y)),
+                            __fsub_rn(w.z, __fmul_rn(l, acc.z)), __fsub_rn(w.w, __fmul_rn(l, acc.w)));
             break;
         }
         }

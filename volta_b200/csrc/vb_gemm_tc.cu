@@ -470,7 +470,9 @@ bool gemm_tc_supported(int layout, const float *A, const float *B, long long m, 
 cudaError_t launch_gemm_tc(int layout, const float *A, const float *B, long long m, long long n, long long k,
                            const Epilogue &epi, unsigned int *status, cudaStream_t s) {
     if (!gemm_tc_supported(layout, A, B, m, n, k, epi)) return cudaErrorNotSupported;
-    static const int version = env_int("VOLTA_B200_TC_VERSION", 2);
+    // Kernel generations: 3 = CTA-pair kernel for outputs of at least 256 x 256 (default), 2 = single-CTA
+    // kernel with in-place high parts (all other shapes), 1 = the first kernel (kept for comparison).
+    static const int version = env_int("VOLTA_B200_TC_VERSION", 3);
     if ((version == 3 || g_force_pair) && m >= 256 && n >= 256) return launch_gemm_tc3(layout, A, B, m, n, k, epi, status, s);
     if (version >= 2) return launch_gemm_tc2(layout, A, B, m, n, k, epi, status, s);
     const bool a_kmajor = (layout != GEMM_TN), b_kmajor = (layout == GEMM_NT);

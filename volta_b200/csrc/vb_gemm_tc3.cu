@@ -37,7 +37,7 @@ constexpr int RING_BYTES = 2 * TILE_BYTES;      // one ring slot: A tile + this 
 constexpr int SMEM_TILES = (RAW_STAGES + LO_STAGES) * RING_BYTES;
 constexpr int SMEM_BYTES = SMEM_TILES + 256 + 1024;
 constexpr int TMEM_COLS = 512;                  // 2 accumulator sets x 256 columns
-constexpr int CHUNK = 4;                        // k-blocks per accumulator drain
+constexpr int DEFAULT_CHUNK = 4;                // k-blocks per accumulator drain (48 additions per accumulator)
                     // drain chunk c-1 when about to split k-block c*CHUNK + LAG
 constexpr int GROUP_M = 8;
 
@@ -185,7 +185,7 @@ __device__ __forceinline__ void split_tile(const uint8_t *raw, uint8_t *lo_t, in
 template <bool A_KMAJOR, bool B_KMAJOR>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, long long M,
-                long long N, long long K, int tiles_m, int tiles_n, Epilogue epi, unsigned int *status) {
+                long long N, long long K, int tiles_m, int tiles_n, Epilogue epi, unsigned int *status, int CHUNK) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + SMEM_TILES);
@@ -455,7 +455,8 @@ cudaError_t launch3(const CUtensorMap &ma, const CUtensorMap &mb, long long m, l
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    gemm_tc3_kernel<AK, BKM><<<2 * tiles_m * tiles_n, THREADS, SMEM_BYTES, s>>>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status);
+    static const int chunk = [] { const char *e = getenv("VOLTA_B200_TC_CHUNK"); int v = e ? atoi(e) : DEFAULT_CHUNK; return v < 2 ? 2 : (v > 16 ? 16 : v); }();
+    gemm_tc3_kernel<AK, BKM><<<2 * tiles_m * tiles_n, THREADS, SMEM_BYTES, s>>>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, chunk);
     return cudaGetLastError();
 }
 

@@ -78,6 +78,7 @@ struct vb200_handle {
     std::vector<cudaEvent_t> ev_bucket;
     cudaGraphExec_t graph[2] = {nullptr, nullptr};
     bool use_graph = true;
+    bool fuse_sgd = false;   // plain SGD on one GPU: dW GEMMs update W in their epilogue
     int kernels_per_step = 0;
 
     DpComm *dp = nullptr;
@@ -86,8 +87,14 @@ struct vb200_handle {
     bool profiling = false;
     std::vector<KernelRecord> records;
 
+    // a failure of the handle itself (CUDA, NCCL, a device-side wait): stays in `status`
     int fail(int code, const std::string &msg) {
         status = code;
+        error = msg;
+        return code;
+    }
+    // a refused call (bad argument): reported to the caller, the handle stays healthy
+    int reject(int code, const std::string &msg) {
         error = msg;
         return code;
     }
@@ -152,17 +159,16 @@ cudaError_t run_gemm(vb200_handle *h, int layout, const float *A, const float *B
     return launch_gemm_ffma(layout, A, Bm, m, n, k, epi, h->stream, h->gemm_scratch);
 }
 
-// Enqueue one whole step on h->stream reading inputs from `slot`.
-int enqueue_step(vb200_handle *h, int slot) {
-    const int n = h->n, B = h->B, act = h->cfg.activation;
+// Forward pass over the first `rows` rows of input slot `slot` (rows <= batch): every layer's GEMM
+// with bias and activation fused.  Used by the training step (rows = batch) and by inference.
+int enqueue_forward(vb200_handle *h, int slot, long long rows) {
+    const int n = h->n, act = h->cfg.activation;
+    const long long B = rows;
     const std::vector<int> &L = h->L;
     cudaStream_t s = h->stream;
-    h->kernels_per_step = 0;
     const float *act0 = h->xin[slot];
     auto A = [&](int i) -> float * { return i == 0 ? const_cast<float *>(act0) : h->act[i]; };
-    char nm[48];
-
-    // forward
+    char nm[64];
     for (int i = 0; i < n; ++i) {
         const long long r = L[i], c = L[i + 1];
         Epilogue e{};
@@ -179,14 +185,31 @@ int enqueue_step(vb200_handle *h, int slot) {
         }
         if (i == n - 1 && c == 1) {
             // width-one output layer: a row-dot, bandwidth-bound on act_i
-            snprintf(nm, sizeof nm, "fwd%d_rowdot_%lldx%lld", i, (long long)B, r);
+            snprintf(nm, sizeof nm, "fwd%d_rowdot_%lldx%lld", i, B, r);
             Scope sc(h, nm, 2.0 * B * r, 4.0 * (B * r + r + B));
             VB_CUDA(h, launch_rowdot(h->act[n], A(i), h->params + h->off_w[i], e.bias, B, r, s));
             continue;
         }
-        snprintf(nm, sizeof nm, "fwd%d_gemm_nn_%lldx%lldx%lld", i, (long long)B, c, r);
+        snprintf(nm, sizeof nm, "fwd%d_gemm_nn_%lldx%lldx%lld", i, B, c, r);
         Scope sc(h, nm, 2.0 * B * r * c, 4.0 * (B * r + r * c + B * c * (e.out1 ? 2 : 1)));
         VB_CUDA(h, run_gemm(h, GEMM_NN, A(i), h->params + h->off_w[i], B, c, r, e));
+    }
+    return VB200_OK;
+}
+
+// Enqueue one whole step on h->stream reading inputs from `slot`.
+int enqueue_step(vb200_handle *h, int slot) {
+    const int n = h->n, B = h->B, act = h->cfg.activation;
+    const std::vector<int> &L = h->L;
+    cudaStream_t s = h->stream;
+    h->kernels_per_step = 0;
+    const float *act0 = h->xin[slot];
+    auto A = [&](int i) -> float * { return i == 0 ? const_cast<float *>(act0) : h->act[i]; };
+    char nm[64];
+
+    {
+        int rc = enqueue_forward(h, slot, B);
+        if (rc) return rc;
     }
     // loss + seed gradient
     {
@@ -196,9 +219,28 @@ int enqueue_step(vb200_handle *h, int slot) {
         VB_CUDA(h, launch_mse_seed(h->delta[n - 1], h->loss_sum, h->act[n], h->yin[slot], nt, (float)h->global_nt,
                                    h->mse_scratch, s));
     }
-    // backward
+    // backward.  Per layer: dW_i, db_i, then dX_i -> delta_{i-1}.  With the SGD update folded into
+    // the dW epilogue, dX_i (which must read the pre-update W_i) goes first.
     for (int i = n - 1; i >= 0; --i) {
         const long long r = L[i], c = L[i + 1];
+        auto do_dx = [&]() -> int {
+            if (i == 0) return VB200_OK;
+            Epilogue e{};
+            e.mode = EPI_DACT;
+            e.act = act;
+            e.out0 = h->delta[i - 1];
+            e.saved = act_needs_pre(act) ? h->pre[i - 1] : h->act[i];
+            e.ld = r;
+            snprintf(nm, sizeof nm, "dX%d_gemm_nt_%lldx%lldx%lld", i, (long long)B, r, c);
+            Scope sc(h, nm, 2.0 * B * r * c, 4.0 * (B * c + r * c + 2.0 * B * r));
+            VB_CUDA(h, run_gemm(h, GEMM_NT, h->delta[i], h->params + h->off_w[i], B, r, c, e));
+            return VB200_OK;
+        };
+        const bool fused = h->fuse_sgd && c != 1;
+        if (fused) {
+            int rc = do_dx();
+            if (rc) return rc;
+        }
         if (c == 1) {
             // dW of a width-one layer: column sums of act_i weighted by delta_i[row]
             snprintf(nm, sizeof nm, "dW%d_wcolsum_%lldx%lld", i, (long long)B, r);
@@ -207,11 +249,12 @@ int enqueue_step(vb200_handle *h, int slot) {
             VB_CUDA(h, launch_colsum(h->grads + h->off_w[i], A(i), B, r, h->colsum_scratch, s, h->delta[i]));
         } else {
             Epilogue e{};
-            e.mode = EPI_STORE;
-            e.out0 = h->grads + h->off_w[i];
+            e.mode = fused ? EPI_SGD : EPI_STORE;
+            e.out0 = fused ? h->params + h->off_w[i] : h->grads + h->off_w[i];
+            e.lr = &h->scalars->lr;
             e.ld = c;
-            snprintf(nm, sizeof nm, "dW%d_gemm_tn_%lldx%lldx%lld", i, r, c, (long long)B);
-            Scope sc(h, nm, 2.0 * B * r * c, 4.0 * (B * r + B * c + r * c));
+            snprintf(nm, sizeof nm, fused ? "dW%d_sgd_gemm_tn_%lldx%lldx%lld" : "dW%d_gemm_tn_%lldx%lldx%lld", i, r, c, (long long)B);
+            Scope sc(h, nm, 2.0 * B * r * c, 4.0 * (B * r + B * c + (fused ? 2.0 : 1.0) * r * c));
             VB_CUDA(h, run_gemm(h, GEMM_TN, A(i), h->delta[i], r, c, B, e));
         }
         if (h->dp) {
@@ -227,16 +270,9 @@ int enqueue_step(vb200_handle *h, int slot) {
             h->kernels_per_step++;
             VB_CUDA(h, launch_colsum(h->grads + h->off_b[i], h->delta[i], B, c, h->colsum_scratch, s));
         }
-        if (i > 0) {
-            Epilogue e{};
-            e.mode = EPI_DACT;
-            e.act = act;
-            e.out0 = h->delta[i - 1];
-            e.saved = act_needs_pre(act) ? h->pre[i - 1] : h->act[i];
-            e.ld = r;
-            snprintf(nm, sizeof nm, "dX%d_gemm_nt_%lldx%lldx%lld", i, (long long)B, r, c);
-            Scope sc(h, nm, 2.0 * B * r * c, 4.0 * (B * c + r * c + 2.0 * B * r));
-            VB_CUDA(h, run_gemm(h, GEMM_NT, h->delta[i], h->params + h->off_w[i], B, r, c, e));
+        if (!fused) {
+            int rc = do_dx();
+            if (rc) return rc;
         }
     }
     if (h->dp) {
@@ -253,9 +289,23 @@ int enqueue_step(vb200_handle *h, int slot) {
     {
         const int opt = h->cfg.optimizer;
         double bpp = opt == VB200_OPT_SGD ? 12.0 : (opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW) ? 28.0 : 20.0;
-        Scope sc(h, "optimizer", 0.0, bpp * h->n_params_padded);
-        VB_CUDA(h, launch_optimizer(opt, h->params, h->s1, h->s2, h->grads, h->n_params_padded, h->n_weights_padded,
-                                    h->scalars, s));
+        if (h->fuse_sgd) {
+            // weights of every layer wider than one were updated by their dW GEMM; the rest follows here
+            for (int i = 0; i < n; ++i)
+                if (L[i + 1] == 1) {
+                    Scope sc(h, "optimizer_w1", 0.0, bpp * L[i]);
+                    VB_CUDA(h, launch_optimizer(opt, h->params + h->off_w[i], h->s1, h->s2, h->grads + h->off_w[i],
+                                                pad64(L[i]), 0, h->scalars, s));
+                }
+            const int64_t nb = h->n_params_padded - h->n_weights_padded;
+            Scope sc(h, "optimizer_bias", 0.0, bpp * nb);
+            VB_CUDA(h, launch_optimizer(opt, h->params + h->n_weights_padded, h->s1, h->s2, h->grads + h->n_weights_padded,
+                                        nb, 0, h->scalars, s));
+        } else {
+            Scope sc(h, "optimizer", 0.0, bpp * h->n_params_padded);
+            VB_CUDA(h, launch_optimizer(opt, h->params, h->s1, h->s2, h->grads, h->n_params_padded, h->n_weights_padded,
+                                        h->scalars, s));
+        }
     }
     VB_CUDA(h, cudaMemcpyAsync(&h->host_loss[slot], h->loss_sum, sizeof(float), cudaMemcpyDeviceToHost, s));
     VB_CUDA(h, cudaMemcpyAsync(h->host_status, h->status_word, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
@@ -320,7 +370,7 @@ int copy_inputs(vb200_handle *h, int slot, const float *X, const float *Y, bool 
 }
 
 int do_step(vb200_handle *h, const float *X, const float *Y, float lr, bool profile) {
-    if (!X || !Y) return h->fail(VB200_ERR_INVALID, "volta_b200_step: null input pointer");
+    if (!X || !Y) return h->reject(VB200_ERR_INVALID, "volta_b200_step: null input pointer");
     const int slot = profile ? 0 : (int)(h->steps_done & 1);
     bool host_wait = false;
     int rc = copy_inputs(h, slot, X, Y, &host_wait);
@@ -478,6 +528,7 @@ int build(vb200_handle *h) {
     const long long gb = c.global_batch ? c.global_batch : (long long)c.batch * h->world;
     h->global_nt = gb * h->L[n];
     h->use_graph = c.use_graph != 2;
+    h->fuse_sgd = (c.reserved[1] == 1) && c.optimizer == VB200_OPT_SGD && h->world == 1 && c.reserved[0] != 1;
     const int B = h->B;
     const std::vector<int> &L = h->L;
 
@@ -629,7 +680,7 @@ float volta_b200_loss(vb200_handle *h) {
 int volta_b200_set_params(vb200_handle *h, int32_t li, const float *w, const float *b) {
     if (!h) return VB200_ERR_INVALID;
     if (li < 0 || li >= h->n) return VB200_OK;  // ignored, as in the reference
-    if (!w || !b) return h->fail(VB200_ERR_INVALID, "set_params: null pointer");
+    if (!w || !b) return h->reject(VB200_ERR_INVALID, "set_params: null pointer");
     const size_t wn = (size_t)h->L[li] * h->L[li + 1], bn = (size_t)h->L[li + 1];
     VB_CUDA(h, cudaStreamSynchronize(h->stream));
     VB_CUDA(h, cudaMemcpy(h->params + h->off_w[li], w, wn * 4, cudaMemcpyHostToDevice));
@@ -672,7 +723,7 @@ int64_t volta_b200_state_floats(vb200_handle *h) {
 int volta_b200_save_state(vb200_handle *h, float *out, int64_t n, uint64_t *step_out) {
     if (!h) return VB200_ERR_INVALID;
     const int64_t need = volta_b200_state_floats(h);
-    if (n < need || (need && !out)) return h->fail(VB200_ERR_INVALID, "save_state: buffer too small");
+    if (n < need || (need && !out)) return h->reject(VB200_ERR_INVALID, "save_state: buffer too small");
     VB_CUDA(h, cudaStreamSynchronize(h->stream));
     const int64_t P = h->n_params_padded;
     if (need >= P) VB_CUDA(h, cudaMemcpy(out, h->s1, (size_t)P * 4, cudaMemcpyDeviceToHost));
@@ -684,7 +735,7 @@ int volta_b200_save_state(vb200_handle *h, float *out, int64_t n, uint64_t *step
 int volta_b200_load_state(vb200_handle *h, const float *in, int64_t n, uint64_t step) {
     if (!h) return VB200_ERR_INVALID;
     const int64_t need = volta_b200_state_floats(h);
-    if (n < need || (need && !in)) return h->fail(VB200_ERR_INVALID, "load_state: buffer too small");
+    if (n < need || (need && !in)) return h->reject(VB200_ERR_INVALID, "load_state: buffer too small");
     VB_CUDA(h, cudaStreamSynchronize(h->stream));
     const int64_t P = h->n_params_padded;
     if (need >= P) VB_CUDA(h, cudaMemcpy(h->s1, in, (size_t)P * 4, cudaMemcpyHostToDevice));
@@ -784,6 +835,31 @@ int volta_b200_profile_step(vb200_handle *h, const float *X, const float *Y, flo
         o.bytes = r.bytes;
     }
     return cnt;
+}
+
+int volta_b200_infer(vb200_handle *h, const float *in, int64_t in_n, float *out, int64_t out_n) {
+    if (!h) return VB200_ERR_INVALID;
+    if (!in || !out) return h->reject(VB200_ERR_INVALID, "infer: null pointer");
+    const int64_t L0 = h->L[0], Ln = h->L[h->n];
+    if (in_n <= 0 || in_n % L0 != 0) return h->reject(VB200_ERR_INVALID, "infer: input length is not a multiple of the input width");
+    const int64_t rows = in_n / L0;
+    if (rows > h->B) return h->reject(VB200_ERR_INVALID, "infer: more rows than the handle's batch");
+    if (out_n != rows * Ln) return h->reject(VB200_ERR_INVALID, "infer: output length does not match rows x output width");
+    // between steps only: wait for queued training work, then reuse its buffers
+    VB_CUDA(h, cudaStreamSynchronize(h->copy_stream));
+    VB_CUDA(h, cudaStreamSynchronize(h->stream));
+    cudaPointerAttributes ai{}, ao{};
+    bool idev = false, odev = false;
+    if (cudaPointerGetAttributes(&ai, in) == cudaSuccess) idev = ai.type == cudaMemoryTypeDevice || ai.type == cudaMemoryTypeManaged; else cudaGetLastError();
+    if (cudaPointerGetAttributes(&ao, out) == cudaSuccess) odev = ao.type == cudaMemoryTypeDevice || ao.type == cudaMemoryTypeManaged; else cudaGetLastError();
+    VB_CUDA(h, cudaMemcpyAsync(h->xin[0], in, (size_t)in_n * 4, idev ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, h->stream));
+    const int saved = h->kernels_per_step;
+    int rc = enqueue_forward(h, 0, rows);
+    h->kernels_per_step = saved;
+    if (rc) return rc;
+    VB_CUDA(h, cudaMemcpyAsync(out, h->act[h->n], (size_t)out_n * 4, odev ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, h->stream));
+    VB_CUDA(h, cudaStreamSynchronize(h->stream));
+    return check_device_status(h);
 }
 
 int volta_b200_dp_unique_id(uint8_t out[128]) { return DpComm::unique_id(out) ? VB200_ERR_NCCL : VB200_OK; }

@@ -31,7 +31,7 @@ class KernelRecord(C.Structure):
 # every symbol include/volta_b200.h declares
 EXPORTS = [
     "volta_b200_create", "volta_b200_destroy", "volta_b200_step", "volta_b200_loss", "volta_b200_set_params",
-    "volta_b200_get_params", "volta_b200_get_grads", "volta_b200_state_floats", "volta_b200_save_state",
+    "volta_b200_get_params", "volta_b200_infer", "volta_b200_get_grads", "volta_b200_state_floats", "volta_b200_save_state",
     "volta_b200_load_state", "volta_b200_status", "volta_b200_last_error", "volta_b200_stream",
     "volta_b200_synchronize", "volta_b200_arena_bytes", "volta_b200_plan", "volta_b200_kernels_per_step",
     "volta_b200_profile_step", "volta_b200_dp_unique_id", "volta_b200_optimizer_apply", "volta_b200_gemm",
@@ -64,6 +64,7 @@ def load_library():
         "volta_b200_loss": (C.c_float, [vp]),
         "volta_b200_set_params": (C.c_int, [vp, i32, fp, fp]),
         "volta_b200_get_params": (C.c_int, [vp, fpp, fpp]),
+        "volta_b200_infer": (C.c_int, [vp, vp, i64, vp, i64]),
         "volta_b200_get_grads": (C.c_int, [vp, fpp, fpp]),
         "volta_b200_state_floats": (i64, [vp]),
         "volta_b200_save_state": (C.c_int, [vp, fp, i64, C.POINTER(C.c_uint64)]),

@@ -52,7 +52,7 @@ class TrainHandle:
 
     def __init__(self, layers, activation="relu", optimizer="sgd", batch=1, *, global_batch=0, world_size=1, rank=0,
                  unique_id: bytes | None = None, momentum=0.0, weight_decay=0.0, gemm_path="auto", use_graph=True,
-                 force_dp=False):
+                 force_dp=False, fuse_sgd=False):
         act = activation.lower()
         opt = optimizer.lower()
         if act not in ACTIVATIONS:
@@ -85,6 +85,7 @@ class TrainHandle:
         cfg.weight_decay = float(weight_decay)
         cfg.gemm_path = GEMM_PATHS[gemm_path]
         cfg.use_graph = 1 if use_graph else 2
+        cfg.reserved[1] = 1 if fuse_sgd else 0
         self._cfg = cfg
         h = C.c_void_p()
         rc = self.lib.volta_b200_create(C.byref(cfg), C.byref(h))
@@ -134,6 +135,15 @@ class TrainHandle:
         if getattr(self, "h", None):
             self.lib.volta_b200_destroy(self.h)
             self.h = None
+
+    def infer(self, x):
+        """Forward pass with the current weights (the reference's volta_infer, for up to `batch` rows).
+        x: [rows x L0] float32 numpy array or CUDA tensor; returns a numpy array [rows x Ln]."""
+        n_in = int(np.prod(x.shape))
+        rows = n_in // self.layers[0]
+        out = np.empty((rows, self.layers[-1]), dtype=np.float32)
+        self._check(self.lib.volta_b200_infer(self.h, _ptr(x), n_in, out.ctypes.data, out.size))
+        return out
 
     # -- extensions -------------------------------------------------------------------------
     def get_grads(self):
