@@ -184,6 +184,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--gemm-path", default="auto", choices=["auto", "ffma", "tensor", "tensor_pair"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-other-workloads", action="store_true")
     ap.add_argument("--batch", type=int, default=None,
                     help="override the workload's global batch (for small profiler captures; not a headline number)")
     args = ap.parse_args()
@@ -361,6 +362,45 @@ def main():
         except Exception as exc:  # secondary line only
             cpu_baseline["torch_cpu_eager"] = {"error": str(exc)}
 
+    # ---- the single-GPU configurations, briefly (device-resident inputs, L2 flushed between steps)
+    others = None
+    if world == 1 and not args.batch and not args.no_other_workloads:
+        others = {}
+        for name in ("c1", "c2", "c3_b64", "c3_b1024"):
+            if name == args.workload:
+                continue
+            oc = CONFIGS[name]
+            ol = list(oc.layers)
+            oh = TrainHandle(ol, oc.activation, oc.optimizer, oc.batch, gemm_path=args.gemm_path,
+                             fuse_sgd=(oc.optimizer == "sgd"))
+            for i, (w, b) in enumerate(zip(*synth.kaiming_uniform_weights(ol, 42))):
+                oh.set_params(i, w, b)
+            ox = torch.from_numpy(synth.rows(oc.x_dist, 1234, 0, oc.batch, ol[0])).cuda()
+            oy = torch.from_numpy(synth.rows(oc.y_dist, 4321, 0, oc.batch, ol[-1])).cuda()
+            ostream = torch.cuda.ExternalStream(oh.stream)
+            if flush_buf is None:
+                flush_buf = torch.empty(int(256e6) // 4, device="cuda")
+            for _ in range(5):
+                oh.step(ox, oy, oc.lr)
+            oh.synchronize()
+            pairs = []
+            for _ in range(oc.steps):
+                with torch.cuda.stream(ostream):
+                    flush_buf.zero_()
+                a, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(ostream)
+                oh.step(ox, oy, oc.lr)
+                b2.record(ostream)
+                pairs.append((a, b2))
+            oh.synchronize()
+            torch.cuda.synchronize()
+            ms = sorted(x.elapsed_time(y2) for x, y2 in pairs)
+            med = ms[len(ms) // 2]
+            others[name] = {"ms_per_step": med, "samples_per_s": oc.batch / (med * 1e-3), "steps": oc.steps,
+                            "kernels_per_step": oh.kernels_per_step, "loss": oh.loss(),
+                            "workload": "MLP %s, %s, %s, B=%d" % ("->".join(map(str, ol)), oc.activation, oc.optimizer, oc.batch)}
+            oh.free()
+
     if rank == 0:
         line = {"metric": "train_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": world, "steps": steps,
                 "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
@@ -371,7 +411,7 @@ def main():
                 "tflops_logical_fp32": cfg.flops_per_step() / (ms_per_step * 1e-3) / 1e12,
                 "loss": loss_dev, "loss_e2e": last, "e2e": e2e, "gpu_launches": h.kernels_per_step * steps,
                 "kernels_per_step": h.kernels_per_step, "clocks": sampler.summary(), "roofline": roofline,
-                "cpu_baseline": cpu_baseline, "kernels": kernel_table}
+                "cpu_baseline": cpu_baseline, "other_workloads": others, "kernels": kernel_table}
         print(json.dumps(line))
     h.free()
     if world > 1:

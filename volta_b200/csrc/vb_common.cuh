@@ -7,7 +7,42 @@
 
 #include "../../include/volta_b200.h"
 
+#include <stdlib.h>
+
+#include <utility>
+
 namespace vb {
+
+// ---------------------------------------------------------------------------------------
+// Programmatic dependent launch.  The step is a chain of short kernels, each depending on the
+// one before; launched this way a kernel's CTAs can be scheduled while its predecessor drains,
+// and they block in pdl_wait() until the predecessor has completed and its writes are visible.
+// Rule for every kernel launched through launch_pdl: call pdl_wait() before the first access
+// to global memory, and pdl_trigger() once the dependent may start being scheduled.
+// VOLTA_B200_PDL=0 turns the launch attribute off (the device-side calls are then no-ops).
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+    static const bool on = [] { const char *e = getenv("VOLTA_B200_PDL"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
 
 // ---------------------------------------------------------------------------------------
 // Activation math, following the reference's generated helpers

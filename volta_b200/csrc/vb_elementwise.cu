@@ -51,6 +51,8 @@ __global__ void __launch_bounds__(256) optimizer_kernel(float *__restrict__ p, f
                                                         float *__restrict__ s2, const float *__restrict__ g,
                                                         long long n, long long n_decay,
                                                         const StepScalars *__restrict__ scp) {
+    pdl_wait();
+    pdl_trigger();
     const StepScalars sc = *scp;
     constexpr bool HAS1 = (OPT != VB200_OPT_SGD);
     constexpr bool HAS2 = (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW);
@@ -110,13 +112,12 @@ cudaError_t launch_optimizer(int optimizer, float *p, float *s1, float *s2, cons
     long long cap = (long long)sm_count() * 8;  // 8 resident CTAs of 256 threads per SM, grid-stride beyond
     int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
     switch (optimizer) {
-    case VB200_OPT_SGD: optimizer_kernel<VB200_OPT_SGD><<<blocks, 256, 0, s>>>(p, s1, s2, g, n, n_decay, sc); break;
-    case VB200_OPT_ADAM: optimizer_kernel<VB200_OPT_ADAM><<<blocks, 256, 0, s>>>(p, s1, s2, g, n, n_decay, sc); break;
-    case VB200_OPT_ADAMW: optimizer_kernel<VB200_OPT_ADAMW><<<blocks, 256, 0, s>>>(p, s1, s2, g, n, n_decay, sc); break;
-    case VB200_OPT_ADAGRAD: optimizer_kernel<VB200_OPT_ADAGRAD><<<blocks, 256, 0, s>>>(p, s1, s2, g, n, n_decay, sc); break;
+    case VB200_OPT_SGD: return launch_pdl(optimizer_kernel<VB200_OPT_SGD>, dim3(blocks), dim3(256), 0, s, p, s1, s2, g, n, n_decay, sc);
+    case VB200_OPT_ADAM: return launch_pdl(optimizer_kernel<VB200_OPT_ADAM>, dim3(blocks), dim3(256), 0, s, p, s1, s2, g, n, n_decay, sc);
+    case VB200_OPT_ADAMW: return launch_pdl(optimizer_kernel<VB200_OPT_ADAMW>, dim3(blocks), dim3(256), 0, s, p, s1, s2, g, n, n_decay, sc);
+    case VB200_OPT_ADAGRAD: return launch_pdl(optimizer_kernel<VB200_OPT_ADAGRAD>, dim3(blocks), dim3(256), 0, s, p, s1, s2, g, n, n_decay, sc);
     case VB200_OPT_SGD_MOMENTUM:
-        optimizer_kernel<VB200_OPT_SGD_MOMENTUM><<<blocks, 256, 0, s>>>(p, s1, s2, g, n, n_decay, sc);
-        break;
+        return launch_pdl(optimizer_kernel<VB200_OPT_SGD_MOMENTUM>, dim3(blocks), dim3(256), 0, s, p, s1, s2, g, n, n_decay, sc);
     default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();
@@ -152,6 +153,8 @@ __global__ void __launch_bounds__(32 * CS_TY) colsum_pass1(float *__restrict__ p
                                                            const float *__restrict__ wgt, long long rows,
                                                            long long cols, long long rows_per_chunk) {
     __shared__ float4 sm[CS_TY][32];
+    pdl_wait();
+    pdl_trigger();
     const int tx = threadIdx.x, ty = threadIdx.y;
     const long long c0 = (long long)blockIdx.x * CS_COLS + tx * 4;
     const long long r0 = (long long)blockIdx.y * rows_per_chunk;
@@ -196,6 +199,8 @@ __global__ void __launch_bounds__(32 * CS_TY) colsum_pass1(float *__restrict__ p
 
 __global__ void colsum_pass2(float *__restrict__ out, const float *__restrict__ partial, long long chunks,
                              long long cols) {
+    pdl_wait();
+    pdl_trigger();
     long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= cols) return;
     float t = partial[c];
@@ -209,11 +214,9 @@ cudaError_t launch_colsum(float *out, const float *in, long long rows, long long
     long long chunks = colsum_chunks(rows, cols);
     long long rpc = (rows + chunks - 1) / chunks;
     dim3 grid((unsigned)((cols + CS_COLS - 1) / CS_COLS), (unsigned)chunks), block(32, CS_TY);
-    colsum_pass1<<<grid, block, 0, s>>>(scratch, in, row_weight, rows, cols, rpc);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(colsum_pass1, grid, block, 0, s, scratch, in, row_weight, rows, cols, rpc);
     if (e != cudaSuccess) return e;
-    colsum_pass2<<<(unsigned)((cols + 255) / 256), 256, 0, s>>>(out, scratch, chunks, cols);
-    return cudaGetLastError();
+    return launch_pdl(colsum_pass2, dim3((unsigned)((cols + 255) / 256)), dim3(256), 0, s, out, (const float *)scratch, chunks, cols);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -223,6 +226,8 @@ cudaError_t launch_colsum(float *out, const float *in, long long rows, long long
 __global__ void __launch_bounds__(256) rowdot_kernel(float *__restrict__ out, const float *__restrict__ in,
                                                      const float *__restrict__ w, const float *__restrict__ bias,
                                                      long long rows, long long cols) {
+    pdl_wait();
+    pdl_trigger();
     const int lane = threadIdx.x & 31;
     const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
     const bool vec = ((cols & 3) == 0) && (((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(w)) & 15) == 0);
@@ -249,8 +254,7 @@ cudaError_t launch_rowdot(float *out, const float *in, const float *w, const flo
     if (rows <= 0 || cols <= 0) return cudaErrorInvalidValue;
     long long want = (rows + 7) / 8, cap = (long long)sm_count() * 8;
     int blocks = (int)(want > cap ? cap : want);
-    rowdot_kernel<<<blocks, 256, 0, s>>>(out, in, w, bias, rows, cols);
-    return cudaGetLastError();
+    return launch_pdl(rowdot_kernel, dim3(blocks), dim3(256), 0, s, out, in, w, bias, rows, cols);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -286,6 +290,8 @@ __global__ void __launch_bounds__(MSE_THREADS) mse_pass1(float *__restrict__ del
                                                          const float *__restrict__ out, const float *__restrict__ y,
                                                          long long nt, float nt_global) {
     __shared__ float sm[MSE_THREADS / 32];
+    pdl_wait();
+    pdl_trigger();
     long long base = (long long)blockIdx.x * MSE_PER_BLOCK;
     float acc = 0.0f;
 #pragma unroll 4
@@ -304,6 +310,8 @@ __global__ void __launch_bounds__(MSE_THREADS) mse_pass1(float *__restrict__ del
 __global__ void __launch_bounds__(MSE_THREADS) mse_pass2(float *__restrict__ loss_sum,
                                                          const float *__restrict__ partial, long long nblocks) {
     __shared__ float sm[MSE_THREADS / 32];
+    pdl_wait();
+    pdl_trigger();
     float acc = 0.0f;
     for (long long k = threadIdx.x; k < nblocks; k += MSE_THREADS) acc += partial[k];
     float t = block_sum_256(acc, sm);
@@ -313,11 +321,9 @@ __global__ void __launch_bounds__(MSE_THREADS) mse_pass2(float *__restrict__ los
 cudaError_t launch_mse_seed(float *delta, float *loss_sum, const float *out, const float *y, long long nt,
                             float nt_global, float *scratch, cudaStream_t s) {
     long long nb = loss_blocks(nt);
-    mse_pass1<<<(unsigned)nb, MSE_THREADS, 0, s>>>(delta, scratch, out, y, nt, nt_global);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(mse_pass1, dim3((unsigned)nb), dim3(MSE_THREADS), 0, s, delta, scratch, out, y, nt, nt_global);
     if (e != cudaSuccess) return e;
-    mse_pass2<<<1, MSE_THREADS, 0, s>>>(loss_sum, scratch, nb);
-    return cudaGetLastError();
+    return launch_pdl(mse_pass2, dim3(1), dim3(MSE_THREADS), 0, s, loss_sum, (const float *)scratch, nb);
 }
 
 }  // namespace vb

@@ -22,6 +22,8 @@ gemm_ffma_kernel(const float *__restrict__ A, const float *__restrict__ B, long 
     __shared__ __align__(16) float As[2][BK][BM + PAD];
     __shared__ __align__(16) float Bs[2][BK][BN + PAD];
 
+    pdl_wait();
+    pdl_trigger();
     const int tid = threadIdx.x;
     const int tx = tid % (BN / TN), ty = tid / (BN / TN);
     const long long m0 = (long long)blockIdx.y * BM, n0 = (long long)blockIdx.x * BN;
@@ -145,6 +147,8 @@ gemm_ffma_kernel(const float *__restrict__ A, const float *__restrict__ B, long 
 // Adds the split-K slabs in split order and applies the epilogue.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ partial, long long M, long long N,
                                                             int splits, Epilogue epi) {
+    pdl_wait();
+    pdl_trigger();
     const long long total = M * N;
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
@@ -202,26 +206,23 @@ cudaError_t launch_gemm_ffma(int layout, const float *A, const float *B, long lo
         const long long k_len = ((k + splits - 1) / splits + 15) / 16 * 16;
         const int zs = (int)((k + k_len - 1) / k_len);
         dim3 grid((unsigned)((n + 63) / 64), (unsigned)((m + 63) / 64), (unsigned)zs);
-        gemm_ffma_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, s>>>(A, B, m, n, k, a_sm, a_sk, b_sk, b_sn, epi, k_len, scratch);
-        cudaError_t e = cudaGetLastError();
+        cudaError_t e = launch_pdl(gemm_ffma_kernel<64, 64, 16, 4, 4>, grid, dim3(256), 0, s, A, B, m, n, k, a_sm, a_sk, b_sk, b_sn, epi, k_len, scratch);
         if (e != cudaSuccess) return e;
         long long total = m * n;
         int blocks = (int)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184);
-        splitk_reduce_kernel<<<blocks, 256, 0, s>>>(scratch, m, n, zs, epi);
-        return cudaGetLastError();
+        return launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, s, (const float *)scratch, m, n, zs, epi);
     }
     // Small outputs get small tiles so that more SMs take part; the choice depends on the shape only.
     long long tiles64 = ((m + 63) / 64) * ((n + 63) / 64);
     if (tiles64 >= 96 || (m >= 64 && n >= 64 && tiles64 >= 48)) {
         dim3 grid((unsigned)((n + 63) / 64), (unsigned)((m + 63) / 64));
         if (grid.y > 65535) return cudaErrorInvalidConfiguration;
-        gemm_ffma_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, s>>>(A, B, m, n, k, a_sm, a_sk, b_sk, b_sn, epi, k, nullptr);
+        return launch_pdl(gemm_ffma_kernel<64, 64, 16, 4, 4>, grid, dim3(256), 0, s, A, B, m, n, k, a_sm, a_sk, b_sk, b_sn, epi, k, (float *)nullptr);
     } else {
         dim3 grid((unsigned)((n + 31) / 32), (unsigned)((m + 31) / 32));
         if (grid.y > 65535) return cudaErrorInvalidConfiguration;
-        gemm_ffma_kernel<32, 32, 16, 4, 4><<<grid, 64, 0, s>>>(A, B, m, n, k, a_sm, a_sk, b_sk, b_sn, epi, k, nullptr);
+        return launch_pdl(gemm_ffma_kernel<32, 32, 16, 4, 4>, grid, dim3(64), 0, s, A, B, m, n, k, a_sm, a_sk, b_sk, b_sn, epi, k, (float *)nullptr);
     }
-    return cudaGetLastError();
 }
 
 }  // namespace vb

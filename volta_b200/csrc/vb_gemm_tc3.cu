@@ -187,6 +187,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, long long M,
                 long long N, long long K, int tiles_m, int tiles_n, Epilogue epi, unsigned int *status, int CHUNK) {
     extern __shared__ uint8_t smem_raw[];
+    pdl_wait();   // nothing of the previous kernel's output is touched before this
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + SMEM_TILES);
     uint64_t *raw_full = bars, *lo_full = bars + 8, *mma_done = bars + 16, *acc_full = bars + 24, *acc_empty = bars + 26;
@@ -382,6 +383,7 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             ok = drain(next_drain);
             ++next_drain;
         }
+        if (tid == 0) pdl_trigger();   // the next kernel's CTAs may take SMs as ours retire
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             const long long m = m0 + q * 32 + lane;
@@ -456,8 +458,7 @@ cudaError_t launch3(const CUtensorMap &ma, const CUtensorMap &mb, long long m, l
         configured = true;
     }
     static const int chunk = [] { const char *e = getenv("VOLTA_B200_TC_CHUNK"); int v = e ? atoi(e) : DEFAULT_CHUNK; return v < 2 ? 2 : (v > 16 ? 16 : v); }();
-    gemm_tc3_kernel<AK, BKM><<<2 * tiles_m * tiles_n, THREADS, SMEM_BYTES, s>>>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, chunk);
-    return cudaGetLastError();
+    return launch_pdl(gemm_tc3_kernel<AK, BKM>, dim3(2 * tiles_m * tiles_n), dim3(THREADS), SMEM_BYTES, s, ma, mb, m, n, k, tiles_m, tiles_n, epi, status, chunk);
 }
 
 }  // namespace
