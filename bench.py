@@ -44,12 +44,12 @@ def measured_peaks():
 
 
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per batch row of one launch, from
-# the ncu capture summarised in profiles/gemm_tc_c4_batch8192.md (taken at batch 8192; traffic of
-# these GEMMs grows in proportion to the batch, so a full launch is rows x this figure).
+# the ncu capture summarised in profiles/gemm_tc3_pair_c4_batch8192.md (taken at batch 8192; traffic
+# of these GEMMs grows in proportion to the batch, so a full launch is rows x this figure).
 NCU_TRAFFIC_PER_ROW = {
-    "fwd_gemm_nn_Bx4096x4096": (742.602496e6 + 247.932672e6) / 8192,
-    "fwd_gemm_nn_Bx1024x4096": (203.244288e6 + 44.418816e6) / 8192,
-    "dW_gemm_tn_4096x1024xB": (233.943040e6 + 14.075648e6) / 8192,
+    "fwd_gemm_nn_Bx4096x4096": (688.751872e6 + 297.116416e6) / 8192,
+    "fwd_gemm_nn_Bx1024x4096": (210.639872e6 + 50.569216e6) / 8192,
+    "dW_gemm_tn_4096x1024xB": (168.156160e6 + 5.256448e6) / 8192,
 }
 
 

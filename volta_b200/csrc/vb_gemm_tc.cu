@@ -473,7 +473,11 @@ cudaError_t launch_gemm_tc(int layout, const float *A, const float *B, long long
     // Kernel generations: 3 = CTA-pair kernel for outputs of at least 256 x 256 (default), 2 = single-CTA
     // kernel with in-place high parts (all other shapes), 1 = the first kernel (kept for comparison).
     static const int version = env_int("VOLTA_B200_TC_VERSION", 3);
-    if ((version == 3 || g_force_pair) && m >= 256 && n >= 256) return launch_gemm_tc3(layout, A, B, m, n, k, epi, status, s);
+    // the pair kernel needs enough pair tiles to put a CTA on every SM, otherwise the single-CTA
+    // kernel's smaller tiles spread the work better
+    const long long pair_ctas = 2 * ((m + 255) / 256) * ((n + 255) / 256);
+    if (m >= 256 && n >= 256 && (g_force_pair || (version == 3 && pair_ctas >= 148)))
+        return launch_gemm_tc3(layout, A, B, m, n, k, epi, status, s);
     if (version >= 2) return launch_gemm_tc2(layout, A, B, m, n, k, epi, status, s);
     const bool a_kmajor = (layout != GEMM_TN), b_kmajor = (layout == GEMM_NT);
     CUtensorMap ma, mb;
