@@ -185,6 +185,9 @@ def main():
     ap.add_argument("--gemm-path", default="auto", choices=["auto", "ffma", "tensor", "tensor_pair"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-workloads", action="store_true")
+    ap.add_argument("--dp-mode", default="nccl", choices=["nccl", "fused"],
+                    help="gradient exchange under data parallelism: bucketed NCCL all-reduce + optimizer, or the fused "
+                         "peer-memory reduce + update kernels")
     ap.add_argument("--batch", type=int, default=None,
                     help="override the workload's global batch (for small profiler captures; not a headline number)")
     args = ap.parse_args()
@@ -203,7 +206,7 @@ def main():
     workload_desc = {"workload": "%s: MLP %s, %s, MSE, %s lr=%g, fp32, global batch %d" % (
         cfg.name, "->".join(map(str, cfg.layers)), cfg.activation, cfg.optimizer, cfg.lr, cfg.batch),
         "global_batch": cfg.batch, "x_dist": cfg.x_dist, "y_dist": cfg.y_dist,
-        "weights": "Kaiming-uniform, seed 42", "parallelism": "dp%d" % world, "note": cfg.note}
+        "weights": "Kaiming-uniform, seed 42", "parallelism": "dp%d" % world, "dp_mode": args.dp_mode if world > 1 else None, "note": cfg.note}
 
     if args.impl == "reference":
         if rank != 0:
@@ -238,6 +241,10 @@ def main():
 
     h = TrainHandle(layers, cfg.activation, cfg.optimizer, B, global_batch=cfg.batch, world_size=world, rank=rank,
                     unique_id=uid, gemm_path=args.gemm_path, fuse_sgd=(cfg.optimizer == "sgd" and world == 1))
+    if world > 1 and args.dp_mode == "fused":
+        handles = [None] * world
+        dist.all_gather_object(handles, h.ipc_handle())
+        h.attach_peers(handles)
     ws, bs = synth.kaiming_uniform_weights(layers, 42)
     for i, (w, b) in enumerate(zip(ws, bs)):
         h.set_params(i, w, b)

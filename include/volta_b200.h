@@ -157,6 +157,17 @@ int volta_b200_profile_step(vb200_handle *h, const float *X, const float *Y, flo
  * rank's config (any host transport).  Uses NCCL, loaded at run time. */
 int volta_b200_dp_unique_id(uint8_t out[128]);
 
+/* Fused data parallelism over peer memory (no counterpart in the reference).  After every rank has
+ * created its handle (same configuration, world_size > 1), each exports the 64-byte IPC handle of its
+ * arena; all ranks exchange them (any host transport) and attach the full list, ordered by rank.  From
+ * then on a step no longer calls NCCL: per layer, one kernel per rank sums its share of every rank's
+ * gradients with peer loads in rank order, applies the optimizer to that share and stores the new
+ * parameters into every rank's arena; flag words in the arenas order the ranks, with bounded waits.
+ * Needs peer access between the GPUs (NVLink); at most 8 ranks; optimizer state becomes sharded
+ * (save_state is refused). */
+int volta_b200_dp_ipc_handle(vb200_handle *h, uint8_t out[64]);
+int volta_b200_dp_attach_peers(vb200_handle *h, const uint8_t *handles, int32_t count);
+
 /* Stand-alone kernel entry points on device pointers (used by parity tests to check
  * single kernels against the oracle; `stream` is a cudaStream_t or NULL). */
 int volta_b200_optimizer_apply(int32_t optimizer, float *p, float *s1, float *s2, const float *g, int64_t n,

@@ -54,7 +54,7 @@ def oracle_shard_worker(rank, world, port, opt, real, out_dir):
     dist.destroy_process_group()
 
 
-def gpu_shard_worker(rank, world, port, opt, out_dir, repeat):
+def gpu_shard_worker(rank, world, port, opt, out_dir, repeat, fused=False):
     """One GPU rank: libvolta_b200 handle on its row shard; the unique id travels over gloo."""
     import torch
     import torch.distributed as dist
@@ -70,6 +70,10 @@ def gpu_shard_worker(rank, world, port, opt, out_dir, repeat):
         box = [dp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         h = TrainHandle(LAYERS, "silu", opt, B, global_batch=GLOBAL_BATCH, world_size=world, rank=rank, unique_id=box[0])
+        if fused:
+            handles = [None] * world
+            dist.all_gather_object(handles, h.ipc_handle())
+            h.attach_peers(handles)
         for i, (w, b) in enumerate(zip(ws, bs)):
             h.set_params(i, w, b)
         losses = []

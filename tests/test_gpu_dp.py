@@ -46,12 +46,39 @@ def test_data_parallel_path_on_a_single_rank_matches_the_plain_path():
         assert np.array_equal(a, b)
 
 
+@pytest.mark.parametrize("opt", ["adam", "sgd_momentum"])
+def test_fused_peer_memory_update_on_a_single_rank_matches_the_plain_path(opt):
+    """The fused reduce + update + redistribute kernels and their flag barriers with one rank (its
+    own arena as the only peer): a sum over one rank adds nothing, so the bits must equal the plain
+    handle's."""
+    from volta_b200 import TrainHandle
+    from volta_b200.train import dp_unique_id
+    x, y, ws, bs = dpc.inputs()
+    outs = []
+    for fused in (False, True):
+        h = TrainHandle(dpc.LAYERS, "silu", opt, dpc.GLOBAL_BATCH, force_dp=fused, unique_id=dp_unique_id() if fused else None)
+        if fused:
+            h.attach_peers([h.ipc_handle()])
+        for i, (w, b) in enumerate(zip(ws, bs)):
+            h.set_params(i, w, b)
+        losses = []
+        for _ in range(dpc.STEPS):
+            h.step(x, y, 0.01)
+            losses.append(np.float32(h.loss()))
+        outs.append((losses, sum(h.get_params(), [])))
+        h.free()
+    assert outs[0][0] == outs[1][0]
+    for a, b in zip(outs[0][1], outs[1][1]):
+        assert np.array_equal(a, b)
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("mode", ["nccl", "fused"])
 @pytest.mark.parametrize("opt", ["sgd_momentum", "adam"])
-def test_two_gpu_ranks_match_the_full_batch_oracle(opt):
+def test_two_gpu_ranks_match_the_full_batch_oracle(opt, mode):
     world = 2
     out = tempfile.mkdtemp()
-    mp.spawn(dpc.gpu_shard_worker, args=(world, _free_port(), opt, out, 2), nprocs=world, join=True)
+    mp.spawn(dpc.gpu_shard_worker, args=(world, _free_port(), opt, out, 2, mode == "fused"), nprocs=world, join=True)
     x, y, ws, bs = dpc.inputs()
     o = Oracle(dpc.LAYERS, "silu", opt, dpc.GLOBAL_BATCH)
     for i, (w, b) in enumerate(zip(ws, bs)):

@@ -181,7 +181,8 @@ struct StepScalars {
     float weight_decay;
     float momentum;
     float inv_unused;
-    unsigned int pad[7];
+    unsigned int epoch;   // step counter, the same on every data-parallel rank (orders the peer barriers)
+    unsigned int pad[6];
 };
 
 // ---------------------------------------------------------------------------------------
@@ -209,6 +210,24 @@ bool gemm_tc_supported(int layout, const float *A, const float *B, long long m, 
 cudaError_t launch_optimizer(int optimizer, float *p, float *s1, float *s2, const float *g, long long n,
                              long long n_decay, const StepScalars *sc, cudaStream_t s);
 cudaError_t launch_set_scalars(StepScalars *dst, StepScalars v, cudaStream_t s);
+
+// ---- fused data-parallel update over peer memory (vb_dp_fused.cu)
+constexpr int kMaxPeers = 8;
+struct PeerTable {
+    char *base[kMaxPeers];   // every rank's arena, mapped into this process (own arena at [rank])
+};
+// One barrier among the ranks: write `*epoch * stride + index` into slot `rank` of every peer's flag
+// array, then wait (bounded) until all of this rank's slots have reached it.
+cudaError_t launch_dp_barrier(const PeerTable &peers, long long flags_off, int world, int rank,
+                              const StepScalars *scalars, unsigned stride, unsigned index, unsigned int *status,
+                              cudaStream_t s);
+// For the floats [seg_begin, seg_begin + seg_len) of the flat layout: this rank sums its 1/world share
+// of every rank's gradients in rank order, applies the optimizer to its share of the parameters, and
+// writes the new parameters into every rank's arena.
+cudaError_t launch_dp_reduce_update(int optimizer, const PeerTable &peers, long long params_off, long long grads_off,
+                                    long long s1_off, long long s2_off, long long seg_begin, long long seg_len,
+                                    long long n_decay, int world, int rank, const StepScalars *scalars,
+                                    long long loss_off, cudaStream_t s);
 
 long long colsum_chunks(long long rows, long long cols);
 // out[j] = sum_rows in[row, j] * (row_weight ? row_weight[row] : 1), fixed order

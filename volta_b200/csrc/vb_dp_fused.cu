@@ -1,0 +1,136 @@
+// Data-parallel gradient exchange fused with the optimizer, over peer memory (NVLink P2P).
+//
+// The NCCL path all-reduces every gradient bucket and then every rank runs the same optimizer over
+// all parameters.  Here the collective and the update are ONE kernel per bucket: rank r owns the
+// r-th share of the bucket; it reads that share of every rank's gradient buffer with plain 128-bit
+// peer loads, adds them in rank order 0..N-1 (so the sum is the same bits on every run), applies the
+// optimizer to its share (only the owner keeps optimizer state for it), and stores the new
+// parameters into every rank's arena (reduce-scatter + update + all-gather).  Optimizer traffic per
+// GPU drops by the rank count; gradients cross NVLink once and parameters once.
+//
+// Ordering between ranks uses flag words in each arena: before a bucket's kernel every rank announces
+// "my backward for this layer is done" and waits for all others (so nobody's weights are overwritten
+// while it still reads them, and every gradient is final); one more barrier at the end of the step
+// makes all updates visible before the next forward.  Waits are bounded (~4 s): on expiry a status
+// bit is set and the kernel carries on, so a missing rank never hangs the GPU.
+// The reference has no collective of any kind; parity target is the full-batch CPU oracle.
+#include "vb_common.cuh"
+#include "vb_optimizer.cuh"
+
+namespace vb {
+namespace {
+
+constexpr unsigned ST_DP_BARRIER = 64u;
+
+__device__ __forceinline__ unsigned long long dp_global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__global__ void dp_barrier_kernel(PeerTable peers, long long flags_off, int world, int rank,
+                                  const StepScalars *__restrict__ scalars, unsigned stride, unsigned index,
+                                  unsigned int *status) {
+    pdl_wait();
+    const int t = threadIdx.x;
+    if (t >= world) return;
+    const unsigned value = scalars->epoch * stride + index;
+    __threadfence_system();   // everything this GPU wrote before the barrier is visible to its peers
+    volatile unsigned *theirs = reinterpret_cast<volatile unsigned *>(peers.base[t] + flags_off) + rank;
+    *theirs = value;
+    volatile unsigned *mine = reinterpret_cast<volatile unsigned *>(peers.base[rank] + flags_off) + t;
+    unsigned long long t0 = 0;
+    for (unsigned it = 0;; ++it) {
+        if ((int)(*mine - value) >= 0) break;
+        if ((it & 1023u) == 1023u) {
+            unsigned long long now = dp_global_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > 4000000000ull) {
+                atomicOr(status, ST_DP_BARRIER);
+                break;
+            }
+        }
+    }
+    __threadfence_system();
+}
+
+template <int OPT>
+__global__ void __launch_bounds__(256) dp_reduce_update_kernel(PeerTable peers, long long params_off, long long grads_off,
+                                                               long long s1_off, long long s2_off, long long seg_begin,
+                                                               long long seg_len, long long n_decay, int world, int rank,
+                                                               const StepScalars *__restrict__ scp, long long loss_off) {
+    pdl_wait();
+    const StepScalars sc = *scp;
+    constexpr bool HAS1 = (OPT != VB200_OPT_SGD);
+    constexpr bool HAS2 = (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW);
+    // this rank's share of the segment, in float4 units (segments are multiples of 64 floats)
+    const long long seg4 = seg_len >> 2;
+    const long long per = (seg4 + world - 1) / world;
+    const long long lo = rank * per, hi = (lo + per < seg4) ? (lo + per) : seg4;
+    float4 *my_p = reinterpret_cast<float4 *>(peers.base[rank] + params_off) + (seg_begin >> 2);
+    float4 *my_s1 = reinterpret_cast<float4 *>(peers.base[rank] + s1_off) + (seg_begin >> 2);
+    float4 *my_s2 = reinterpret_cast<float4 *>(peers.base[rank] + s2_off) + (seg_begin >> 2);
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += stride) {
+        float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int q = 0; q < world; ++q) {   // fixed rank order
+            const float4 v = __ldcv(reinterpret_cast<const float4 *>(peers.base[q] + grads_off) + (seg_begin >> 2) + i);
+            g.x += v.x; g.y += v.y; g.z += v.z; g.w += v.w;
+        }
+        float4 pv = my_p[i];
+        float4 a = HAS1 ? my_s1[i] : make_float4(0, 0, 0, 0);
+        float4 b = HAS2 ? my_s2[i] : make_float4(0, 0, 0, 0);
+        const long long e = seg_begin + (i << 2);
+        const float wd0 = (OPT == VB200_OPT_ADAMW && e + 0 < n_decay) ? sc.weight_decay : 0.0f;
+        const float wd1 = (OPT == VB200_OPT_ADAMW && e + 1 < n_decay) ? sc.weight_decay : 0.0f;
+        const float wd2 = (OPT == VB200_OPT_ADAMW && e + 2 < n_decay) ? sc.weight_decay : 0.0f;
+        const float wd3 = (OPT == VB200_OPT_ADAMW && e + 3 < n_decay) ? sc.weight_decay : 0.0f;
+        update_one<OPT>(pv.x, a.x, b.x, g.x, sc, wd0);
+        update_one<OPT>(pv.y, a.y, b.y, g.y, sc, wd1);
+        update_one<OPT>(pv.z, a.z, b.z, g.z, sc, wd2);
+        update_one<OPT>(pv.w, a.w, b.w, g.w, sc, wd3);
+        if (HAS1) my_s1[i] = a;
+        if (HAS2) my_s2[i] = b;
+        for (int q = 0; q < world; ++q)   // all-gather: the new parameters land in every rank's arena
+            reinterpret_cast<float4 *>(peers.base[q] + params_off)[(seg_begin >> 2) + i] = pv;
+    }
+    // the loss travels with the last bucket: every rank adds all ranks' partial sums in rank order
+    if (loss_off >= 0 && blockIdx.x == 0 && threadIdx.x == 0) {
+        float total = 0.0f;
+        for (int q = 0; q < world; ++q) total += *reinterpret_cast<volatile const float *>(peers.base[q] + loss_off);
+        reinterpret_cast<float *>(peers.base[rank] + loss_off)[1] = total;
+    }
+    __threadfence_system();
+}
+
+}  // namespace
+
+cudaError_t launch_dp_barrier(const PeerTable &peers, long long flags_off, int world, int rank,
+                              const StepScalars *scalars, unsigned stride, unsigned index, unsigned int *status,
+                              cudaStream_t s) {
+    return launch_pdl(dp_barrier_kernel, dim3(1), dim3(32), 0, s, peers, flags_off, world, rank, scalars, stride, index, status);
+}
+
+cudaError_t launch_dp_reduce_update(int optimizer, const PeerTable &peers, long long params_off, long long grads_off,
+                                    long long s1_off, long long s2_off, long long seg_begin, long long seg_len,
+                                    long long n_decay, int world, int rank, const StepScalars *scalars,
+                                    long long loss_off, cudaStream_t s) {
+    if (seg_len <= 0 || (seg_len & 3) || (seg_begin & 3)) return cudaErrorInvalidValue;
+    const long long per = ((seg_len >> 2) + world - 1) / world;
+    long long want = (per + 255) / 256;
+    int blocks = (int)(want < 1 ? 1 : (want > 148 * 4 ? 148 * 4 : want));
+#define VB_DP_LAUNCH(O)                                                                                              \
+    return launch_pdl(dp_reduce_update_kernel<O>, dim3(blocks), dim3(256), 0, s, peers, params_off, grads_off, s1_off, \
+                      s2_off, seg_begin, seg_len, n_decay, world, rank, scalars, loss_off)
+    switch (optimizer) {
+    case VB200_OPT_SGD: VB_DP_LAUNCH(VB200_OPT_SGD);
+    case VB200_OPT_ADAM: VB_DP_LAUNCH(VB200_OPT_ADAM);
+    case VB200_OPT_ADAMW: VB_DP_LAUNCH(VB200_OPT_ADAMW);
+    case VB200_OPT_ADAGRAD: VB_DP_LAUNCH(VB200_OPT_ADAGRAD);
+    case VB200_OPT_SGD_MOMENTUM: VB_DP_LAUNCH(VB200_OPT_SGD_MOMENTUM);
+    }
+#undef VB_DP_LAUNCH
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace vb

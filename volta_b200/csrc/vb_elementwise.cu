@@ -2,6 +2,7 @@
 // column reduction and the MSE loss + seed gradient.  All reductions use a fixed order and no
 // atomics, so a step is bit-identical from run to run.
 #include "vb_common.cuh"
+#include "vb_optimizer.cuh"
 
 namespace vb {
 
@@ -20,32 +21,6 @@ namespace vb {
 // Weight decay applies to the first n_decay elements only (the weights; biases follow
 // them in the flat layout), as the generated step decays weights but not biases (:962-966).
 // ---------------------------------------------------------------------------------------
-template <int OPT>
-__device__ __forceinline__ void update_one(float &p, float &s1, float &s2, float g, const StepScalars &sc, float wd) {
-    if (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW) {
-        float one_m_b1 = __fsub_rn(1.0f, sc.beta1), one_m_b2 = __fsub_rn(1.0f, sc.beta2);
-        float m1 = __fadd_rn(__fmul_rn(sc.beta1, s1), __fmul_rn(one_m_b1, g));
-        float v1 = __fadd_rn(__fmul_rn(sc.beta2, s2), __fmul_rn(one_m_b2, __fmul_rn(g, g)));
-        s1 = m1;
-        s2 = v1;
-        float mhat = __fdiv_rn(m1, sc.bc1);
-        float vhat = __fdiv_rn(v1, sc.bc2);
-        float denom = __fadd_rn(__fsqrt_rn(vhat), sc.eps);
-        float step = __fmul_rn(sc.lr, __fadd_rn(__fdiv_rn(mhat, denom), __fmul_rn(wd, p)));
-        p = __fsub_rn(p, step);
-    } else if (OPT == VB200_OPT_ADAGRAD) {
-        float G = __fadd_rn(s1, __fmul_rn(g, g));
-        s1 = G;
-        p = __fsub_rn(p, __fdiv_rn(__fmul_rn(sc.lr, g), __fadd_rn(__fsqrt_rn(G), sc.eps)));
-    } else if (OPT == VB200_OPT_SGD_MOMENTUM) {
-        float v = __fadd_rn(__fmul_rn(sc.momentum, s1), g);
-        s1 = v;
-        p = __fsub_rn(p, __fmul_rn(sc.lr, v));
-    } else {
-        p = __fsub_rn(p, __fmul_rn(sc.lr, g));
-    }
-}
-
 template <int OPT>
 __global__ void __launch_bounds__(256) optimizer_kernel(float *__restrict__ p, float *__restrict__ s1,
                                                         float *__restrict__ s2, const float *__restrict__ g,

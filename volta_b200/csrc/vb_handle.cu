@@ -82,6 +82,11 @@ struct vb200_handle {
     int kernels_per_step = 0;
 
     DpComm *dp = nullptr;
+    // fused data parallelism over peer memory (after volta_b200_dp_attach_peers)
+    bool dp_fused = false;
+    PeerTable peers{};
+    std::vector<void *> peer_mappings;   // cudaIpcOpenMemHandle results to close
+    long long off_params = 0, off_grads = 0, off_s1 = 0, off_s2 = 0, off_flags = 0, off_loss = 0;  // bytes in the arena
 
     // profiling (plain launches with an event pair per kernel)
     bool profiling = false;
@@ -257,7 +262,7 @@ int enqueue_step(vb200_handle *h, int slot) {
             Scope sc(h, nm, 2.0 * B * r * c, 4.0 * (B * r + B * c + (fused ? 2.0 : 1.0) * r * c));
             VB_CUDA(h, run_gemm(h, GEMM_TN, A(i), h->delta[i], r, c, B, e));
         }
-        if (h->dp) {
+        if (h->dp && !h->dp_fused) {
             // bucket i = dW_i: reduce on the side stream while the main stream goes on
             VB_CUDA(h, cudaEventRecord(h->ev_bucket[i], s));
             VB_CUDA(h, cudaStreamWaitEvent(h->comm_stream, h->ev_bucket[i], 0));
@@ -274,8 +279,36 @@ int enqueue_step(vb200_handle *h, int slot) {
             int rc = do_dx();
             if (rc) return rc;
         }
+        if (h->dp_fused) {
+            // bucket i over peer memory, on the side stream: once EVERY rank is past dX_i (nobody reads
+            // W_i any more, every dW_i is final) reduce + update + redistribute W_i in one kernel
+            VB_CUDA(h, cudaEventRecord(h->ev_bucket[i], s));
+            VB_CUDA(h, cudaStreamWaitEvent(h->comm_stream, h->ev_bucket[i], 0));
+            h->kernels_per_step += 2;
+            VB_CUDA(h, launch_dp_barrier(h->peers, h->off_flags, h->world, h->rank, h->scalars, (unsigned)(n + 2),
+                                         (unsigned)(n - i), h->status_word, h->comm_stream));
+            VB_CUDA(h, launch_dp_reduce_update(h->cfg.optimizer, h->peers, h->off_params, h->off_grads, h->off_s1, h->off_s2,
+                                               h->off_w[i], pad64(r * c), h->n_weights_padded, h->world, h->rank,
+                                               h->scalars, -1, h->comm_stream));
+        }
     }
-    if (h->dp) {
+    if (h->dp_fused) {
+        // last bucket: all biases, and the loss; then one barrier so that every update has landed
+        // everywhere before the step ends
+        VB_CUDA(h, cudaEventRecord(h->ev_bucket[n], s));
+        VB_CUDA(h, cudaStreamWaitEvent(h->comm_stream, h->ev_bucket[n], 0));
+        h->kernels_per_step += 3;
+        VB_CUDA(h, launch_dp_barrier(h->peers, h->off_flags, h->world, h->rank, h->scalars, (unsigned)(n + 2),
+                                     (unsigned)(n + 1), h->status_word, h->comm_stream));
+        VB_CUDA(h, launch_dp_reduce_update(h->cfg.optimizer, h->peers, h->off_params, h->off_grads, h->off_s1, h->off_s2,
+                                           h->n_weights_padded, h->n_params_padded - h->n_weights_padded,
+                                           h->n_weights_padded, h->world, h->rank, h->scalars, h->off_loss, h->comm_stream));
+        VB_CUDA(h, launch_dp_barrier(h->peers, h->off_flags, h->world, h->rank, h->scalars, (unsigned)(n + 2),
+                                     (unsigned)(n + 2), h->status_word, h->comm_stream));
+        VB_CUDA(h, cudaEventRecord(h->ev_join, h->comm_stream));
+        VB_CUDA(h, cudaStreamWaitEvent(s, h->ev_join, 0));
+    }
+    if (h->dp && !h->dp_fused) {
         // last bucket: every bias gradient plus the loss sum, contiguous behind the weights
         VB_CUDA(h, cudaEventRecord(h->ev_bucket[n], s));
         VB_CUDA(h, cudaStreamWaitEvent(h->comm_stream, h->ev_bucket[n], 0));
@@ -289,7 +322,9 @@ int enqueue_step(vb200_handle *h, int slot) {
     {
         const int opt = h->cfg.optimizer;
         double bpp = opt == VB200_OPT_SGD ? 12.0 : (opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW) ? 28.0 : 20.0;
-        if (h->fuse_sgd) {
+        if (h->dp_fused) {
+            // every parameter was updated by its owner rank inside the bucket kernels
+        } else if (h->fuse_sgd) {
             // weights of every layer wider than one were updated by their dW GEMM; the rest follows here
             for (int i = 0; i < n; ++i)
                 if (L[i + 1] == 1) {
@@ -307,7 +342,8 @@ int enqueue_step(vb200_handle *h, int slot) {
                                         h->scalars, s));
         }
     }
-    VB_CUDA(h, cudaMemcpyAsync(&h->host_loss[slot], h->loss_sum, sizeof(float), cudaMemcpyDeviceToHost, s));
+    VB_CUDA(h, cudaMemcpyAsync(&h->host_loss[slot], h->dp_fused ? h->loss_sum + 1 : h->loss_sum, sizeof(float),
+                               cudaMemcpyDeviceToHost, s));
     VB_CUDA(h, cudaMemcpyAsync(h->host_status, h->status_word, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
     return VB200_OK;
 }
@@ -343,6 +379,7 @@ StepScalars make_scalars(vb200_handle *h, float lr) {
     float t = (float)h->adam_step;
     sc.bc1 = 1.0f - powf(sc.beta1, t);
     sc.bc2 = 1.0f - powf(sc.beta2, t);
+    sc.epoch = (unsigned int)(h->steps_done + 1);
     return sc;
 }
 
@@ -426,6 +463,7 @@ void destroy(vb200_handle *h) {
     }
     if (h->ev_join) cudaEventDestroy(h->ev_join);
     for (auto e : h->ev_bucket) cudaEventDestroy(e);
+    for (void *m : h->peer_mappings) cudaIpcCloseMemHandle(m);
     if (h->arena) cudaFree(h->arena);
     if (h->mirror_params) cudaFreeHost(h->mirror_params);
     if (h->mirror_grads) cudaFreeHost(h->mirror_grads);
@@ -563,6 +601,13 @@ int build(vb200_handle *h) {
     h->mse_scratch = at(i_mse);
     h->colsum_scratch = at(i_cs);
     h->gemm_scratch = at(ix.gs);
+    h->off_params = pl.offset(i_params);
+    h->off_grads = pl.offset(i_grads);
+    h->off_s1 = pl.offset(i_s1);
+    h->off_s2 = pl.offset(i_s2);
+    h->off_flags = pl.offset(i_sc) + 768;   // 8 barrier words behind the scalars (offset 0) and the status word (512)
+    h->off_loss = h->off_grads + P * 4;
+
     for (int s = 0; s < 2; ++s) { h->xin[s] = at(i_x[s]); h->yin[s] = at(i_y[s]); }
     h->act.assign(n + 1, nullptr);
     h->pre.assign(n, nullptr);
@@ -722,6 +767,7 @@ int64_t volta_b200_state_floats(vb200_handle *h) {
 
 int volta_b200_save_state(vb200_handle *h, float *out, int64_t n, uint64_t *step_out) {
     if (!h) return VB200_ERR_INVALID;
+    if (h->dp_fused) return h->reject(VB200_ERR_UNSUPPORTED, "save_state: optimizer state is sharded over the ranks in fused data-parallel mode");
     const int64_t need = volta_b200_state_floats(h);
     if (n < need || (need && !out)) return h->reject(VB200_ERR_INVALID, "save_state: buffer too small");
     VB_CUDA(h, cudaStreamSynchronize(h->stream));
@@ -860,6 +906,48 @@ int volta_b200_infer(vb200_handle *h, const float *in, int64_t in_n, float *out,
     VB_CUDA(h, cudaMemcpyAsync(out, h->act[h->n], (size_t)out_n * 4, odev ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, h->stream));
     VB_CUDA(h, cudaStreamSynchronize(h->stream));
     return check_device_status(h);
+}
+
+int volta_b200_dp_ipc_handle(vb200_handle *h, uint8_t out[64]) {
+    if (!h || !out) return VB200_ERR_INVALID;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t ipc;
+    VB_CUDA(h, cudaIpcGetMemHandle(&ipc, h->arena));
+    memcpy(out, &ipc, 64);
+    return VB200_OK;
+}
+
+int volta_b200_dp_attach_peers(vb200_handle *h, const uint8_t *handles, int32_t count) {
+    if (!h) return VB200_ERR_INVALID;
+    if (!h->dp) return h->reject(VB200_ERR_INVALID, "attach_peers: the handle was not created for data parallelism");
+    if (count != h->world || count > kMaxPeers || !handles)
+        return h->reject(VB200_ERR_INVALID, "attach_peers: need one 64-byte handle per rank (at most 8 ranks)");
+    if (h->dp_fused) return h->reject(VB200_ERR_INVALID, "attach_peers: already attached");
+    VB_CUDA(h, cudaStreamSynchronize(h->stream));
+    for (int q = 0; q < count; ++q) {
+        if (q == h->rank) {
+            h->peers.base[q] = h->arena;
+            continue;
+        }
+        cudaIpcMemHandle_t ipc;
+        memcpy(&ipc, handles + 64 * q, 64);
+        void *p = nullptr;
+        VB_CUDA(h, cudaIpcOpenMemHandle(&p, ipc, cudaIpcMemLazyEnablePeerAccess));
+        h->peer_mappings.push_back(p);
+        h->peers.base[q] = static_cast<char *>(p);
+    }
+    // from now on the step graph uses the peer-memory buckets instead of NCCL + the flat optimizer
+    for (int sl = 0; sl < 2; ++sl)
+        if (h->graph[sl]) {
+            cudaGraphExecDestroy(h->graph[sl]);
+            h->graph[sl] = nullptr;
+        }
+    h->dp_fused = true;
+    if (h->use_graph) {
+        int rc = capture_graphs(h);
+        if (rc) return rc;
+    }
+    return VB200_OK;
 }
 
 int volta_b200_dp_unique_id(uint8_t out[128]) { return DpComm::unique_id(out) ? VB200_ERR_NCCL : VB200_OK; }

@@ -34,7 +34,7 @@ EXPORTS = [
     "volta_b200_get_params", "volta_b200_infer", "volta_b200_get_grads", "volta_b200_state_floats", "volta_b200_save_state",
     "volta_b200_load_state", "volta_b200_status", "volta_b200_last_error", "volta_b200_stream",
     "volta_b200_synchronize", "volta_b200_arena_bytes", "volta_b200_plan", "volta_b200_kernels_per_step",
-    "volta_b200_profile_step", "volta_b200_dp_unique_id", "volta_b200_optimizer_apply", "volta_b200_gemm",
+    "volta_b200_profile_step", "volta_b200_dp_unique_id", "volta_b200_dp_ipc_handle", "volta_b200_dp_attach_peers", "volta_b200_optimizer_apply", "volta_b200_gemm",
     "volta_b200_colsum_scratch_floats", "volta_b200_colsum", "volta_b200_colsum_noalloc", "volta_b200_version",
 ]
 
@@ -78,6 +78,8 @@ def load_library():
         "volta_b200_plan": (C.c_int, [C.POINTER(Config), C.POINTER(i64), C.POINTER(i64), C.c_char_p, i64]),
         "volta_b200_profile_step": (C.c_int, [vp, vp, vp, C.c_float, C.POINTER(KernelRecord), i32]),
         "volta_b200_dp_unique_id": (C.c_int, [C.POINTER(C.c_uint8 * 128)]),
+        "volta_b200_dp_ipc_handle": (C.c_int, [vp, C.POINTER(C.c_uint8 * 64)]),
+        "volta_b200_dp_attach_peers": (C.c_int, [vp, C.c_char_p, i32]),
         "volta_b200_optimizer_apply": (C.c_int, [i32, vp, vp, vp, vp, i64, i64, C.c_float, C.c_float, C.c_float,
                                                  C.c_uint64, vp]),
         "volta_b200_gemm": (C.c_int, [i32, i32, vp, vp, vp, i64, i64, i64, vp]),

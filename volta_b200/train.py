@@ -188,6 +188,17 @@ class TrainHandle:
                     buf[base + ob[i]: base + ob[i] + bs[i].size] = np.asarray(bs[i], np.float32).ravel()
         self.load_state(buf[:n], step)
 
+    def ipc_handle(self) -> bytes:
+        """64-byte handle of this rank's arena, to be exchanged among the data-parallel ranks."""
+        buf = (C.c_uint8 * 64)()
+        self._check(self.lib.volta_b200_dp_ipc_handle(self.h, C.byref(buf)))
+        return bytes(buf)
+
+    def attach_peers(self, handles):
+        """Switch to the fused peer-memory gradient exchange; `handles` lists every rank's ipc_handle() by rank."""
+        blob = b"".join(handles)
+        self._check(self.lib.volta_b200_dp_attach_peers(self.h, blob, len(handles)))
+
     def synchronize(self):
         self._check(self.lib.volta_b200_synchronize(self.h))
 
