@@ -10,7 +10,7 @@ import numpy as np
 
 from . import build as _build
 
-ACTIVATIONS = {"relu": 0, "sigmoid": 1, "tanh": 2, "leaky_relu": 3, "silu": 4, "gelu": 5}
+ACTIVATIONS = {"relu": 0, "sigmoid": 1, "tanh": 2, "leaky_relu": 3, "silu": 4, "gelu": 5, "softmax": 6}
 OPTIMIZERS = {"sgd": 0, "adam": 1, "adamw": 2, "adagrad": 3, "sgd_momentum": 4}
 
 _libs: dict = {}
@@ -33,6 +33,9 @@ def _lib(real: str):
         lib.oracle_get_adam_step.restype = C.c_uint64
         lib.oracle_get_adam_step.argtypes = [C.c_void_p]
         lib.oracle_set_adam_step.argtypes = [C.c_void_p, C.c_uint64]
+        lib.oracle_set_options.argtypes = [C.c_void_p, C.c_double, C.c_int, C.c_double]
+        lib.oracle_get_ln.restype = rp
+        lib.oracle_get_ln.argtypes = [C.c_void_p, C.c_int, C.c_int]
         lib.oracle_set_gemm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         lib.oracle_set_params.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float)]
         lib.oracle_get_params.argtypes = [C.c_void_p, C.POINTER(rp), C.POINTER(rp)]
@@ -59,7 +62,8 @@ class Oracle:
     """One training handle of the oracle; mirrors volta_train_init/_step/_loss/_get_params/
     _set_params/_free of the reference's generated library."""
 
-    def __init__(self, layers, activation="relu", optimizer="sgd", batch=1, real="f32", momentum=0.9):
+    def __init__(self, layers, activation="relu", optimizer="sgd", batch=1, real="f32", momentum=0.9, dropout_p=0.0,
+                 use_layernorm=False, clip_grad=0.0):
         self.layers = [int(x) for x in layers]
         self.n = len(self.layers) - 1
         self.batch = int(batch)
@@ -72,6 +76,8 @@ class Oracle:
         if not self.h:
             raise ValueError("oracle_create rejected the topology")
         self.lib.oracle_set_momentum(self.h, float(momentum))
+        if dropout_p or use_layernorm or clip_grad:
+            self.lib.oracle_set_options(self.h, float(dropout_p), int(bool(use_layernorm)), float(clip_grad))
         self._shim = None
 
     def use_reference_gemm(self) -> str | None:
@@ -164,6 +170,11 @@ class Oracle:
                 lst.append(np.ctypeslib.as_array(a[i], shape=shape).copy() if a[i] else None)
             out.append(lst)
         return out[0], out[1], out[2], out[3], int(self.lib.oracle_get_adam_step(self.h))
+
+    def get_layernorm(self, i: int):
+        """(gamma, beta) of the LayerNorm behind hidden layer i."""
+        c = self.layers[i + 1]
+        return tuple(np.ctypeslib.as_array(self.lib.oracle_get_ln(self.h, i, w), shape=(c,)).copy() for w in (0, 1))
 
     def loss(self) -> float:
         return float(self.lib.oracle_loss(self.h))

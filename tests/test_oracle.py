@@ -251,3 +251,117 @@ def test_adam_first_step_is_ill_conditioned_in_the_oracle_too():
         if bad.any():
             assert np.max(np.abs(gb[bad])) < 1e-5 * np.max(np.abs(gb))
     assert 0 < n_bad < 200
+
+
+# ---- template options that no benchmark configuration uses (mlp_train_rust_codegen.rs:727-788, 829-955)
+def _run_torch_mlp(layers, act_fn, x, y, ws, bs, lr, steps, opt="sgd", post=None, extra_params=()):
+    tw = [torch.tensor(w, dtype=torch.float64, requires_grad=True) for w in ws]
+    tb = [torch.tensor(b, dtype=torch.float64, requires_grad=True) for b in bs]
+    params = tw + tb + list(extra_params)
+    topt = torch.optim.SGD(params, lr=lr) if opt == "sgd" else torch.optim.Adam(params, lr=lr, betas=(0.9, 0.999), eps=1e-8)
+    tx, ty = torch.tensor(x, dtype=torch.float64), torch.tensor(y, dtype=torch.float64)
+    losses = []
+    for s in range(steps):
+        h = tx
+        for i in range(len(tw)):
+            h = h @ tw[i] + tb[i]
+            if i < len(tw) - 1:
+                h = act_fn(h)
+                if post is not None:
+                    h = post(h, i, s)
+        loss = torch.mean((h - ty) ** 2)
+        topt.zero_grad()
+        loss.backward()
+        topt.step()
+        losses.append(float(loss.detach()))
+    return losses, tw, tb
+
+
+@pytest.mark.parametrize("opt", ["sgd", "adam"])
+def test_softmax_hidden_activation_matches_torch(opt):
+    rs = np.random.RandomState(2)
+    layers, B, steps, lr = [6, 9, 8, 3], 5, 4, 0.05
+    x, y = rs.randn(B, 6).astype(np.float32), rs.randn(B, 3).astype(np.float32)
+    o = Oracle(layers, "softmax", opt, B, real="f64")
+    ws, bs = o.get_params()
+    losses, tw, tb = _run_torch_mlp(layers, lambda t: torch.softmax(t, dim=1), x, y, ws, bs, lr, steps, opt)
+    for s in range(steps):
+        o.step(x, y, lr)
+        assert abs(o.loss() - losses[s]) < 1e-8
+    for a, b in zip(o.get_params()[0], tw):
+        np.testing.assert_allclose(a, b.detach().numpy(), rtol=1e-6, atol=1e-8)
+
+
+def test_layernorm_after_the_activation_matches_torch():
+    """relu -> LayerNorm (biased variance, eps 1e-5, gamma/beta updated by plain SGD with the step's lr)."""
+    rs = np.random.RandomState(4)
+    layers, B, steps, lr = [6, 10, 7, 2], 6, 4, 0.05
+    x, y = rs.randn(B, 6).astype(np.float32), rs.randn(B, 2).astype(np.float32)
+    o = Oracle(layers, "relu", "sgd", B, real="f64", use_layernorm=True)
+    ws, bs = o.get_params()
+    g = [torch.ones(c, dtype=torch.float64, requires_grad=True) for c in layers[1:-1]]
+    be = [torch.zeros(c, dtype=torch.float64, requires_grad=True) for c in layers[1:-1]]
+    post = lambda h, i, s: torch.nn.functional.layer_norm(h, (h.shape[1],), g[i], be[i], 1e-5)
+    losses, tw, tb = _run_torch_mlp(layers, torch.relu, x, y, ws, bs, lr, steps, "sgd", post, g + be)
+    for s in range(steps):
+        o.step(x, y, lr)
+        assert abs(o.loss() - losses[s]) < 1e-7
+    for a, b in zip(o.get_params()[0], tw):
+        np.testing.assert_allclose(a, b.detach().numpy(), rtol=1e-6, atol=1e-7)
+    for i in range(len(g)):
+        og, ob = o.get_layernorm(i)
+        np.testing.assert_allclose(og, g[i].detach().numpy(), rtol=1e-6, atol=1e-8)
+        np.testing.assert_allclose(ob, be[i].detach().numpy(), rtol=1e-6, atol=1e-8)
+
+
+def test_dropout_uses_the_reference_lcg_mask_stream():
+    """Inverted dropout with the mask stream of mlp_train_rust_codegen.rs:773-788 restated in Python
+    integers: one LCG seeded 12345678, advanced once per hidden activation element, layer after layer,
+    step after step; keep when (rng >> 33) / 2^31 >= p.  relu, because for tanh/sigmoid the template
+    differentiates through the dropped activation value (:855-868) and is then no true gradient."""
+    rs = np.random.RandomState(6)
+    layers, B, steps, lr, p = [5, 12, 9, 2], 4, 3, 0.05, 0.25
+    x, y = rs.randn(B, 5).astype(np.float32), rs.randn(B, 2).astype(np.float32)
+    o = Oracle(layers, "relu", "sgd", B, real="f64", dropout_p=p)
+    ws, bs = o.get_params()
+    state = {"rng": 12345678}
+    scale = float(np.float32(1.0 / (1.0 - p)))
+
+    def post(h, i, s):
+        n = h.numel()
+        keep = np.empty(n, dtype=np.float64)
+        for k in range(n):
+            state["rng"] = (state["rng"] * 6364136223846793005 + 1442695040888963407) & ((1 << 64) - 1)
+            r = np.float32(state["rng"] >> 33) / np.float32(2147483648.0)
+            keep[k] = 1.0 if r >= np.float32(p) else 0.0
+        return h * torch.tensor(keep.reshape(h.shape) * scale)
+
+    losses, tw, tb = _run_torch_mlp(layers, torch.relu, x, y, ws, bs, lr, steps, "sgd", post)
+    for s in range(steps):
+        o.step(x, y, lr)
+        assert abs(o.loss() - losses[s]) < 1e-7
+    for a, b in zip(o.get_params()[0], tw):
+        np.testing.assert_allclose(a, b.detach().numpy(), rtol=1e-6, atol=1e-7)
+
+
+def test_clip_scales_the_deltas_not_the_bias_gradients():
+    """The template's "clip by global norm" (:936-955) scales the deltas after the bias gradients were
+    summed: dW shrinks by clip/norm(deltas), db does not."""
+    rs = np.random.RandomState(8)
+    layers, B = [7, 11, 6, 2], 5
+    x, y = rs.randn(B, 7).astype(np.float32), (3 * rs.randn(B, 2)).astype(np.float32)
+    a = Oracle(layers, "relu", "sgd", B, real="f64")
+    a.grad_step(x, y)
+    norm = np.sqrt(sum(float(np.sum(a.get_delta(i) ** 2)) for i in range(3)))
+    clip = 0.5 * norm
+    b = Oracle(layers, "relu", "sgd", B, real="f64", clip_grad=clip)
+    b.grad_step(x, y)
+    (aw, ab), (bw, bb) = a.get_grads(), b.get_grads()
+    for u, v in zip(aw, bw):
+        np.testing.assert_allclose(v, u * 0.5, rtol=1e-6)
+    for u, v in zip(ab, bb):
+        np.testing.assert_allclose(v, u, rtol=1e-12)
+    c = Oracle(layers, "relu", "sgd", B, real="f64", clip_grad=10 * norm)   # above the norm: untouched
+    c.grad_step(x, y)
+    for u, v in zip(aw, c.get_grads()[0]):
+        assert np.array_equal(u, v)
