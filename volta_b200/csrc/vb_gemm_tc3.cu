@@ -461,7 +461,7 @@ cudaError_t launch3(const CUtensorMap &ma, const CUtensorMap &mb, long long m, l
     }
     static const int chunk = [] { const char *e = getenv("VOLTA_B200_TC_CHUNK"); int v = e ? atoi(e) : DEFAULT_CHUNK; return v < 2 ? 2 : (v > 16 ? 16 : v); }();
     static const int raw_stages = [] { const char *e = getenv("VOLTA_B200_TC_RAW_STAGES"); int v = e ? atoi(e) : DEFAULT_RAW_STAGES; return v < 2 ? 2 : (v > 4 ? 4 : v); }();
-    return launch_pdl(gemm_tc3_kernel<AK, BKM>, dim3(2 * tiles_m * tiles_n), dim3(THREADS), SMEM_BYTES, s, ma, mb, m, n, k, tiles_m, tiles_n, epi, status, chunk);
+    return launch_pdl(gemm_tc3_kernel<AK, BKM>, dim3(2 * tiles_m * tiles_n), dim3(THREADS), SMEM_BYTES, s, ma, mb, m, n, k, tiles_m, tiles_n, epi, status, chunk, raw_stages);
 }
 
 }  // namespace
