@@ -28,9 +28,10 @@ extern "C" {
 
 #define VB200_MAX_LAYERS 32
 
-/* Hidden-layer activation (MlpTopology::activation, mlp_train_rust_codegen.rs:268-275). */
+/* Hidden-layer activation (MlpTopology::activation, mlp_train_rust_codegen.rs:268-275).
+ * SOFTMAX is the row-wise softmax over each hidden layer's outputs (:727-740, backward :898-906). */
 enum { VB200_ACT_RELU = 0, VB200_ACT_SIGMOID = 1, VB200_ACT_TANH = 2, VB200_ACT_LEAKY_RELU = 3,
-       VB200_ACT_SILU = 4, VB200_ACT_GELU = 5 };
+       VB200_ACT_SILU = 4, VB200_ACT_GELU = 5, VB200_ACT_SOFTMAX = 6 };
 
 /* Optimizer (MlpTopology::optimizer, mlp_train_rust_codegen.rs:263-267).  SGD with
  * momentum has no counterpart in the reference; it is an extension. */
@@ -67,11 +68,24 @@ typedef struct vb200_config {
     float weight_decay;                /* AdamW; 0 = 0.01 */
     int32_t gemm_path;                 /* VB200_GEMM_* */
     int32_t use_graph;                 /* 0 = default (captured CUDA graph), 1 = graph, 2 = plain launches */
-    int32_t reserved[8];               /* reserved[0] = 1: build the data-parallel path (communicator, bucketed
-                                          all-reduce) even for world_size 1, so it can be exercised on one GPU;
-                                          reserved[1] = 1: plain SGD on one GPU folds the update into the dW GEMM
-                                          epilogue (the reference's sgd_fused_tn); gradients of those layers are
-                                          then never materialised and volta_b200_get_grads does not return them */
+    int32_t force_dp;                  /* 1: build the data-parallel path (communicator, bucketed all-reduce)
+                                          even for world_size 1, so it can be exercised on one GPU */
+    int32_t fuse_sgd;                  /* 1: plain SGD on one GPU folds the update into the dW GEMM epilogue (the
+                                          reference's sgd_fused_tn); gradients of those layers are then never
+                                          materialised and volta_b200_get_grads does not return them */
+    /* MlpTopology's remaining switches (mlp_train_rust_codegen.rs:34-38), all off when zero.  Every hidden
+     * layer's output goes through activation -> LayerNorm -> dropout, in that order (:725-788). */
+    int32_t use_layernorm;             /* 1: LayerNorm over each hidden row (biased variance, eps 1e-5, gamma 1 /
+                                          beta 0 at start), whose gamma/beta take a plain SGD step with the
+                                          step's lr whatever the optimizer is (:744-772, 829-887) */
+    float dropout_p;                   /* in (0,1): inverted dropout; the keep mask is the reference's LCG stream
+                                          (seed 12345678, one draw per hidden element in layer, row, column order,
+                                          keep when (state >> 33) / 2^31 >= p; :773-788).  Data-parallel ranks
+                                          draw the slice of that stream that belongs to their rows */
+    float clip_grad;                   /* > 0: the template's "clip": when the norm over ALL deltas exceeds this,
+                                          the deltas are scaled by clip/norm after the bias gradients were taken,
+                                          so dW shrinks and db does not (:936-955) */
+    int32_t reserved[3];
 } vb200_config;
 
 typedef struct vb200_handle vb200_handle;
@@ -112,9 +126,18 @@ int volta_b200_get_params(vb200_handle *h, float **wo, float **bo);
  * `in` and `out` may be host or device pointers; out_n must equal rows * Ln.  Call between steps. */
 int volta_b200_infer(vb200_handle *h, const float *in, int64_t in_n, float *out, int64_t out_n);
 
+/* LayerNorm scale and shift of hidden layer li (0 <= li < n-1), c = layers[li+1] floats each, host
+ * pointers.  The reference keeps them inside the handle with no accessor (Handle fields ln_g/ln_b,
+ * mlp_train_rust_codegen.rs:505-523); a checkpoint needs them.  Refused when use_layernorm is off. */
+int volta_b200_get_layernorm(vb200_handle *h, int32_t li, float *gamma, float *beta);
+int volta_b200_set_layernorm(vb200_handle *h, int32_t li, const float *gamma, const float *beta);
+
 /* Test/diagnostic extensions (no counterpart in the reference): gradients of the
  * last step (same mirror convention), optimizer-state export/import for checkpoints
- * (the reference cannot export Adam moments, :670-684), and the Adam step counter. */
+ * (the reference cannot export Adam moments, :670-684), and the Adam step counter.
+ * The state is volta_b200_state_floats floats: first moments, second moments (as the
+ * optimizer has them), then - with dropout on - two floats that carry the 64 raw bits of
+ * the mask stream's position (copy them, do not do arithmetic on them). */
 int volta_b200_get_grads(vb200_handle *h, float **dwo, float **dbo);
 int64_t volta_b200_state_floats(vb200_handle *h);
 int volta_b200_save_state(vb200_handle *h, float *out, int64_t n, uint64_t *step_out);

@@ -78,6 +78,44 @@ def test_memory_plan_reuses_temporaries_and_fits_one_gpu():
     assert total8 < total
 
 
+def _check_no_live_overlap(total, bufs):
+    for i, a in enumerate(bufs):
+        assert a[1] % 1024 == 0 and a[1] + a[2] <= total
+        for b in bufs[i + 1:]:
+            if a[5] or b[5] or (a[3] <= b[4] and b[3] <= a[4]):
+                assert a[1] + a[2] <= b[1] or b[1] + b[2] <= a[1], (a, b)
+
+
+def test_memory_plan_with_the_optional_stages():
+    """Dropout masks (one byte per hidden element), the LayerNorm parameters and 1/sigma rows, and
+    pre-activations for relu once the stored output is no longer the activation's own; the clip keeps
+    every activation and delta alive until the dW sweep at the end of the step."""
+    c = _cfg(CONFIGS["c2"])
+    n, B, L = c.n_sizes - 1, c.batch, list(c.layers[:c.n_sizes])
+    base_total, _, base = _plan(c)
+    assert not any(b[0].startswith(("pre", "mask", "ln_", "layernorm")) for b in base)
+    c.dropout_p, c.use_layernorm = 0.5, 1
+    total, _, bufs = _plan(c)
+    _check_no_live_overlap(total, bufs)
+    by = {b[0]: b for b in bufs}
+    for k in range(n - 1):
+        assert by["mask%d" % k][2] == B * L[k + 1] and by["pre%d" % k][2] == 4 * B * L[k + 1]
+        assert 4 * B <= by["ln_invstd%d" % k][2] <= 4 * B + 1023
+        # alive from the layer's forward position to the backward position of its own delta
+        assert by["mask%d" % k][3] == k and by["mask%d" % k][4] == n + 1 + (n - 1 - k)
+        assert by["act%d" % (k + 1)][4] == by["mask%d" % k][4]
+    assert by["layernorm_params"][5] == 1 and by["layernorm_params"][2] >= 4 * 2 * sum(L[1:n])
+    assert total > base_total
+    c.clip_grad = 1.0
+    total_clip, _, bufs = _plan(c)
+    _check_no_live_overlap(total_clip, bufs)
+    end = 2 * n + 1
+    assert all(b[4] == end for b in bufs if b[0].startswith("delta") or (b[0].startswith("act") and b[0] != "act%d" % n))
+    assert total_clip >= total
+    c.dropout_p = 1.0
+    assert load_library().volta_b200_plan(C.byref(c), None, None, None, 0) == 1
+
+
 def test_plan_rejects_bad_configs():
     lib = load_library()
     c = _cfg(CONFIGS["c1"])
@@ -131,4 +169,19 @@ def test_codegen_rejects_what_the_reference_rejects(tmp_path):
     with pytest.raises(codegen.CodegenError, match="need >= 2 layer sizes"):
         codegen.compile_model([4], "relu", "sgd", str(tmp_path / "b.so"))
     with pytest.raises(codegen.CodegenError, match="does not support activation"):
-        codegen.compile_model([4, 4, 1], "softmax", "sgd", str(tmp_path / "c.so"))
+        codegen.compile_model([4, 4, 1], "mish", "sgd", str(tmp_path / "c.so"))
+    with pytest.raises(codegen.CodegenError, match="--dropout must lie"):
+        codegen.compile_model([4, 4, 1], "relu", "sgd", str(tmp_path / "d.so"), dropout_p=1.5)
+
+
+def test_codegen_compiles_the_topology_switches_in(tmp_path):
+    """MlpTopology's dropout_p / use_layernorm / clip_grad (mlp_train_rust_codegen.rs:34-38) and the
+    softmax activation end up in the emitted init function."""
+    from volta_b200 import codegen
+    out = codegen.compile_model([8, 16, 4], "softmax", "sgd", str(tmp_path / "o.so"), emit_only=True,
+                                dropout_p=0.25, use_layernorm=True, clip_grad=1.5)
+    src = open(out).read()
+    assert "cfg.activation = 6;" in src and "cfg.use_layernorm = 1;" in src
+    assert "cfg.dropout_p = (float)0.25;" in src and "cfg.clip_grad = (float)1.5;" in src
+    plain = open(codegen.compile_model([8, 16, 4], "relu", "sgd", str(tmp_path / "p.so"), emit_only=True)).read()
+    assert "cfg.use_layernorm = 0;" in plain and "cfg.dropout_p = (float)0;" in plain

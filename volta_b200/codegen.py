@@ -28,11 +28,18 @@ def build_tool(force: bool = False) -> str:
     return TOOL
 
 
-def compile_model(layers, activation: str, optimizer: str, out_path: str, emit_only: bool = False) -> str:
+def compile_model(layers, activation: str, optimizer: str, out_path: str, emit_only: bool = False, *,
+                  dropout_p: float = 0.0, use_layernorm: bool = False, clip_grad: float = 0.0) -> str:
     """Emit (and link) the training library for one model; returns the path produced."""
     tool = build_tool()
     cmd = [tool, "--layers", ",".join(str(int(x)) for x in layers), "--activation", activation, "--optimizer",
            optimizer, "-o", out_path, "--libdir", HERE, "--include", INCLUDE]
+    if dropout_p:
+        cmd += ["--dropout", repr(float(dropout_p))]
+    if use_layernorm:
+        cmd.append("--layernorm")
+    if clip_grad:
+        cmd += ["--clip-grad", repr(float(clip_grad))]
     if emit_only:
         cmd.append("--emit-only")
     r = subprocess.run(cmd, capture_output=True, text=True)

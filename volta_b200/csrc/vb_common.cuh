@@ -182,8 +182,25 @@ struct StepScalars {
     float momentum;
     float inv_unused;
     unsigned int epoch;   // step counter, the same on every data-parallel rank (orders the peer barriers)
-    unsigned int pad[6];
+    unsigned long long rng_base;  // dropout: state of the mask stream before this step's first draw
+    unsigned int pad[4];
 };
+static_assert(sizeof(StepScalars) == 64, "StepScalars is one 64-byte record");
+
+// The dropout mask stream (mlp_train_rust_codegen.rs:773-788): a 64-bit LCG, one draw per element.
+constexpr unsigned long long kLcgA = 6364136223846793005ULL, kLcgC = 1442695040888963407ULL;
+// State after n more draws.  The map s -> a*s + c composed with itself is s -> a*a*s + (a+1)*c, so the
+// draws are applied by the binary digits of n.
+__host__ __device__ inline unsigned long long lcg_jump(unsigned long long s, unsigned long long n) {
+    unsigned long long a = kLcgA, c = kLcgC;
+    while (n) {
+        if (n & 1ULL) s = s * a + c;
+        c = (a + 1ULL) * c;
+        a = a * a;
+        n >>= 1;
+    }
+    return s;
+}
 
 // ---------------------------------------------------------------------------------------
 // Kernel launchers (defined in the .cu files of this directory).
@@ -236,6 +253,38 @@ cudaError_t launch_colsum(float *out, const float *in, long long rows, long long
 // out[row] = in[row, :] . w + bias[0]
 cudaError_t launch_rowdot(float *out, const float *in, const float *w, const float *bias, long long rows,
                           long long cols, cudaStream_t s);
+
+// ---- row-wise kernels of the optional stages (vb_options.cu)
+struct RowFwd {
+    int softmax;                 // 1: x holds bias-added pre-activations and leaves as their row softmax
+    const float *ln_g, *ln_b;    // LayerNorm scale/shift [cols], or null
+    float *ln_is;                // [rows] 1/sqrt(var + eps) kept for backward
+    float dropout_p;             // 0 = no dropout
+    unsigned char *mask;         // [rows x cols] keep flags kept for backward
+    unsigned long long draw_off; // draws of this step that precede row 0 of this call
+};
+struct RowBwd {
+    int act;                     // VB200_ACT_*
+    const float *a1;             // the layer's stored output (after every stage) [rows x cols]
+    const float *saved;          // what act_backward takes (pre-activation or a1); unused for softmax
+    const float *ln_g, *ln_b, *ln_is;  // or null
+    float dropout_p;
+    const unsigned char *mask;
+};
+// Largest hidden width the row kernels take (one row is staged in shared memory).
+constexpr int kRowMaxCols = 51200;
+cudaError_t launch_row_forward(float *x, long long rows, int cols, const RowFwd &o, const StepScalars *sc, cudaStream_t s);
+cudaError_t launch_row_backward(float *delta, long long rows, int cols, const RowBwd &o, cudaStream_t s);
+// out[0..cols) = sum_rows dout*xhat, out[cols..2cols) = sum_rows dout, xhat rebuilt from a1 as the
+// reference does; scratch holds colsum_chunks(rows, cols) * 2 * cols floats
+cudaError_t launch_ln_param_grads(float *out, const float *dout, const float *a1, const float *g, const float *b,
+                                  long long rows, int cols, float *scratch, cudaStream_t s);
+// partial[0..loss_blocks(n)) = fixed-order block sums of v*v
+cudaError_t launch_sumsq_partials(float *partial, const float *v, long long n, cudaStream_t s);
+// *out = sum of partial[0..nblocks) in a fixed order
+cudaError_t launch_sum_partials(float *out, const float *partial, long long nblocks, cudaStream_t s);
+// v *= clip/sqrt(*norm_sq) when sqrt(*norm_sq) > clip, else untouched
+cudaError_t launch_clip_scale(float *v, long long n, const float *norm_sq, float clip, cudaStream_t s);
 
 long long loss_blocks(long long nt);
 // delta[k] = 2*(out[k]-y[k])/nt_global ; *loss_sum = sum_k (out[k]-y[k])^2 (fixed order)

@@ -64,6 +64,21 @@ struct vb200_handle {
     float *xin[2] = {nullptr, nullptr}, *yin[2] = {nullptr, nullptr};
     std::vector<float *> act, pre, delta;  // act[0] unused (slot dependent)
 
+    // optional stages (softmax hidden activation, LayerNorm, dropout, clip); all off in the benchmark configurations
+    bool row_opts = false;       // any stage that needs the row kernels
+    bool keep_pre = false;       // backward takes the pre-activation from its own buffer
+    bool layernorm = false;
+    float dropout_p = 0.0f, clip = 0.0f;
+    int64_t ln_floats = 0;                   // all gamma/beta blocks, each [gamma(c) | beta(c)] padded to 64 floats
+    std::vector<int64_t> off_ln;             // per hidden layer, in floats
+    float *ln_params = nullptr, *ln_grads = nullptr, *clip_norm = nullptr;
+    std::vector<float *> ln_is;              // per hidden layer [batch]
+    std::vector<unsigned char *> mask;       // per hidden layer [batch x c]
+    unsigned long long dropout_rng = 12345678ULL;   // mask stream position before the next step (:612, 773)
+    unsigned long long draws_per_step = 0;
+    std::vector<unsigned long long> draw_off;       // draws of a step that precede this rank's rows of layer k
+    cudaEvent_t ev_clip[2] = {nullptr, nullptr};
+
     // host side
     float *mirror_params = nullptr, *mirror_grads = nullptr;  // pinned
     float *host_loss = nullptr;                               // pinned, one float per slot
@@ -121,6 +136,18 @@ int pos_fwd(int i) { return i; }
 int pos_loss(int n) { return n; }
 int pos_bwd(int n, int i) { return n + 1 + (n - 1 - i); }
 
+bool cfg_row_opts(const vb200_config &c) {
+    return c.activation == VB200_ACT_SOFTMAX || c.use_layernorm == 1 || c.dropout_p > 0.0f;
+}
+// Backward needs the pre-activation in a buffer of its own: always for silu/gelu; for relu/leaky
+// once LayerNorm or dropout change the stored output, whose sign then no longer tells pre > 0.
+// Sigmoid/tanh (and softmax) differentiate through the stored output in the reference (:898-912).
+bool cfg_keep_pre(const vb200_config &c) {
+    if (act_needs_pre(c.activation)) return true;
+    const bool changed = c.use_layernorm == 1 || c.dropout_p > 0.0f;
+    return changed && (c.activation == VB200_ACT_RELU || c.activation == VB200_ACT_LEAKY_RELU);
+}
+
 // The reference's LCG-Xavier stream (mlp_train_rust_codegen.rs:630-638, 653-658).
 void lcg_xavier(float *w, int64_t n, int r, int c, uint64_t *rng) {
     float lim = sqrtf(6.0f / ((float)r + (float)c));
@@ -166,7 +193,7 @@ cudaError_t run_gemm(vb200_handle *h, int layout, const float *A, const float *B
 
 // Forward pass over the first `rows` rows of input slot `slot` (rows <= batch): every layer's GEMM
 // with bias and activation fused.  Used by the training step (rows = batch) and by inference.
-int enqueue_forward(vb200_handle *h, int slot, long long rows) {
+int enqueue_forward(vb200_handle *h, int slot, long long rows, bool training) {
     const int n = h->n, act = h->cfg.activation;
     const long long B = rows;
     const std::vector<int> &L = h->L;
@@ -183,10 +210,13 @@ int enqueue_forward(vb200_handle *h, int slot, long long rows) {
         if (i == n - 1) {
             e.mode = EPI_BIAS;
             e.out0 = h->act[n];
+        } else if (act == VB200_ACT_SOFTMAX) {
+            e.mode = EPI_BIAS;  // the row kernel below turns the pre-activations into their softmax in place
+            e.out0 = h->act[i + 1];
         } else {
             e.mode = EPI_BIAS_ACT;
             e.out0 = h->act[i + 1];
-            e.out1 = act_needs_pre(act) ? h->pre[i] : nullptr;
+            e.out1 = h->keep_pre ? h->pre[i] : nullptr;
         }
         if (i == n - 1 && c == 1) {
             // width-one output layer: a row-dot, bandwidth-bound on act_i
@@ -198,6 +228,24 @@ int enqueue_forward(vb200_handle *h, int slot, long long rows) {
         snprintf(nm, sizeof nm, "fwd%d_gemm_nn_%lldx%lldx%lld", i, B, c, r);
         Scope sc(h, nm, 2.0 * B * r * c, 4.0 * (B * r + r * c + B * c * (e.out1 ? 2 : 1)));
         VB_CUDA(h, run_gemm(h, GEMM_NN, A(i), h->params + h->off_w[i], B, c, r, e));
+        const bool drop = training && h->dropout_p > 0.0f;
+        if (i < n - 1 && (act == VB200_ACT_SOFTMAX || h->layernorm || drop)) {
+            RowFwd o{};
+            o.softmax = act == VB200_ACT_SOFTMAX;
+            if (h->layernorm) {
+                o.ln_g = h->ln_params + h->off_ln[i];
+                o.ln_b = o.ln_g + c;
+                o.ln_is = h->ln_is[i];
+            }
+            if (drop) {
+                o.dropout_p = h->dropout_p;
+                o.mask = h->mask[i];
+                o.draw_off = h->draw_off[i];
+            }
+            snprintf(nm, sizeof nm, "fwd%d_rows_%lldx%lld", i, B, c);
+            Scope sc(h, nm, 0.0, (8.0 + (drop ? 1.0 : 0.0)) * B * c);
+            VB_CUDA(h, launch_row_forward(h->act[i + 1], B, (int)c, o, h->scalars, s));
+        }
     }
     return VB200_OK;
 }
@@ -213,7 +261,7 @@ int enqueue_step(vb200_handle *h, int slot) {
     char nm[64];
 
     {
-        int rc = enqueue_forward(h, slot, B);
+        int rc = enqueue_forward(h, slot, B, true);
         if (rc) return rc;
     }
     // loss + seed gradient
@@ -225,27 +273,57 @@ int enqueue_step(vb200_handle *h, int slot) {
                                    h->mse_scratch, s));
     }
     // backward.  Per layer: dW_i, db_i, then dX_i -> delta_{i-1}.  With the SGD update folded into
-    // the dW epilogue, dX_i (which must read the pre-update W_i) goes first.
-    for (int i = n - 1; i >= 0; --i) {
-        const long long r = L[i], c = L[i + 1];
-        auto do_dx = [&]() -> int {
-            if (i == 0) return VB200_OK;
-            Epilogue e{};
-            e.mode = EPI_DACT;
-            e.act = act;
-            e.out0 = h->delta[i - 1];
-            e.saved = act_needs_pre(act) ? h->pre[i - 1] : h->act[i];
-            e.ld = r;
-            snprintf(nm, sizeof nm, "dX%d_gemm_nt_%lldx%lldx%lld", i, (long long)B, r, c);
-            Scope sc(h, nm, 2.0 * B * r * c, 4.0 * (B * c + r * c + 2.0 * B * r));
-            VB_CUDA(h, run_gemm(h, GEMM_NT, h->delta[i], h->params + h->off_w[i], B, r, c, e));
-            return VB200_OK;
-        };
-        const bool fused = h->fuse_sgd && c != 1;
-        if (fused) {
-            int rc = do_dx();
-            if (rc) return rc;
+    // the dW epilogue, dX_i (which must read the pre-update W_i) goes first.  With the clip every
+    // delta must exist before any dW is taken (:936-955), so the dW GEMMs form a second sweep.
+    const bool two_sweeps = h->clip > 0.0f;
+    // LayerNorm backward -> dropout mask -> activation backward on the raw delta of hidden layer i
+    auto do_rows = [&](int i) -> int {
+        if (!h->row_opts || i == n - 1) return VB200_OK;
+        const long long c = L[i + 1];
+        RowBwd o{};
+        o.act = act;
+        o.a1 = h->act[i + 1];
+        o.saved = h->keep_pre ? h->pre[i] : h->act[i + 1];
+        if (h->layernorm) {
+            o.ln_g = h->ln_params + h->off_ln[i];
+            o.ln_b = o.ln_g + c;
+            o.ln_is = h->ln_is[i];
+            snprintf(nm, sizeof nm, "ln%d_param_grads_%lldx%lld", i, (long long)B, c);
+            Scope sc(h, nm, 3.0 * B * c, 8.0 * B * c);
+            h->kernels_per_step++;
+            VB_CUDA(h, launch_ln_param_grads(h->ln_grads + h->off_ln[i], h->delta[i], h->act[i + 1], o.ln_g, o.ln_b, B,
+                                             (int)c, h->colsum_scratch, s));
         }
+        if (h->dropout_p > 0.0f) {
+            o.dropout_p = h->dropout_p;
+            o.mask = h->mask[i];
+        }
+        snprintf(nm, sizeof nm, "bwd%d_rows_%lldx%lld", i, (long long)B, c);
+        Scope sc(h, nm, 0.0, 16.0 * B * c);
+        VB_CUDA(h, launch_row_backward(h->delta[i], B, (int)c, o, s));
+        return VB200_OK;
+    };
+    auto do_dx = [&](int i) -> int {
+        if (i == 0) return VB200_OK;
+        const long long r = L[i], c = L[i + 1];
+        Epilogue e{};
+        e.act = act;
+        e.out0 = h->delta[i - 1];
+        e.ld = r;
+        if (h->row_opts) {
+            e.mode = EPI_STORE;  // do_rows(i - 1) finishes this delta
+        } else {
+            e.mode = EPI_DACT;
+            e.saved = h->keep_pre ? h->pre[i - 1] : h->act[i];
+        }
+        snprintf(nm, sizeof nm, "dX%d_gemm_nt_%lldx%lldx%lld", i, (long long)B, r, c);
+        Scope sc(h, nm, 2.0 * B * r * c, 4.0 * (B * c + r * c + 2.0 * B * r));
+        VB_CUDA(h, run_gemm(h, GEMM_NT, h->delta[i], h->params + h->off_w[i], B, r, c, e));
+        return VB200_OK;
+    };
+    auto do_dw = [&](int i) -> int {
+        const long long r = L[i], c = L[i + 1];
+        const bool fused = h->fuse_sgd && c != 1;
         if (c == 1) {
             // dW of a width-one layer: column sums of act_i weighted by delta_i[row]
             snprintf(nm, sizeof nm, "dW%d_wcolsum_%lldx%lld", i, (long long)B, r);
@@ -269,16 +347,34 @@ int enqueue_step(vb200_handle *h, int slot) {
             int rc = h->dp->all_reduce_sum(h->grads + h->off_w[i], pad64(r * c), h->comm_stream);
             if (rc) return h->fail(VB200_ERR_NCCL, h->dp->error());
         }
-        {
-            snprintf(nm, sizeof nm, "db%d_colsum_%lldx%lld", i, (long long)B, c);
-            Scope sc(h, nm, (double)B * c, 4.0 * (B * c + c));
-            h->kernels_per_step++;
-            VB_CUDA(h, launch_colsum(h->grads + h->off_b[i], h->delta[i], B, c, h->colsum_scratch, s));
+        return VB200_OK;
+    };
+    auto do_db = [&](int i) -> int {
+        const long long c = L[i + 1];
+        snprintf(nm, sizeof nm, "db%d_colsum_%lldx%lld", i, (long long)B, c);
+        Scope sc(h, nm, (double)B * c, 4.0 * (B * c + c));
+        h->kernels_per_step++;
+        VB_CUDA(h, launch_colsum(h->grads + h->off_b[i], h->delta[i], B, c, h->colsum_scratch, s));
+        return VB200_OK;
+    };
+#define VB_TRY(call)          \
+    do {                      \
+        int _rc = (call);     \
+        if (_rc) return _rc;  \
+    } while (0)
+    for (int i = n - 1; i >= 0; --i) {
+        const long long r = L[i], c = L[i + 1];
+        VB_TRY(do_rows(i));
+        if (two_sweeps) {
+            VB_TRY(do_db(i));
+            VB_TRY(do_dx(i));
+            continue;
         }
-        if (!fused) {
-            int rc = do_dx();
-            if (rc) return rc;
-        }
+        const bool fused = h->fuse_sgd && c != 1;
+        if (fused) VB_TRY(do_dx(i));
+        VB_TRY(do_dw(i));
+        VB_TRY(do_db(i));
+        if (!fused) VB_TRY(do_dx(i));
         if (h->dp_fused) {
             // bucket i over peer memory, on the side stream: once EVERY rank is past dX_i (nobody reads
             // W_i any more, every dW_i is final) reduce + update + redistribute W_i in one kernel
@@ -292,6 +388,36 @@ int enqueue_step(vb200_handle *h, int slot) {
                                                h->scalars, -1, h->comm_stream));
         }
     }
+    if (two_sweeps) {
+        // norm over every delta (all ranks' rows under data parallelism), then scale, then the dW sweep
+        long long nb = 0;
+        {
+            Scope sc(h, "clip_norm", 0.0, 0.0);
+            for (int i = 0; i < n; ++i) {
+                const long long cnt = (long long)B * L[i + 1];
+                h->kernels_per_step++;
+                VB_CUDA(h, launch_sumsq_partials(h->mse_scratch + nb, h->delta[i], cnt, s));
+                nb += loss_blocks(cnt);
+            }
+            VB_CUDA(h, launch_sum_partials(h->clip_norm, h->mse_scratch, nb, s));
+        }
+        if (h->dp) {
+            VB_CUDA(h, cudaEventRecord(h->ev_clip[0], s));
+            VB_CUDA(h, cudaStreamWaitEvent(h->comm_stream, h->ev_clip[0], 0));
+            int rc = h->dp->all_reduce_sum(h->clip_norm, 64, h->comm_stream);
+            if (rc) return h->fail(VB200_ERR_NCCL, h->dp->error());
+            VB_CUDA(h, cudaEventRecord(h->ev_clip[1], h->comm_stream));
+            VB_CUDA(h, cudaStreamWaitEvent(s, h->ev_clip[1], 0));
+        }
+        {
+            Scope sc(h, "clip_scale", 0.0, 0.0);
+            h->kernels_per_step += n - 1;
+            for (int i = 0; i < n; ++i)
+                VB_CUDA(h, launch_clip_scale(h->delta[i], (long long)B * L[i + 1], h->clip_norm, h->clip, s));
+        }
+        for (int i = n - 1; i >= 0; --i) VB_TRY(do_dw(i));
+    }
+#undef VB_TRY
     if (h->dp_fused) {
         // last bucket: all biases, and the loss; then one barrier so that every update has landed
         // everywhere before the step ends
@@ -312,7 +438,8 @@ int enqueue_step(vb200_handle *h, int slot) {
         // last bucket: every bias gradient plus the loss sum, contiguous behind the weights
         VB_CUDA(h, cudaEventRecord(h->ev_bucket[n], s));
         VB_CUDA(h, cudaStreamWaitEvent(h->comm_stream, h->ev_bucket[n], 0));
-        int64_t cnt = h->n_params_padded - h->n_weights_padded + 64;
+        // (and the LayerNorm gradients, which follow the loss slot)
+        int64_t cnt = h->n_params_padded - h->n_weights_padded + 64 + h->ln_floats;
         int rc = h->dp->all_reduce_sum(h->grads + h->n_weights_padded, cnt, h->comm_stream);
         if (rc) return h->fail(VB200_ERR_NCCL, h->dp->error());
         VB_CUDA(h, cudaEventRecord(h->ev_join, h->comm_stream));
@@ -339,6 +466,14 @@ int enqueue_step(vb200_handle *h, int slot) {
         } else {
             Scope sc(h, "optimizer", 0.0, bpp * h->n_params_padded);
             VB_CUDA(h, launch_optimizer(opt, h->params, h->s1, h->s2, h->grads, h->n_params_padded, h->n_weights_padded,
+                                        h->scalars, s));
+        }
+        if (h->layernorm) {
+            // gamma/beta always take a plain SGD step with this step's lr (:876-887).  The reference does it
+            // inside the backward sweep; nothing reads them again before the next forward, so it can wait
+            // for the (possibly all-reduced) gradients here.
+            Scope sc(h, "layernorm_sgd", 0.0, 12.0 * h->ln_floats);
+            VB_CUDA(h, launch_optimizer(VB200_OPT_SGD, h->ln_params, nullptr, nullptr, h->ln_grads, h->ln_floats, 0,
                                         h->scalars, s));
         }
     }
@@ -380,6 +515,7 @@ StepScalars make_scalars(vb200_handle *h, float lr) {
     sc.bc1 = 1.0f - powf(sc.beta1, t);
     sc.bc2 = 1.0f - powf(sc.beta2, t);
     sc.epoch = (unsigned int)(h->steps_done + 1);
+    sc.rng_base = h->dropout_rng;
     return sc;
 }
 
@@ -426,6 +562,7 @@ int do_step(vb200_handle *h, const float *X, const float *Y, float lr, bool prof
     VB_CUDA(h, cudaEventRecord(h->ev_slot_free[slot], h->stream));
     h->last_slot = slot;
     h->steps_done += 1;
+    if (h->draws_per_step) h->dropout_rng = lcg_jump(h->dropout_rng, h->draws_per_step);
     // X and Y are borrowed for the call only (mlp_train_rust_codegen.rs:704-707 copies X
     // before returning): wait until the device has taken them out of host memory.
     if (host_wait) VB_CUDA(h, cudaEventSynchronize(h->ev_copied[slot]));
@@ -462,6 +599,8 @@ void destroy(vb200_handle *h) {
         if (h->ev_slot_free[s]) cudaEventDestroy(h->ev_slot_free[s]);
     }
     if (h->ev_join) cudaEventDestroy(h->ev_join);
+    for (int q = 0; q < 2; ++q)
+        if (h->ev_clip[q]) cudaEventDestroy(h->ev_clip[q]);
     for (auto e : h->ev_bucket) cudaEventDestroy(e);
     for (void *m : h->peer_mappings) cudaIpcCloseMemHandle(m);
     if (h->arena) cudaFree(h->arena);
@@ -481,7 +620,13 @@ int validate(const vb200_config *c, std::string *why) {
     for (int i = 0; i < c->n_sizes; ++i)
         if (c->layers[i] <= 0) { *why = "layer widths must be positive"; return VB200_ERR_INVALID; }
     if (c->batch <= 0) { *why = "batch must be positive"; return VB200_ERR_INVALID; }
-    if (c->activation < VB200_ACT_RELU || c->activation > VB200_ACT_GELU) { *why = "unknown activation"; return VB200_ERR_UNSUPPORTED; }
+    if (c->activation < VB200_ACT_RELU || c->activation > VB200_ACT_SOFTMAX) { *why = "unknown activation"; return VB200_ERR_UNSUPPORTED; }
+    if (!(c->dropout_p >= 0.0f && c->dropout_p < 1.0f)) { *why = "dropout_p must lie in [0, 1)"; return VB200_ERR_INVALID; }
+    if (!(c->clip_grad >= 0.0f)) { *why = "clip_grad must not be negative"; return VB200_ERR_INVALID; }
+    if (c->use_layernorm != 0 && c->use_layernorm != 1) { *why = "use_layernorm must be 0 or 1"; return VB200_ERR_INVALID; }
+    if (cfg_row_opts(*c))
+        for (int i = 1; i < c->n_sizes - 1; ++i)
+            if (c->layers[i] > kRowMaxCols) { *why = "softmax, LayerNorm and dropout take hidden widths up to 51200"; return VB200_ERR_UNSUPPORTED; }
     if (c->optimizer < VB200_OPT_SGD || c->optimizer > VB200_OPT_SGD_MOMENTUM) { *why = "unknown optimizer"; return VB200_ERR_UNSUPPORTED; }
     int world = c->world_size > 1 ? c->world_size : 1;
     if (c->rank < 0 || c->rank >= world) { *why = "rank out of range"; return VB200_ERR_INVALID; }
@@ -491,8 +636,10 @@ int validate(const vb200_config *c, std::string *why) {
 }
 
 struct PlanIdx {
-    int params, grads, s1, s2, sc, mse, cs, gs, x[2], y[2];
-    std::vector<int> act, pre, delta;
+    int params, grads, s1, s2, sc, mse, cs, gs, x[2], y[2], ln = -1;
+    std::vector<int> act, pre, delta, ln_is, mask;
+    int64_t ln_floats = 0;
+    std::vector<int64_t> off_ln;
 };
 
 // Lay the step's buffers out on the fixed schedule (forward 0..n-1, loss n, backward
@@ -515,15 +662,29 @@ void make_plan(const vb200_config &c, ArenaPlan &pl, PlanIdx &ix, std::vector<in
     const int opt = c.optimizer;
     const bool has1 = opt != VB200_OPT_SGD, has2 = (opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW);
     const int end = 2 * n + 1;
+    const bool row_opts = cfg_row_opts(c), keep_pre = cfg_keep_pre(c), ln = c.use_layernorm == 1;
+    const bool drop = c.dropout_p > 0.0f, clip = c.clip_grad > 0.0f;
+    ix.off_ln.assign(n > 1 ? n - 1 : 0, 0);
+    ix.ln_floats = 0;
+    if (ln)
+        for (int k = 0; k + 1 < n; ++k) { ix.off_ln[k] = ix.ln_floats; ix.ln_floats += pad64(2LL * L[k + 1]); }
     ix.params = pl.add("params", P * 4, 0, end, true);
-    ix.grads = pl.add("grads+loss", (P + 64) * 4, 0, end, true);
+    // gradients, then the loss slot, then the LayerNorm gradients, then the clip's norm slot
+    ix.grads = pl.add("grads+loss", (P + 64 + ix.ln_floats + 64) * 4, 0, end, true);
+    if (ln) ix.ln = pl.add("layernorm_params", ix.ln_floats * 4, 0, end, true);
     ix.s1 = pl.add("opt_state1", has1 ? P * 4 : 4, 0, end, true);
     ix.s2 = pl.add("opt_state2", has2 ? P * 4 : 4, 0, end, true);
     ix.sc = pl.add("scalars+status", 1024, 0, end, true);
-    ix.mse = pl.add("mse_scratch", loss_blocks((long long)B * L[n]) * 4, 0, end, true);
+    long long mse = loss_blocks((long long)B * L[n]);
+    if (clip) {  // block partials of every delta's sum of squares
+        long long all = 0;
+        for (int i = 0; i < n; ++i) all += loss_blocks((long long)B * L[i + 1]);
+        mse = std::max(mse, all);
+    }
+    ix.mse = pl.add("mse_scratch", mse * 4, 0, end, true);
     long long cs = 0;
     for (int i = 0; i < n; ++i) {
-        cs = std::max(cs, colsum_chunks(B, L[i + 1]) * (long long)L[i + 1]);
+        cs = std::max(cs, colsum_chunks(B, L[i + 1]) * (long long)L[i + 1] * ((ln && i < n - 1) ? 2 : 1));
         if (L[i + 1] == 1) cs = std::max(cs, colsum_chunks(B, L[i]) * (long long)L[i]);  // weighted sums for dW
     }
     ix.cs = pl.add("colsum_scratch", cs * 4, 0, end, true);
@@ -542,15 +703,25 @@ void make_plan(const vb200_config &c, ArenaPlan &pl, PlanIdx &ix, std::vector<in
     ix.act.assign(n + 1, -1);
     ix.pre.assign(n, -1);
     ix.delta.assign(n, -1);
+    ix.ln_is.assign(n, -1);
+    ix.mask.assign(n, -1);
+    // Hidden layer k = i-1 writes act_i (and pre_k, mask_k, 1/sigma_k).  act_i is last read by dW_i;
+    // with the row stages also by the backward of delta_{i-1}, one position later.  The clip moves
+    // every dW behind the whole backward sweep, so activations and deltas then live to the end.
     for (int i = 1; i < n; ++i) {
-        ix.act[i] = pl.add("act" + std::to_string(i), (int64_t)B * L[i] * 4, pos_fwd(i - 1), pos_bwd(n, i), false);
-        if (act_needs_pre(c.activation))
-            ix.pre[i - 1] = pl.add("pre" + std::to_string(i - 1), (int64_t)B * L[i] * 4, pos_fwd(i - 1), pos_bwd(n, i), false);
+        const int bwd_rows = pos_bwd(n, i - 1);
+        const int act_last = clip ? end : (row_opts ? bwd_rows : pos_bwd(n, i));
+        ix.act[i] = pl.add("act" + std::to_string(i), (int64_t)B * L[i] * 4, pos_fwd(i - 1), act_last, false);
+        if (keep_pre)
+            ix.pre[i - 1] = pl.add("pre" + std::to_string(i - 1), (int64_t)B * L[i] * 4, pos_fwd(i - 1),
+                                   row_opts ? bwd_rows : pos_bwd(n, i), false);
+        if (drop) ix.mask[i - 1] = pl.add("mask" + std::to_string(i - 1), (int64_t)B * L[i], pos_fwd(i - 1), bwd_rows, false);
+        if (ln) ix.ln_is[i - 1] = pl.add("ln_invstd" + std::to_string(i - 1), (int64_t)B * 4, pos_fwd(i - 1), bwd_rows, false);
     }
     ix.act[n] = pl.add("act" + std::to_string(n), (int64_t)B * L[n] * 4, pos_fwd(n - 1), pos_loss(n), false);
     for (int i = n - 1; i >= 0; --i) {
         int first = (i == n - 1) ? pos_loss(n) : pos_bwd(n, i + 1);
-        ix.delta[i] = pl.add("delta" + std::to_string(i), (int64_t)B * L[i + 1] * 4, first, pos_bwd(n, i), false);
+        ix.delta[i] = pl.add("delta" + std::to_string(i), (int64_t)B * L[i + 1] * 4, first, clip ? end : pos_bwd(n, i), false);
     }
     pl.plan();
 }
@@ -566,7 +737,12 @@ int build(vb200_handle *h) {
     const long long gb = c.global_batch ? c.global_batch : (long long)c.batch * h->world;
     h->global_nt = gb * h->L[n];
     h->use_graph = c.use_graph != 2;
-    h->fuse_sgd = (c.reserved[1] == 1) && c.optimizer == VB200_OPT_SGD && h->world == 1 && c.reserved[0] != 1;
+    h->fuse_sgd = (c.fuse_sgd == 1) && c.optimizer == VB200_OPT_SGD && h->world == 1 && c.force_dp != 1;
+    h->row_opts = cfg_row_opts(c);
+    h->keep_pre = cfg_keep_pre(c);
+    h->layernorm = c.use_layernorm == 1;
+    h->dropout_p = c.dropout_p;
+    h->clip = c.clip_grad;
     const int B = h->B;
     const std::vector<int> &L = h->L;
 
@@ -594,6 +770,26 @@ int build(vb200_handle *h) {
     h->params = at(i_params);
     h->grads = at(i_grads);
     h->loss_sum = h->grads + P;
+    h->ln_floats = ix.ln_floats;
+    h->off_ln = ix.off_ln;
+    h->ln_grads = h->loss_sum + 64;
+    h->clip_norm = h->ln_grads + h->ln_floats;
+    if (ix.ln >= 0) h->ln_params = at(ix.ln);
+    h->ln_is.assign(n, nullptr);
+    h->mask.assign(n, nullptr);
+    for (int k = 0; k + 1 < n; ++k) {
+        if (ix.ln_is[k] >= 0) h->ln_is[k] = at(ix.ln_is[k]);
+        if (ix.mask[k] >= 0) h->mask[k] = reinterpret_cast<unsigned char *>(at(ix.mask[k]));
+    }
+    // dropout: one draw per hidden element of the GLOBAL batch, layer after layer (:773-788); this rank's
+    // rows start rank * batch rows into each layer's share
+    h->draw_off.assign(n, 0);
+    h->draws_per_step = 0;
+    if (h->dropout_p > 0.0f)
+        for (int k = 0; k + 1 < n; ++k) {
+            h->draw_off[k] = h->draws_per_step + (unsigned long long)h->rank * B * L[k + 1];
+            h->draws_per_step += (unsigned long long)gb * L[k + 1];
+        }
     h->s1 = at(i_s1);
     h->s2 = at(i_s2);
     h->scalars = reinterpret_cast<StepScalars *>(at(i_sc));
@@ -635,10 +831,16 @@ int build(vb200_handle *h) {
         lcg_xavier(h->mirror_params + h->off_w[i], (int64_t)L[i] * L[i + 1], L[i], L[i + 1], &rng);
     VB_CUDA(h, cudaMemcpyAsync(h->params, h->mirror_params, (size_t)P * 4, cudaMemcpyHostToDevice, h->stream));
     VB_CUDA(h, cudaStreamSynchronize(h->stream));
+    if (h->layernorm) {  // gamma = 1, beta = 0 (:660-664)
+        std::vector<float> ln((size_t)h->ln_floats, 0.0f);
+        for (int k = 0; k + 1 < n; ++k) std::fill_n(ln.begin() + h->off_ln[k], L[k + 1], 1.0f);
+        VB_CUDA(h, cudaMemcpy(h->ln_params, ln.data(), ln.size() * 4, cudaMemcpyHostToDevice));
+    }
 
-    if (h->world > 1 || c.reserved[0] == 1) {
+    if (h->world > 1 || c.force_dp == 1) {
         VB_CUDA(h, cudaStreamCreateWithFlags(&h->comm_stream, cudaStreamNonBlocking));
         VB_CUDA(h, cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming));
+        for (int q = 0; q < 2; ++q) VB_CUDA(h, cudaEventCreateWithFlags(&h->ev_clip[q], cudaEventDisableTiming));
         h->ev_bucket.resize(n + 1);
         for (auto &ev : h->ev_bucket) VB_CUDA(h, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
         h->dp = new DpComm();
@@ -758,34 +960,64 @@ int volta_b200_get_grads(vb200_handle *h, float **dwo, float **dbo) {
     return VB200_OK;
 }
 
-int64_t volta_b200_state_floats(vb200_handle *h) {
-    if (!h) return 0;
+namespace {
+int64_t moment_floats(vb200_handle *h) {
     const int opt = h->cfg.optimizer;
     if (opt == VB200_OPT_SGD) return 0;
     return (opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW) ? 2 * h->n_params_padded : h->n_params_padded;
+}
+}  // namespace
+
+int64_t volta_b200_state_floats(vb200_handle *h) {
+    if (!h) return 0;
+    return moment_floats(h) + (h->dropout_p > 0.0f ? 2 : 0);
+}
+
+int volta_b200_get_layernorm(vb200_handle *h, int32_t li, float *gamma, float *beta) {
+    if (!h) return VB200_ERR_INVALID;
+    if (!h->layernorm) return h->reject(VB200_ERR_INVALID, "get_layernorm: the handle was created without LayerNorm");
+    if (li < 0 || li >= h->n - 1 || !gamma || !beta) return h->reject(VB200_ERR_INVALID, "get_layernorm: bad layer index or null pointer");
+    const size_t c = (size_t)h->L[li + 1];
+    VB_CUDA(h, cudaStreamSynchronize(h->stream));
+    VB_CUDA(h, cudaMemcpy(gamma, h->ln_params + h->off_ln[li], c * 4, cudaMemcpyDeviceToHost));
+    VB_CUDA(h, cudaMemcpy(beta, h->ln_params + h->off_ln[li] + c, c * 4, cudaMemcpyDeviceToHost));
+    return check_device_status(h);
+}
+
+int volta_b200_set_layernorm(vb200_handle *h, int32_t li, const float *gamma, const float *beta) {
+    if (!h) return VB200_ERR_INVALID;
+    if (!h->layernorm) return h->reject(VB200_ERR_INVALID, "set_layernorm: the handle was created without LayerNorm");
+    if (li < 0 || li >= h->n - 1 || !gamma || !beta) return h->reject(VB200_ERR_INVALID, "set_layernorm: bad layer index or null pointer");
+    const size_t c = (size_t)h->L[li + 1];
+    VB_CUDA(h, cudaStreamSynchronize(h->stream));
+    VB_CUDA(h, cudaMemcpy(h->ln_params + h->off_ln[li], gamma, c * 4, cudaMemcpyHostToDevice));
+    VB_CUDA(h, cudaMemcpy(h->ln_params + h->off_ln[li] + c, beta, c * 4, cudaMemcpyHostToDevice));
+    return VB200_OK;
 }
 
 int volta_b200_save_state(vb200_handle *h, float *out, int64_t n, uint64_t *step_out) {
     if (!h) return VB200_ERR_INVALID;
     if (h->dp_fused) return h->reject(VB200_ERR_UNSUPPORTED, "save_state: optimizer state is sharded over the ranks in fused data-parallel mode");
-    const int64_t need = volta_b200_state_floats(h);
+    const int64_t need = volta_b200_state_floats(h), mom = moment_floats(h);
     if (n < need || (need && !out)) return h->reject(VB200_ERR_INVALID, "save_state: buffer too small");
     VB_CUDA(h, cudaStreamSynchronize(h->stream));
     const int64_t P = h->n_params_padded;
-    if (need >= P) VB_CUDA(h, cudaMemcpy(out, h->s1, (size_t)P * 4, cudaMemcpyDeviceToHost));
-    if (need >= 2 * P) VB_CUDA(h, cudaMemcpy(out + P, h->s2, (size_t)P * 4, cudaMemcpyDeviceToHost));
+    if (mom >= P) VB_CUDA(h, cudaMemcpy(out, h->s1, (size_t)P * 4, cudaMemcpyDeviceToHost));
+    if (mom >= 2 * P) VB_CUDA(h, cudaMemcpy(out + P, h->s2, (size_t)P * 4, cudaMemcpyDeviceToHost));
+    if (need > mom) memcpy(out + mom, &h->dropout_rng, 8);  // raw bits of the mask stream position
     if (step_out) *step_out = h->adam_step;
     return VB200_OK;
 }
 
 int volta_b200_load_state(vb200_handle *h, const float *in, int64_t n, uint64_t step) {
     if (!h) return VB200_ERR_INVALID;
-    const int64_t need = volta_b200_state_floats(h);
+    const int64_t need = volta_b200_state_floats(h), mom = moment_floats(h);
     if (n < need || (need && !in)) return h->reject(VB200_ERR_INVALID, "load_state: buffer too small");
     VB_CUDA(h, cudaStreamSynchronize(h->stream));
     const int64_t P = h->n_params_padded;
-    if (need >= P) VB_CUDA(h, cudaMemcpy(h->s1, in, (size_t)P * 4, cudaMemcpyHostToDevice));
-    if (need >= 2 * P) VB_CUDA(h, cudaMemcpy(h->s2, in + P, (size_t)P * 4, cudaMemcpyHostToDevice));
+    if (mom >= P) VB_CUDA(h, cudaMemcpy(h->s1, in, (size_t)P * 4, cudaMemcpyHostToDevice));
+    if (mom >= 2 * P) VB_CUDA(h, cudaMemcpy(h->s2, in + P, (size_t)P * 4, cudaMemcpyHostToDevice));
+    if (need > mom) memcpy(&h->dropout_rng, in + mom, 8);
     h->adam_step = step;
     return VB200_OK;
 }
@@ -900,7 +1132,7 @@ int volta_b200_infer(vb200_handle *h, const float *in, int64_t in_n, float *out,
     if (cudaPointerGetAttributes(&ao, out) == cudaSuccess) odev = ao.type == cudaMemoryTypeDevice || ao.type == cudaMemoryTypeManaged; else cudaGetLastError();
     VB_CUDA(h, cudaMemcpyAsync(h->xin[0], in, (size_t)in_n * 4, idev ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, h->stream));
     const int saved = h->kernels_per_step;
-    int rc = enqueue_forward(h, 0, rows);
+    int rc = enqueue_forward(h, 0, rows, false);
     h->kernels_per_step = saved;
     if (rc) return rc;
     VB_CUDA(h, cudaMemcpyAsync(out, h->act[h->n], (size_t)out_n * 4, odev ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, h->stream));
@@ -923,6 +1155,8 @@ int volta_b200_dp_attach_peers(vb200_handle *h, const uint8_t *handles, int32_t 
     if (count != h->world || count > kMaxPeers || !handles)
         return h->reject(VB200_ERR_INVALID, "attach_peers: need one 64-byte handle per rank (at most 8 ranks)");
     if (h->dp_fused) return h->reject(VB200_ERR_INVALID, "attach_peers: already attached");
+    if (h->layernorm || h->clip > 0.0f)
+        return h->reject(VB200_ERR_UNSUPPORTED, "attach_peers: LayerNorm and the clip need the NCCL data-parallel path");
     VB_CUDA(h, cudaStreamSynchronize(h->stream));
     for (int q = 0; q < count; ++q) {
         if (q == h->rank) {

@@ -20,7 +20,8 @@ class Config(C.Structure):
         ("optimizer", C.c_int32), ("batch", C.c_int32), ("global_batch", C.c_int32), ("world_size", C.c_int32),
         ("rank", C.c_int32), ("nccl_unique_id", C.c_uint8 * 128), ("momentum", C.c_float),
         ("weight_decay", C.c_float), ("gemm_path", C.c_int32), ("use_graph", C.c_int32),
-        ("reserved", C.c_int32 * 8),
+        ("force_dp", C.c_int32), ("fuse_sgd", C.c_int32), ("use_layernorm", C.c_int32), ("dropout_p", C.c_float),
+        ("clip_grad", C.c_float), ("reserved", C.c_int32 * 3),
     ]
 
 
@@ -31,7 +32,7 @@ class KernelRecord(C.Structure):
 # every symbol include/volta_b200.h declares
 EXPORTS = [
     "volta_b200_create", "volta_b200_destroy", "volta_b200_step", "volta_b200_loss", "volta_b200_set_params",
-    "volta_b200_get_params", "volta_b200_infer", "volta_b200_get_grads", "volta_b200_state_floats", "volta_b200_save_state",
+    "volta_b200_get_params", "volta_b200_infer", "volta_b200_get_layernorm", "volta_b200_set_layernorm", "volta_b200_get_grads", "volta_b200_state_floats", "volta_b200_save_state",
     "volta_b200_load_state", "volta_b200_status", "volta_b200_last_error", "volta_b200_stream",
     "volta_b200_synchronize", "volta_b200_arena_bytes", "volta_b200_plan", "volta_b200_kernels_per_step",
     "volta_b200_profile_step", "volta_b200_dp_unique_id", "volta_b200_dp_ipc_handle", "volta_b200_dp_attach_peers", "volta_b200_optimizer_apply", "volta_b200_gemm",
@@ -65,6 +66,8 @@ def load_library():
         "volta_b200_set_params": (C.c_int, [vp, i32, fp, fp]),
         "volta_b200_get_params": (C.c_int, [vp, fpp, fpp]),
         "volta_b200_infer": (C.c_int, [vp, vp, i64, vp, i64]),
+        "volta_b200_get_layernorm": (C.c_int, [vp, i32, fp, fp]),
+        "volta_b200_set_layernorm": (C.c_int, [vp, i32, fp, fp]),
         "volta_b200_get_grads": (C.c_int, [vp, fpp, fpp]),
         "volta_b200_state_floats": (i64, [vp]),
         "volta_b200_save_state": (C.c_int, [vp, fp, i64, C.POINTER(C.c_uint64)]),

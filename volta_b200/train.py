@@ -15,7 +15,8 @@ import numpy as np
 
 from .lib import Config, KernelRecord, VoltaB200Error, load_library
 
-ACTIVATIONS = {"relu": 0, "sigmoid": 1, "tanh": 2, "leaky_relu": 3, "leakyrelu": 3, "silu": 4, "gelu": 5, "": 0}
+ACTIVATIONS = {"relu": 0, "sigmoid": 1, "tanh": 2, "leaky_relu": 3, "leakyrelu": 3, "silu": 4, "gelu": 5, "softmax": 6,
+               "": 0}
 OPTIMIZERS = {"sgd": 0, "adam": 1, "adamw": 2, "adagrad": 3, "sgd_momentum": 4}
 GEMM_PATHS = {"auto": 0, "ffma": 1, "tensor": 2, "tensor_pair": 3}
 
@@ -52,7 +53,7 @@ class TrainHandle:
 
     def __init__(self, layers, activation="relu", optimizer="sgd", batch=1, *, global_batch=0, world_size=1, rank=0,
                  unique_id: bytes | None = None, momentum=0.0, weight_decay=0.0, gemm_path="auto", use_graph=True,
-                 force_dp=False, fuse_sgd=False):
+                 force_dp=False, fuse_sgd=False, dropout_p=0.0, use_layernorm=False, clip_grad=0.0):
         act = activation.lower()
         opt = optimizer.lower()
         if act not in ACTIVATIONS:
@@ -76,7 +77,7 @@ class TrainHandle:
         cfg.world_size = int(world_size)
         cfg.rank = int(rank)
         if world_size > 1 or force_dp:
-            cfg.reserved[0] = 1 if force_dp else 0
+            cfg.force_dp = 1 if force_dp else 0
             if unique_id is None or len(unique_id) != 128:
                 raise VoltaB200Error(1, "world_size > 1 needs the 128-byte unique id")
             for i, b in enumerate(unique_id):
@@ -85,7 +86,12 @@ class TrainHandle:
         cfg.weight_decay = float(weight_decay)
         cfg.gemm_path = GEMM_PATHS[gemm_path]
         cfg.use_graph = 1 if use_graph else 2
-        cfg.reserved[1] = 1 if fuse_sgd else 0
+        cfg.fuse_sgd = 1 if fuse_sgd else 0
+        # MlpTopology's dropout_p / use_layernorm / clip_grad (mlp_train_rust_codegen.rs:34-38)
+        cfg.dropout_p = float(dropout_p)
+        cfg.use_layernorm = 1 if use_layernorm else 0
+        cfg.clip_grad = float(clip_grad)
+        self.dropout_p = float(dropout_p)
         self._cfg = cfg
         h = C.c_void_p()
         rc = self.lib.volta_b200_create(C.byref(cfg), C.byref(h))
@@ -146,6 +152,22 @@ class TrainHandle:
         return out
 
     # -- extensions -------------------------------------------------------------------------
+    def get_layernorm(self, li: int):
+        """(gamma, beta) of hidden layer li; the handle must have been created with use_layernorm."""
+        c = self.layers[li + 1] if 0 <= li < self.n - 1 else 1
+        g, b = np.empty(c, np.float32), np.empty(c, np.float32)
+        fp = C.POINTER(C.c_float)
+        self._check(self.lib.volta_b200_get_layernorm(self.h, int(li), g.ctypes.data_as(fp), b.ctypes.data_as(fp)))
+        return g, b
+
+    def set_layernorm(self, li: int, gamma, beta):
+        g = np.ascontiguousarray(gamma, dtype=np.float32).reshape(-1)
+        b = np.ascontiguousarray(beta, dtype=np.float32).reshape(-1)
+        if 0 <= li < self.n - 1 and (g.size != self.layers[li + 1] or b.size != self.layers[li + 1]):
+            raise ValueError("set_layernorm: wrong tensor size for layer %d" % li)
+        fp = C.POINTER(C.c_float)
+        self._check(self.lib.volta_b200_set_layernorm(self.h, int(li), g.ctypes.data_as(fp), b.ctypes.data_as(fp)))
+
     def get_grads(self):
         return self._lists(self.lib.volta_b200_get_grads)
 
@@ -177,9 +199,12 @@ class TrainHandle:
         """Import per-layer optimizer state (lists of arrays; None where unused) and the step count."""
         ow, ob, total = self.state_offsets()
         n = int(self.lib.volta_b200_state_floats(self.h))
+        moments = n - (2 if self.dropout_p > 0.0 else 0)   # the mask stream position rides behind the moments
         buf = np.zeros(max(n, 1), dtype=np.float32)
+        if moments < n:
+            buf[moments:n] = self.save_state()[0][moments:n]
         for base, (ws, bs) in ((0, (s1w, s1b)), (total, (s2w, s2b))):
-            if base >= n:
+            if base >= moments:
                 break
             for i in range(self.n):
                 if ws[i] is not None:
