@@ -143,6 +143,34 @@ int64_t volta_b200_state_floats(vb200_handle *h);
 int volta_b200_save_state(vb200_handle *h, float *out, int64_t n, uint64_t *step_out);
 int volta_b200_load_state(vb200_handle *h, const float *in, int64_t n, uint64_t step);
 
+/* Checkpoints in the reference's file formats (src/engine/model/checkpoint.rs): format 1 is the v1
+ * text form (:14-44: header "#volta-checkpoint:v1", then "name|d0,d1|v0,v1,..." sorted by name; '#'
+ * lines are comments), format 2 the v2 binary form (:162-213: magic "VOLTA\2\0\0" + a zlib stream of
+ * stored blocks).  Files written here load in Volta's load_checkpoint / load_checkpoint_compressed and
+ * the other way round.  One deviation: values are printed with nine SIGNIFICANT digits (every f32
+ * survives), where the reference prints nine decimals (small values lose bits); both parse the other.
+ * A vb200_checkpoint is a set of named fp32 tensors held on the host; it needs no GPU.
+ * _load returns NULL on failure and volta_b200_last_error(NULL) says why (the reference's messages:
+ * unsupported version, invalid format / shape / value at line N). */
+typedef struct vb200_checkpoint vb200_checkpoint;
+vb200_checkpoint *volta_b200_checkpoint_new(void);
+void volta_b200_checkpoint_free(vb200_checkpoint *ck);
+int volta_b200_checkpoint_add(vb200_checkpoint *ck, const char *name, const int64_t *shape, int32_t ndim,
+                              const float *data);
+int volta_b200_checkpoint_save(const vb200_checkpoint *ck, const char *path, int32_t format);
+vb200_checkpoint *volta_b200_checkpoint_load(const char *path);
+int32_t volta_b200_checkpoint_count(const vb200_checkpoint *ck);
+int volta_b200_checkpoint_entry(const vb200_checkpoint *ck, int32_t i, const char **name, const int64_t **shape,
+                                int32_t *ndim, const float **data, int64_t *count);
+/* Handle <-> checkpoint.  Names: "layer<i>.weight" [in, out], "layer<i>.bias" [out],
+ * "layer<i>.ln_gamma/.ln_beta"; with_state adds the optimizer's moments ("layer<i>.weight.m", ".v",
+ * ".acc" for Adagrad, ".mom" for SGD momentum; same for ".bias") and the counters "meta.adam_step",
+ * "meta.dropout_rng" (three floats holding 22 + 22 + 20 bits each as exact integers) - what the
+ * reference's checkpoint cannot carry (it stores parameters only).  Import takes every tensor it
+ * knows by name, checks its shape, leaves the rest of the handle as it is and ignores other names. */
+int volta_b200_export_checkpoint(vb200_handle *h, vb200_checkpoint *ck, int32_t with_state);
+int volta_b200_import_checkpoint(vb200_handle *h, const vb200_checkpoint *ck);
+
 /* Error reporting: last error code / message of this handle (or of the last failed
  * create when h is NULL).  The message pointer stays valid until the next call. */
 int volta_b200_status(vb200_handle *h);

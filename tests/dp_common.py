@@ -54,7 +54,7 @@ def oracle_shard_worker(rank, world, port, opt, real, out_dir):
     dist.destroy_process_group()
 
 
-def gpu_shard_worker(rank, world, port, opt, out_dir, repeat, fused=False):
+def gpu_shard_worker(rank, world, port, opt, out_dir, repeat, fused=False, act="silu", options=None):
     """One GPU rank: libvolta_b200 handle on its row shard; the unique id travels over gloo."""
     import torch
     import torch.distributed as dist
@@ -69,7 +69,8 @@ def gpu_shard_worker(rank, world, port, opt, out_dir, repeat, fused=False):
     for rep in range(repeat):
         box = [dp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
-        h = TrainHandle(LAYERS, "silu", opt, B, global_batch=GLOBAL_BATCH, world_size=world, rank=rank, unique_id=box[0])
+        h = TrainHandle(LAYERS, act, opt, B, global_batch=GLOBAL_BATCH, world_size=world, rank=rank, unique_id=box[0],
+                        **(options or {}))
         if fused:
             handles = [None] * world
             dist.all_gather_object(handles, h.ipc_handle())

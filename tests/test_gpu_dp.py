@@ -107,3 +107,39 @@ def test_two_gpu_ranks_match_the_full_batch_oracle(opt, mode):
     for i in range(len(pw)):      # run-to-run bit-identical at a fixed GPU count
         assert np.array_equal(runs[0][0]["w%d" % i], runs[1][0]["w%d" % i])
     assert np.array_equal(runs[0][0]["losses"], runs[1][0]["losses"])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_ranks_with_the_optional_stages_match_the_full_batch_oracle():
+    """relu -> LayerNorm -> dropout with the clip active, rows split over two ranks: each rank draws its
+    rows' slice of the single-process mask stream, the LayerNorm gradients travel in the last bucket and
+    the clip's norm is summed over the ranks in mid-step; the result is the full-batch oracle's."""
+    world, opt = 2, "sgd"
+    options = dict(use_layernorm=True, dropout_p=0.25, clip_grad=0.02)
+    out = tempfile.mkdtemp()
+    mp.spawn(dpc.gpu_shard_worker, args=(world, _free_port(), opt, out, 2, False, "relu", options), nprocs=world, join=True)
+    x, y, ws, bs = dpc.inputs()
+    o = Oracle(dpc.LAYERS, "relu", opt, dpc.GLOBAL_BATCH, **options)
+    o64 = Oracle(dpc.LAYERS, "relu", opt, dpc.GLOBAL_BATCH, real="f64", **options)
+    for i, (w, b) in enumerate(zip(ws, bs)):
+        o.set_params(i, w, b)
+        o64.set_params(i, w, b)
+    losses = []
+    for _ in range(dpc.STEPS):
+        o.step(x, y, 0.01)
+        o64.step(x, y, 0.01)
+        losses.append(o64.loss())
+    pw, pw32 = o64.get_params()[0], o.get_params()[0]
+    runs = [[np.load("%s/rank%d_rep%d.npz" % (out, r, rep)) for r in range(world)] for rep in range(2)]
+    for rep in runs:
+        for r in rep:
+            np.testing.assert_allclose(r["losses"], losses, rtol=2e-5)
+            for i in range(len(pw)):
+                err = np.max(np.abs(r["w%d" % i] - pw[i])) / np.max(np.abs(pw[i]))
+                ref = np.max(np.abs(pw32[i] - pw[i])) / np.max(np.abs(pw[i]))
+                assert err <= max(2e-5, 4 * ref)
+        for i in range(len(pw)):
+            assert np.array_equal(rep[0]["w%d" % i], rep[1]["w%d" % i])
+    for i in range(len(pw)):
+        assert np.array_equal(runs[0][0]["w%d" % i], runs[1][0]["w%d" % i])
+    assert np.array_equal(runs[0][0]["losses"], runs[1][0]["losses"])

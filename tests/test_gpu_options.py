@@ -279,3 +279,44 @@ def test_option_arguments_are_validated():
     g.step(np.zeros((2, 4), np.float32), np.zeros((2, 1), np.float32), 0.1)   # the handle stays usable
     assert g.loss() == 0.0
     g.free()
+
+
+@pytest.mark.parametrize("fmt", [1, 2])
+@pytest.mark.parametrize("opt", ["adam", "adagrad", "sgd_momentum"])
+def test_checkpoint_file_resumes_training_bit_exactly(tmp_path, fmt, opt):
+    """export -> file in the reference's v1 text / v2 binary format -> load -> import into a fresh
+    handle: parameters, LayerNorm scale/shift, optimizer moments, the Adam counter and the mask
+    stream position all travel, so both handles continue identically."""
+    from volta_b200.checkpoint import Checkpoint
+    layers, B = [16, 40, 24, 2], 8
+    x = synth.rows("normal", 1, 0, B, 16)
+    y = synth.rows("normal", 2, 0, B, 2)
+    kw = dict(dropout_p=0.4, use_layernorm=True)
+    a = TrainHandle(layers, "gelu", opt, B, **kw)
+    for _ in range(3):
+        a.step(x, y, 1e-2)
+    path = tmp_path / "ck"
+    a.export_checkpoint().save(path, fmt)
+    ck = Checkpoint.load(path)
+    names = set(ck.tensors())
+    assert {"layer0.weight", "layer2.bias", "layer1.ln_gamma", "meta.dropout_rng"} <= names
+    assert ("meta.adam_step" in names) == (opt == "adam")
+    b = TrainHandle(layers, "gelu", opt, B, **kw)
+    b.import_checkpoint(ck)
+    for _ in range(3):
+        a.step(x, y, 1e-2)
+        b.step(x, y, 1e-2)
+    assert np.float32(a.loss()).view(np.uint32) == np.float32(b.loss()).view(np.uint32)
+    for p, q in zip(sum(a.get_params(), []), sum(b.get_params(), [])):
+        assert np.array_equal(p, q)
+    # parameters only: what the reference's own checkpoint holds
+    only = a.export_checkpoint(with_state=False).tensors()
+    assert not any(n.startswith("meta.") or n.endswith((".m", ".v", ".acc", ".mom")) for n in only)
+    # a tensor of the wrong shape is refused and the handle stays usable
+    bad = Checkpoint()
+    bad.add("layer0.weight", np.zeros((16, 41), np.float32))
+    with pytest.raises(VoltaB200Error, match="wrong shape"):
+        b.import_checkpoint(bad)
+    b.step(x, y, 1e-2)
+    a.free()
+    b.free()

@@ -21,6 +21,7 @@
 
 #include "vb_arena.h"
 #include "vb_common.cuh"
+#include "vb_checkpoint.h"
 #include "vb_dp.h"
 
 using namespace vb;
@@ -1019,6 +1020,203 @@ int volta_b200_load_state(vb200_handle *h, const float *in, int64_t n, uint64_t 
     if (mom >= 2 * P) VB_CUDA(h, cudaMemcpy(h->s2, in + P, (size_t)P * 4, cudaMemcpyHostToDevice));
     if (need > mom) memcpy(&h->dropout_rng, in + mom, 8);
     h->adam_step = step;
+    return VB200_OK;
+}
+
+// ---- checkpoints ------------------------------------------------------------------------------
+struct vb200_checkpoint {
+    vb::Checkpoint ck;
+};
+
+namespace {
+void set_global_error(int code, const std::string &msg) {
+    std::lock_guard<std::mutex> lk(g_err_mutex);
+    g_create_status = code;
+    g_create_error = msg;
+}
+const char *state1_suffix(int opt) {
+    switch (opt) {
+    case VB200_OPT_ADAM:
+    case VB200_OPT_ADAMW: return ".m";
+    case VB200_OPT_ADAGRAD: return ".acc";
+    case VB200_OPT_SGD_MOMENTUM: return ".mom";
+    }
+    return nullptr;
+}
+}  // namespace
+
+vb200_checkpoint *volta_b200_checkpoint_new(void) { return new vb200_checkpoint(); }
+
+void volta_b200_checkpoint_free(vb200_checkpoint *ck) { delete ck; }
+
+int volta_b200_checkpoint_add(vb200_checkpoint *ck, const char *name, const int64_t *shape, int32_t ndim, const float *data) {
+    if (!ck || !name || ndim < 0 || (ndim && !shape)) return VB200_ERR_INVALID;
+    std::vector<int64_t> sh(shape, shape + ndim);
+    size_t count = 1;
+    for (int64_t d : sh) {
+        if (d < 0) return VB200_ERR_INVALID;
+        count *= (size_t)d;
+    }
+    if (count && !data) return VB200_ERR_INVALID;
+    ck->ck.put(name, sh, data, count);
+    return VB200_OK;
+}
+
+int volta_b200_checkpoint_save(const vb200_checkpoint *ck, const char *path, int32_t format) {
+    if (!ck || !path) return VB200_ERR_INVALID;
+    std::string err;
+    if (!vb::checkpoint_save(ck->ck, path, format, &err)) {
+        set_global_error(VB200_ERR_INVALID, err);
+        return VB200_ERR_INVALID;
+    }
+    return VB200_OK;
+}
+
+vb200_checkpoint *volta_b200_checkpoint_load(const char *path) {
+    if (!path) return nullptr;
+    vb200_checkpoint *ck = new vb200_checkpoint();
+    std::string err;
+    if (!vb::checkpoint_load(&ck->ck, path, &err)) {
+        set_global_error(VB200_ERR_INVALID, err);
+        delete ck;
+        return nullptr;
+    }
+    return ck;
+}
+
+int32_t volta_b200_checkpoint_count(const vb200_checkpoint *ck) { return ck ? (int32_t)ck->ck.entries.size() : 0; }
+
+int volta_b200_checkpoint_entry(const vb200_checkpoint *ck, int32_t i, const char **name, const int64_t **shape,
+                                int32_t *ndim, const float **data, int64_t *count) {
+    if (!ck || i < 0 || i >= (int32_t)ck->ck.entries.size()) return VB200_ERR_INVALID;
+    const vb::CheckpointEntry &e = ck->ck.entries[(size_t)i];
+    if (name) *name = e.name.c_str();
+    if (shape) *shape = e.shape.data();
+    if (ndim) *ndim = (int32_t)e.shape.size();
+    if (data) *data = e.data.data();
+    if (count) *count = (int64_t)e.data.size();
+    return VB200_OK;
+}
+
+int volta_b200_export_checkpoint(vb200_handle *h, vb200_checkpoint *ck, int32_t with_state) {
+    if (!h || !ck) return VB200_ERR_INVALID;
+    if (with_state && h->dp_fused)
+        return h->reject(VB200_ERR_UNSUPPORTED, "export_checkpoint: optimizer state is sharded over the ranks in fused data-parallel mode");
+    const int opt = h->cfg.optimizer;
+    const int64_t P = h->n_params_padded;
+    VB_CUDA(h, cudaStreamSynchronize(h->stream));
+    std::vector<float> host((size_t)P);
+    auto put_flat = [&](const float *dev, const char *wsuffix, const char *bsuffix) -> int {
+        VB_CUDA(h, cudaMemcpy(host.data(), dev, (size_t)P * 4, cudaMemcpyDeviceToHost));
+        for (int i = 0; i < h->n; ++i) {
+            const int64_t r = h->L[i], c = h->L[i + 1];
+            const std::string base = "layer" + std::to_string(i);
+            ck->ck.put(base + wsuffix, {r, c}, host.data() + h->off_w[i], (size_t)(r * c));
+            ck->ck.put(base + bsuffix, {c}, host.data() + h->off_b[i], (size_t)c);
+        }
+        return VB200_OK;
+    };
+    int rc = put_flat(h->params, ".weight", ".bias");
+    if (rc) return rc;
+    if (h->layernorm) {
+        std::vector<float> ln((size_t)h->ln_floats);
+        VB_CUDA(h, cudaMemcpy(ln.data(), h->ln_params, ln.size() * 4, cudaMemcpyDeviceToHost));
+        for (int k = 0; k + 1 < h->n; ++k) {
+            const int64_t c = h->L[k + 1];
+            ck->ck.put("layer" + std::to_string(k) + ".ln_gamma", {c}, ln.data() + h->off_ln[k], (size_t)c);
+            ck->ck.put("layer" + std::to_string(k) + ".ln_beta", {c}, ln.data() + h->off_ln[k] + c, (size_t)c);
+        }
+    }
+    if (with_state) {
+        if (const char *sfx = state1_suffix(opt)) {
+            const std::string ws = std::string(".weight") + sfx, bs = std::string(".bias") + sfx;
+            rc = put_flat(h->s1, ws.c_str(), bs.c_str());
+            if (rc) return rc;
+        }
+        if (opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW) {
+            rc = put_flat(h->s2, ".weight.v", ".bias.v");
+            if (rc) return rc;
+            float parts[3];
+            vb::split_u64(h->adam_step, parts);
+            ck->ck.put("meta.adam_step", {3}, parts, 3);
+        }
+        if (h->dropout_p > 0.0f) {
+            float parts[3];
+            vb::split_u64(h->dropout_rng, parts);
+            ck->ck.put("meta.dropout_rng", {3}, parts, 3);
+        }
+    }
+    return check_device_status(h);
+}
+
+int volta_b200_import_checkpoint(vb200_handle *h, const vb200_checkpoint *ck) {
+    if (!h || !ck) return VB200_ERR_INVALID;
+    const int opt = h->cfg.optimizer;
+    const int64_t P = h->n_params_padded;
+    VB_CUDA(h, cudaStreamSynchronize(h->stream));
+    std::vector<float> host((size_t)P);
+    // every tensor of the flat region that the checkpoint names replaces the handle's; the rest stays
+    auto take_flat = [&](float *dev, const std::string &wsuffix, const std::string &bsuffix) -> int {
+        VB_CUDA(h, cudaMemcpy(host.data(), dev, (size_t)P * 4, cudaMemcpyDeviceToHost));
+        bool any = false;
+        for (int i = 0; i < h->n; ++i) {
+            const int64_t r = h->L[i], c = h->L[i + 1];
+            const std::string base = "layer" + std::to_string(i);
+            if (const vb::CheckpointEntry *e = ck->ck.find(base + wsuffix)) {
+                if (e->shape != std::vector<int64_t>{r, c})
+                    return h->reject(VB200_ERR_INVALID, "import_checkpoint: '" + e->name + "' has the wrong shape");
+                memcpy(host.data() + h->off_w[i], e->data.data(), (size_t)(r * c) * 4);
+                any = true;
+            }
+            if (const vb::CheckpointEntry *e = ck->ck.find(base + bsuffix)) {
+                if (e->shape != std::vector<int64_t>{c})
+                    return h->reject(VB200_ERR_INVALID, "import_checkpoint: '" + e->name + "' has the wrong shape");
+                memcpy(host.data() + h->off_b[i], e->data.data(), (size_t)c * 4);
+                any = true;
+            }
+        }
+        if (any) VB_CUDA(h, cudaMemcpy(dev, host.data(), (size_t)P * 4, cudaMemcpyHostToDevice));
+        return VB200_OK;
+    };
+    int rc = take_flat(h->params, ".weight", ".bias");
+    if (rc) return rc;
+    if (h->layernorm) {
+        std::vector<float> ln((size_t)h->ln_floats);
+        VB_CUDA(h, cudaMemcpy(ln.data(), h->ln_params, ln.size() * 4, cudaMemcpyDeviceToHost));
+        for (int k = 0; k + 1 < h->n; ++k) {
+            const int64_t c = h->L[k + 1];
+            const vb::CheckpointEntry *g = ck->ck.find("layer" + std::to_string(k) + ".ln_gamma");
+            const vb::CheckpointEntry *b = ck->ck.find("layer" + std::to_string(k) + ".ln_beta");
+            for (const vb::CheckpointEntry *e : {g, b})
+                if (e && e->shape != std::vector<int64_t>{c})
+                    return h->reject(VB200_ERR_INVALID, "import_checkpoint: '" + e->name + "' has the wrong shape");
+            if (g) memcpy(ln.data() + h->off_ln[k], g->data.data(), (size_t)c * 4);
+            if (b) memcpy(ln.data() + h->off_ln[k] + c, b->data.data(), (size_t)c * 4);
+        }
+        VB_CUDA(h, cudaMemcpy(h->ln_params, ln.data(), ln.size() * 4, cudaMemcpyHostToDevice));
+    }
+    if (h->dp_fused) return VB200_OK;  // sharded state: parameters only
+    if (const char *sfx = state1_suffix(opt)) {
+        rc = take_flat(h->s1, std::string(".weight") + sfx, std::string(".bias") + sfx);
+        if (rc) return rc;
+    }
+    if (opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW) {
+        rc = take_flat(h->s2, ".weight.v", ".bias.v");
+        if (rc) return rc;
+        if (const vb::CheckpointEntry *e = ck->ck.find("meta.adam_step")) {
+            uint64_t v = 0;
+            if (e->data.size() != 3 || !vb::join_u64(e->data.data(), &v))
+                return h->reject(VB200_ERR_INVALID, "import_checkpoint: 'meta.adam_step' is not a split counter");
+            h->adam_step = v;
+        }
+    }
+    if (h->dropout_p > 0.0f)
+        if (const vb::CheckpointEntry *e = ck->ck.find("meta.dropout_rng")) {
+            uint64_t v = 0;
+            if (e->data.size() != 3 || !vb::join_u64(e->data.data(), &v))
+                return h->reject(VB200_ERR_INVALID, "import_checkpoint: 'meta.dropout_rng' is not a split counter");
+            h->dropout_rng = v;
+        }
     return VB200_OK;
 }
 

@@ -213,6 +213,17 @@ class TrainHandle:
                     buf[base + ob[i]: base + ob[i] + bs[i].size] = np.asarray(bs[i], np.float32).ravel()
         self.load_state(buf[:n], step)
 
+    def export_checkpoint(self, with_state: bool = True):
+        """Parameters (and, with_state, optimizer moments and counters) as a named-tensor Checkpoint."""
+        from .checkpoint import Checkpoint
+        ck = Checkpoint()
+        self._check(self.lib.volta_b200_export_checkpoint(self.h, ck.h, 1 if with_state else 0))
+        return ck
+
+    def import_checkpoint(self, ck):
+        """Take every tensor the checkpoint names for this topology; other names are ignored."""
+        self._check(self.lib.volta_b200_import_checkpoint(self.h, ck.h))
+
     def ipc_handle(self) -> bytes:
         """64-byte handle of this rank's arena, to be exchanged among the data-parallel ranks."""
         buf = (C.c_uint8 * 64)()
