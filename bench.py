@@ -407,6 +407,57 @@ def main():
                             "kernels_per_step": oh.kernels_per_step, "loss": oh.loss(),
                             "workload": "MLP %s, %s, %s, B=%d" % ("->".join(map(str, ol)), oc.activation, oc.optimizer, oc.batch)}
             oh.free()
+        # the reference's option examples (examples/bench_dropout.vt, bench_layernorm.vt, bench_softmax.vt):
+        # the c2 topology with one optional stage each, SGD lr 0.01, batch 64
+        c2 = CONFIGS["c2"]
+        for name, act, kw in (("c2_dropout", "relu", {"dropout_p": 0.2}), ("c2_layernorm", "relu", {"use_layernorm": True}),
+                              ("c2_softmax", "softmax", {})):
+            ol = list(c2.layers)
+            # weights: the handle's default, the reference's LCG-Xavier stream (with the Kaiming weights of the
+            # main configurations the dropout example diverges at this learning rate, on the CPU oracle too)
+            oh = TrainHandle(ol, act, "sgd", c2.batch, gemm_path=args.gemm_path, **kw)
+            ox = torch.from_numpy(synth.rows(c2.x_dist, 1234, 0, c2.batch, ol[0])).cuda()
+            oy = torch.from_numpy(synth.rows(c2.y_dist, 4321, 0, c2.batch, ol[-1])).cuda()
+            ostream = torch.cuda.ExternalStream(oh.stream)
+            for _ in range(5):
+                oh.step(ox, oy, 0.01)
+            oh.synchronize()
+            pairs = []
+            for _ in range(50):
+                with torch.cuda.stream(ostream):
+                    flush_buf.zero_()
+                a, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(ostream)
+                oh.step(ox, oy, 0.01)
+                b2.record(ostream)
+                pairs.append((a, b2))
+            oh.synchronize()
+            torch.cuda.synchronize()
+            ms = sorted(x.elapsed_time(y2) for x, y2 in pairs)
+            others[name] = {"ms_per_step": ms[len(ms) // 2], "steps": 50, "kernels_per_step": oh.kernels_per_step,
+                            "loss": oh.loss(), "workload": "MLP %s, %s, sgd, B=%d, %s" % (
+                                "->".join(map(str, ol)), act, c2.batch, kw or "softmax hidden activation")}
+            oh.free()
+        # inference through host buffers, the protocol of the reference's examples/bench_infer.c:
+        # c2 topology, 10 000 calls of one row and 1 000 calls of 64 rows, wall clock per call
+        ol = list(c2.layers)
+        oh = TrainHandle(ol, c2.activation, "sgd", 64, gemm_path=args.gemm_path)
+        for i, (w, b) in enumerate(zip(*synth.kaiming_uniform_weights(ol, 42))):
+            oh.set_params(i, w, b)
+        for rows, warm, calls in ((1, 200, 10000), (64, 20, 1000)):
+            xin = synth.rows(c2.x_dist, 1234, 0, rows, ol[0])
+            out = np.empty((rows, ol[-1]), np.float32)
+            fn, hh, n_in = oh.lib.volta_b200_infer, oh.h, xin.size
+            pin, pout = xin.ctypes.data, out.ctypes.data
+            for _ in range(warm):
+                fn(hh, pin, n_in, pout, out.size)
+            t0 = time.perf_counter()
+            for _ in range(calls):
+                fn(hh, pin, n_in, pout, out.size)
+            dt = time.perf_counter() - t0
+            others["infer_c2_b%d" % rows] = {"us_per_call": dt / calls * 1e6, "calls": calls, "rows": rows,
+                                             "workload": "volta_infer protocol, host buffers, wall clock"}
+        oh.free()
 
     if rank == 0:
         line = {"metric": "train_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": world, "steps": steps,

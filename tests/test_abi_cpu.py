@@ -185,3 +185,26 @@ def test_codegen_compiles_the_topology_switches_in(tmp_path):
     assert "cfg.dropout_p = (float)0.25;" in src and "cfg.clip_grad = (float)1.5;" in src
     plain = open(codegen.compile_model([8, 16, 4], "relu", "sgd", str(tmp_path / "p.so"), emit_only=True)).read()
     assert "cfg.use_layernorm = 0;" in plain and "cfg.dropout_p = (float)0;" in plain
+
+
+def test_codegen_emits_an_inference_library_with_the_checkpoint_embedded(tmp_path):
+    """--infer: one exported function, volta_infer (include/volta_infer.h; the reference's
+    src/engine/ir/codegen/inner.rs:194-198), the checkpoint file's bytes inside the image."""
+    import numpy as np
+    from volta_b200 import codegen
+    from volta_b200.checkpoint import Checkpoint
+    ck = Checkpoint()
+    marker = np.arange(32, dtype=np.float32).reshape(8, 4) + np.float32(0.123)
+    ck.add("layer0.weight", marker)
+    ck.save(tmp_path / "m.ckpt", 2)
+    out = codegen.compile_model([8, 4], "relu", "sgd", str(tmp_path / "m.infer.so"), infer=True,
+                                checkpoint=str(tmp_path / "m.ckpt"))
+    lib = C.CDLL(out)
+    assert hasattr(lib, "volta_infer") and not hasattr(lib, "volta_train_init")
+    assert marker.tobytes() in open(out, "rb").read()
+    header = open(os.path.join(ROOT, "include", "volta_infer.h")).read()
+    assert re.findall(r"\b(volta_infer)\s*\(", header)
+    with pytest.raises(codegen.CodegenError, match="cannot read checkpoint"):
+        codegen.compile_model([8, 4], "relu", "sgd", str(tmp_path / "n.so"), infer=True, checkpoint=str(tmp_path / "nope"))
+    with pytest.raises(codegen.CodegenError, match="goes with --infer"):
+        codegen.compile_model([8, 4], "relu", "sgd", str(tmp_path / "n.so"), checkpoint=str(tmp_path / "m.ckpt"))

@@ -320,3 +320,43 @@ def test_checkpoint_file_resumes_training_bit_exactly(tmp_path, fmt, opt):
     b.step(x, y, 1e-2)
     a.free()
     b.free()
+
+
+@pytest.mark.parametrize("act,kw", [("relu", {"dropout_p": 0.2}), ("relu", {"use_layernorm": True}), ("softmax", {})])
+def test_reference_option_examples_at_full_size(act, kw):
+    """examples/bench_dropout.vt, bench_layernorm.vt, bench_softmax.vt: layers 512 1024 1024 512 256 1,
+    batch 64, SGD lr 0.01 - against the oracle at full size."""
+    g, _, _ = run_and_compare([512, 1024, 1024, 512, 256, 1], act, "sgd", 64, steps=4, lr=0.01, **kw)
+    g.free()
+
+
+def test_generated_inference_library_embeds_the_checkpoint(tmp_path):
+    """`volta-b200-codegen --infer --checkpoint F`: one exported function, volta_infer(in, in_n, out, out_n)
+    (src/engine/ir/codegen/inner.rs:194-198), weights from the embedded checkpoint file; called the way
+    examples/bench_infer.c calls it (one row, then 64 rows), then with more rows than the first handle holds."""
+    import ctypes as C
+    from volta_b200 import codegen
+    layers = [48, 300, 64, 3]
+    g = TrainHandle(layers, "gelu", "adam", 200, use_layernorm=True)
+    x = synth.rows("normal", 5, 0, 200, layers[0])
+    y = synth.rows("normal", 6, 0, 200, layers[-1])
+    for _ in range(3):
+        g.step(x, y, 1e-2)
+    ck = tmp_path / "model.ckpt"
+    g.export_checkpoint(with_state=False).save(ck, 2)
+    lib = C.CDLL(codegen.compile_model(layers, "gelu", "adam", str(tmp_path / "model.infer.so"), infer=True,
+                                       checkpoint=str(ck), use_layernorm=True))
+    fp = C.POINTER(C.c_float)
+    lib.volta_infer.argtypes = [fp, C.c_int64, fp, C.c_int64]
+    lib.volta_infer.restype = None
+    want = g.infer(x)
+    for rows in (1, 64, 1, 200, 64):
+        out = np.full((rows, layers[-1]), np.nan, np.float32)
+        xin = np.ascontiguousarray(x[:rows])
+        lib.volta_infer(xin.ctypes.data_as(fp), xin.size, out.ctypes.data_as(fp), out.size)
+        assert np.array_equal(out, g.infer(xin)), rows
+        assert rel_err(out, want[:rows]) <= 1e-5
+    bad = np.full((1, layers[-1]), 7.0, np.float32)   # lengths that do not fit: a no-op
+    lib.volta_infer(x.ctypes.data_as(fp), 47, bad.ctypes.data_as(fp), bad.size)
+    assert np.all(bad == 7.0)
+    g.free()

@@ -29,7 +29,8 @@ def build_tool(force: bool = False) -> str:
 
 
 def compile_model(layers, activation: str, optimizer: str, out_path: str, emit_only: bool = False, *,
-                  dropout_p: float = 0.0, use_layernorm: bool = False, clip_grad: float = 0.0) -> str:
+                  dropout_p: float = 0.0, use_layernorm: bool = False, clip_grad: float = 0.0,
+                  infer: bool = False, checkpoint: str | None = None) -> str:
     """Emit (and link) the training library for one model; returns the path produced."""
     tool = build_tool()
     cmd = [tool, "--layers", ",".join(str(int(x)) for x in layers), "--activation", activation, "--optimizer",
@@ -40,6 +41,10 @@ def compile_model(layers, activation: str, optimizer: str, out_path: str, emit_o
         cmd.append("--layernorm")
     if clip_grad:
         cmd += ["--clip-grad", repr(float(clip_grad))]
+    if infer:
+        cmd.append("--infer")
+    if checkpoint:
+        cmd += ["--checkpoint", str(checkpoint)]
     if emit_only:
         cmd.append("--emit-only")
     r = subprocess.run(cmd, capture_output=True, text=True)

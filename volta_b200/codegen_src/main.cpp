@@ -9,6 +9,8 @@
 //
 //   volta-b200-codegen --layers 512,1024,1024,512,256,1 --activation relu --optimizer adam
 //                      [--dropout P] [--layernorm] [--clip-grad C]
+//                      [--infer [--checkpoint FILE]]   (inference library exporting volta_infer, the
+//                                                       checkpoint file's bytes embedded in the image)
 //                      -o model.train_cuda.so [--libdir DIR] [--include DIR] [--emit-only]
 #include <cstdio>
 #include <cstdlib>
@@ -30,7 +32,8 @@ static std::string lower(std::string s) {
 
 int main(int argc, char **argv) {
     std::string layers_s, act = "relu", opt = "sgd", out, libdir, incdir;
-    bool emit_only = false, layernorm = false;
+    bool emit_only = false, layernorm = false, infer = false;
+    std::string ckpt;
     double dropout = 0.0, clip = 0.0;   // MlpTopology::dropout_p / use_layernorm / clip_grad
     for (int i = 1; i < argc; ++i) {
         std::string a = argv[i];
@@ -46,6 +49,8 @@ int main(int argc, char **argv) {
         else if (a == "--include") incdir = need("--include");
         else if (a == "--emit-only") emit_only = true;
         else if (a == "--layernorm") layernorm = true;
+        else if (a == "--infer") infer = true;
+        else if (a == "--checkpoint") ckpt = need("--checkpoint");
         else if (a == "--dropout") dropout = atof(need("--dropout").c_str());
         else if (a == "--clip-grad") clip = atof(need("--clip-grad").c_str());
         else { fprintf(stderr, "error: unknown argument '%s'\n", a.c_str()); return 2; }
@@ -74,9 +79,57 @@ int main(int argc, char **argv) {
     if (!(clip >= 0.0)) { fprintf(stderr, "error: --clip-grad must not be negative\n"); return 1; }
     if (out.empty()) { fprintf(stderr, "error: -o <output library> is required\n"); return 2; }
 
+    if (!ckpt.empty()) {
+        if (!infer) { fprintf(stderr, "error: --checkpoint goes with --infer\n"); return 2; }
+        FILE *c = fopen(ckpt.c_str(), "rb");
+        if (!c) { fprintf(stderr, "error: cannot read checkpoint %s\n", ckpt.c_str()); return 1; }
+        fclose(c);
+        for (char ch : ckpt)
+            if (ch == '"' || ch == '\\' || ch == '\n') { fprintf(stderr, "error: checkpoint path must not contain quotes, backslashes or newlines\n"); return 1; }
+    }
     std::string src = out + ".shim.c";
     FILE *f = fopen(src.c_str(), "w");
     if (!f) { fprintf(stderr, "error: cannot write %s\n", src.c_str()); return 1; }
+    if (infer) {
+        // The counterpart of the reference's inference DLL (src/engine/ir/codegen/inner.rs:183-406): weights
+        // embedded, one exported function.  The handle is made on the first call, for at least 64 rows, and
+        // remade when a call brings more rows than it holds.
+        fprintf(f, "/* generated by volta-b200-codegen --infer: layers %s, activation %s */\n", layers_s.c_str(), act.c_str());
+        fprintf(f, "#include <pthread.h>\n#include <string.h>\n#include \"volta_b200.h\"\n#include \"volta_infer.h\"\n\n");
+        fprintf(f, "static const int32_t k_layers[%zu] = {", layers.size());
+        for (size_t i = 0; i < layers.size(); ++i) fprintf(f, "%s%ld", i ? ", " : "", layers[i]);
+        fprintf(f, "};\n");
+        if (!ckpt.empty()) {
+            fprintf(f, "__asm__(\".section .rodata\\n.balign 16\\n.global vb_ckpt_begin\\n.hidden vb_ckpt_begin\\nvb_ckpt_begin:\\n\"\n"
+                       "        \".incbin \\\"%s\\\"\\n.global vb_ckpt_end\\n.hidden vb_ckpt_end\\nvb_ckpt_end:\\n.previous\\n\");\n"
+                       "extern const unsigned char vb_ckpt_begin[] __attribute__((visibility(\"hidden\")));\n"
+                       "extern const unsigned char vb_ckpt_end[] __attribute__((visibility(\"hidden\")));\n", ckpt.c_str());
+        }
+        fprintf(f, "\nstatic vb200_handle *g_h;\nstatic int64_t g_rows;\nstatic pthread_mutex_t g_mu = PTHREAD_MUTEX_INITIALIZER;\n\n"
+                   "static int ensure(int64_t rows) {\n"
+                   "    vb200_config cfg;\n    vb200_handle *h = 0;\n"
+                   "    if (g_h && rows <= g_rows) return 0;\n"
+                   "    if (rows > 0x7fffffff) return 1;\n"
+                   "    memset(&cfg, 0, sizeof cfg);\n"
+                   "    cfg.n_sizes = %zu;\n    memcpy(cfg.layers, k_layers, sizeof k_layers);\n"
+                   "    cfg.activation = %d;\n    cfg.use_layernorm = %d;\n    cfg.batch = rows < 64 ? 64 : (int32_t)rows;\n"
+                   "    if (volta_b200_create(&cfg, &h) != 0) return 1;\n",
+                layers.size(), ai, layernorm ? 1 : 0);
+        if (!ckpt.empty())
+            fprintf(f, "    {\n        vb200_checkpoint *ck = volta_b200_checkpoint_parse(vb_ckpt_begin, (int64_t)(vb_ckpt_end - vb_ckpt_begin));\n"
+                       "        int rc = ck ? volta_b200_import_checkpoint(h, ck) : 1;\n"
+                       "        volta_b200_checkpoint_free(ck);\n"
+                       "        if (rc) { volta_b200_destroy(h); return 1; }\n    }\n");
+        fprintf(f, "    volta_b200_destroy(g_h);\n    g_h = h;\n    g_rows = cfg.batch;\n    return 0;\n}\n\n"
+                   "void volta_infer(float *input, int64_t in_n, float *output, int64_t out_n) {\n"
+                   "    if (!input || !output || in_n <= 0 || in_n %% k_layers[0] != 0) return;\n"
+                   "    pthread_mutex_lock(&g_mu);\n"
+                   "    if (ensure(in_n / k_layers[0]) == 0) volta_b200_infer(g_h, input, in_n, output, out_n);\n"
+                   "    pthread_mutex_unlock(&g_mu);\n}\n");
+        fclose(f);
+        f = nullptr;
+    }
+    if (f) {
     fprintf(f, "/* generated by volta-b200-codegen: layers %s, activation %s, optimizer %s */\n", layers_s.c_str(),
             act.c_str(), opt.c_str());
     fprintf(f, "#include <string.h>\n#include \"volta_b200.h\"\n#include \"volta_train.h\"\n\n");
@@ -99,6 +152,7 @@ int main(int argc, char **argv) {
                "    if (h) volta_b200_step(h, X, Y, lr);\n}\n\n"
                "void volta_train_free(VoltaTrainHandle *h) { volta_b200_destroy(h); }\n");
     fclose(f);
+    }
     if (emit_only) { printf("%s\n", src.c_str()); return 0; }
 
     const char *cc = getenv("CC");
@@ -107,6 +161,7 @@ int main(int argc, char **argv) {
     cmd += " '" + src + "' -o '" + out + "'";
     if (!libdir.empty()) cmd += " -L'" + libdir + "' -Wl,-rpath,'" + libdir + "'";
     cmd += " -lvolta_b200";
+    if (infer) cmd += " -lpthread";
     int rc = system(cmd.c_str());
     if (rc != 0) { fprintf(stderr, "error: compile failed; see %s\n", src.c_str()); return 1; }
     printf("%s\n", out.c_str());

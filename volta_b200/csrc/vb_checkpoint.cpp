@@ -316,12 +316,16 @@ bool checkpoint_save(const Checkpoint &ck, const std::string &path, int format, 
     return fail(err, "unknown checkpoint format (1 = v1 text, 2 = v2 binary)");
 }
 
-bool checkpoint_load(Checkpoint *ck, const std::string &path, std::string *err) {
-    std::string raw;
-    if (!read_file(path, &raw, err)) return false;
+bool checkpoint_parse(Checkpoint *ck, const std::string &raw, std::string *err) {
     ck->entries.clear();
     if (raw.size() >= 8 && memcmp(raw.data(), kMagic, 8) == 0) return from_binary(raw.substr(8), ck, err);
     return from_text(raw, ck, err);
+}
+
+bool checkpoint_load(Checkpoint *ck, const std::string &path, std::string *err) {
+    std::string raw;
+    if (!read_file(path, &raw, err)) return false;
+    return checkpoint_parse(ck, raw, err);
 }
 
 void split_u64(uint64_t v, float out[3]) {

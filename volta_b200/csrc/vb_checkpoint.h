@@ -31,6 +31,8 @@ bool checkpoint_save(const Checkpoint &ck, const std::string &path, int format, 
 // Reads either format (v2 by its magic; v1 with or without its header line, '#' lines skipped,
 // an unknown version refused: checkpoint.rs:46-106, 215-266).
 bool checkpoint_load(Checkpoint *ck, const std::string &path, std::string *err);
+// The same for a file's bytes already in memory.
+bool checkpoint_parse(Checkpoint *ck, const std::string &raw, std::string *err);
 
 // A 64-bit counter as three floats holding 22, 22 and 20 bits, each an exact integer in f32.
 void split_u64(uint64_t v, float out[3]);

@@ -28,14 +28,13 @@ __device__ __forceinline__ unsigned long long global_ns3_() { unsigned long long
 namespace {
 
 constexpr int BM = 128, BN = 256, BK = 32;  // per CTA: 128 rows x 256 columns; the pair covers 256 x 256
-constexpr int RING_SLOTS = 6;                   // 32 KiB slots shared by the two rings
-constexpr int DEFAULT_RAW_STAGES = 4;           // raw tiles stay from load to MMA, low parts only from split to MMA
+constexpr int RAW_STAGES = 4, LO_STAGES = 2;   // raw tiles stay from load to MMA, low parts only from split to MMA
 constexpr int SPLIT_WARPS = 16, SPLIT_THREADS = SPLIT_WARPS * 32;
 constexpr int TMA_WARP = SPLIT_WARPS, MMA_WARP = SPLIT_WARPS + 1;
 constexpr int THREADS = (SPLIT_WARPS + 2) * 32;
 constexpr int TILE_BYTES = 128 * BK * 4;        // 16 KiB
 constexpr int RING_BYTES = 2 * TILE_BYTES;      // one ring slot: A tile + this CTA's half of the B tile
-constexpr int SMEM_TILES = RING_SLOTS * RING_BYTES;
+constexpr int SMEM_TILES = (RAW_STAGES + LO_STAGES) * RING_BYTES;
 constexpr int SMEM_BYTES = SMEM_TILES + 256 + 1024;
 constexpr int TMEM_COLS = 512;                  // 2 accumulator sets x 256 columns
 constexpr int DEFAULT_CHUNK = 4;                // k-blocks per accumulator drain (48 additions per accumulator)
@@ -186,8 +185,7 @@ __device__ __forceinline__ void split_tile(const uint8_t *raw, uint8_t *lo_t, in
 template <bool A_KMAJOR, bool B_KMAJOR>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, long long M,
-                long long N, long long K, int tiles_m, int tiles_n, Epilogue epi, unsigned int *status, int CHUNK, int RAW_STAGES) {
-    const int LO_STAGES = RING_SLOTS - RAW_STAGES;
+                long long N, long long K, int tiles_m, int tiles_n, Epilogue epi, unsigned int *status, int CHUNK) {
     extern __shared__ uint8_t smem_raw[];
     pdl_wait();   // nothing of the previous kernel's output is touched before this
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -460,8 +458,7 @@ cudaError_t launch3(const CUtensorMap &ma, const CUtensorMap &mb, long long m, l
         configured = true;
     }
     static const int chunk = [] { const char *e = getenv("VOLTA_B200_TC_CHUNK"); int v = e ? atoi(e) : DEFAULT_CHUNK; return v < 2 ? 2 : (v > 16 ? 16 : v); }();
-    static const int raw_stages = [] { const char *e = getenv("VOLTA_B200_TC_RAW_STAGES"); int v = e ? atoi(e) : DEFAULT_RAW_STAGES; return v < 2 ? 2 : (v > 4 ? 4 : v); }();
-    return launch_pdl(gemm_tc3_kernel<AK, BKM>, dim3(2 * tiles_m * tiles_n), dim3(THREADS), SMEM_BYTES, s, ma, mb, m, n, k, tiles_m, tiles_n, epi, status, chunk, raw_stages);
+    return launch_pdl(gemm_tc3_kernel<AK, BKM>, dim3(2 * tiles_m * tiles_n), dim3(THREADS), SMEM_BYTES, s, ma, mb, m, n, k, tiles_m, tiles_n, epi, status, chunk);
 }
 
 }  // namespace

@@ -15,6 +15,7 @@
 #include <math.h>
 #include <string.h>
 
+#include <map>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -93,6 +94,9 @@ struct vb200_handle {
     cudaEvent_t ev_join = nullptr;
     std::vector<cudaEvent_t> ev_bucket;
     cudaGraphExec_t graph[2] = {nullptr, nullptr};
+    // inference: pinned staging for host callers and one captured forward graph per row count
+    float *infer_in = nullptr, *infer_out = nullptr;
+    std::map<long long, cudaGraphExec_t> infer_graphs;
     bool use_graph = true;
     bool fuse_sgd = false;   // plain SGD on one GPU: dW GEMMs update W in their epilogue
     int kernels_per_step = 0;
@@ -591,6 +595,10 @@ void destroy(vb200_handle *h) {
             cudaGraphExecDestroy(h->graph[s]);
             h->graph[s] = nullptr;
         }
+    for (auto &kv : h->infer_graphs) cudaGraphExecDestroy(kv.second);
+    h->infer_graphs.clear();
+    if (h->infer_in) cudaFreeHost(h->infer_in);
+    if (h->infer_out) cudaFreeHost(h->infer_out);
     if (h->dp) {
         delete h->dp;
         h->dp = nullptr;
@@ -1084,6 +1092,18 @@ vb200_checkpoint *volta_b200_checkpoint_load(const char *path) {
     return ck;
 }
 
+vb200_checkpoint *volta_b200_checkpoint_parse(const void *bytes, int64_t n) {
+    if (!bytes || n < 0) return nullptr;
+    vb200_checkpoint *ck = new vb200_checkpoint();
+    std::string err;
+    if (!vb::checkpoint_parse(&ck->ck, std::string(static_cast<const char *>(bytes), (size_t)n), &err)) {
+        set_global_error(VB200_ERR_INVALID, err);
+        delete ck;
+        return nullptr;
+    }
+    return ck;
+}
+
 int32_t volta_b200_checkpoint_count(const vb200_checkpoint *ck) { return ck ? (int32_t)ck->ck.entries.size() : 0; }
 
 int volta_b200_checkpoint_entry(const vb200_checkpoint *ck, int32_t i, const char **name, const int64_t **shape,
@@ -1328,12 +1348,53 @@ int volta_b200_infer(vb200_handle *h, const float *in, int64_t in_n, float *out,
     bool idev = false, odev = false;
     if (cudaPointerGetAttributes(&ai, in) == cudaSuccess) idev = ai.type == cudaMemoryTypeDevice || ai.type == cudaMemoryTypeManaged; else cudaGetLastError();
     if (cudaPointerGetAttributes(&ao, out) == cudaSuccess) odev = ao.type == cudaMemoryTypeDevice || ao.type == cudaMemoryTypeManaged; else cudaGetLastError();
-    VB_CUDA(h, cudaMemcpyAsync(h->xin[0], in, (size_t)in_n * 4, idev ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, h->stream));
+    const size_t in_bytes = (size_t)in_n * 4, out_bytes = (size_t)out_n * 4;
+    // Host callers of small batches (the reference's protocol: 10 000 calls of one row, 1 000 of 64;
+    // examples/bench_infer.c) are bound by launch and copy latency: stage through pinned memory and
+    // replay ONE captured graph per row count (copy in, every layer, copy out).
+    const bool staged = !idev && !odev && in_bytes <= (8u << 20) && out_bytes <= (8u << 20) && h->use_graph;
+    if (staged) {
+        if (!h->infer_in) {
+            const size_t cap_in = std::min<size_t>((size_t)h->B * L0 * 4, 8u << 20);
+            const size_t cap_out = std::min<size_t>((size_t)h->B * Ln * 4, 8u << 20);
+            VB_CUDA(h, cudaMallocHost(&h->infer_in, cap_in));
+            VB_CUDA(h, cudaMallocHost(&h->infer_out, cap_out));
+        }
+        auto it = h->infer_graphs.find(rows);
+        if (it == h->infer_graphs.end() && h->infer_graphs.size() < 16) {
+            cudaGraph_t g = nullptr;
+            const int saved = h->kernels_per_step;
+            VB_CUDA(h, cudaStreamBeginCapture(h->stream, cudaStreamCaptureModeThreadLocal));
+            cudaError_t e1 = cudaMemcpyAsync(h->xin[0], h->infer_in, in_bytes, cudaMemcpyHostToDevice, h->stream);
+            int rc = e1 == cudaSuccess ? enqueue_forward(h, 0, rows, false) : VB200_ERR_CUDA;
+            cudaError_t e2 = cudaMemcpyAsync(h->infer_out, h->act[h->n], out_bytes, cudaMemcpyDeviceToHost, h->stream);
+            cudaError_t e3 = cudaStreamEndCapture(h->stream, &g);
+            h->kernels_per_step = saved;
+            if (rc || e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess) {
+                if (g) cudaGraphDestroy(g);
+                cudaGetLastError();
+                return rc ? rc : h->fail(VB200_ERR_CUDA, "infer: capturing the forward graph failed");
+            }
+            cudaGraphExec_t ge = nullptr;
+            cudaError_t e4 = cudaGraphInstantiate(&ge, g, 0);
+            cudaGraphDestroy(g);
+            if (e4 != cudaSuccess) return h->fail(VB200_ERR_CUDA, std::string("infer: cudaGraphInstantiate: ") + cudaGetErrorString(e4));
+            it = h->infer_graphs.emplace(rows, ge).first;
+        }
+        if (it != h->infer_graphs.end()) {
+            memcpy(h->infer_in, in, in_bytes);
+            VB_CUDA(h, cudaGraphLaunch(it->second, h->stream));
+            VB_CUDA(h, cudaStreamSynchronize(h->stream));
+            memcpy(out, h->infer_out, out_bytes);
+            return VB200_OK;
+        }
+    }
+    VB_CUDA(h, cudaMemcpyAsync(h->xin[0], in, in_bytes, idev ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, h->stream));
     const int saved = h->kernels_per_step;
     int rc = enqueue_forward(h, 0, rows, false);
     h->kernels_per_step = saved;
     if (rc) return rc;
-    VB_CUDA(h, cudaMemcpyAsync(out, h->act[h->n], (size_t)out_n * 4, odev ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, h->stream));
+    VB_CUDA(h, cudaMemcpyAsync(out, h->act[h->n], out_bytes, odev ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, h->stream));
     VB_CUDA(h, cudaStreamSynchronize(h->stream));
     return check_device_status(h);
 }

@@ -38,7 +38,7 @@ EXPORTS = [
     "volta_b200_profile_step", "volta_b200_dp_unique_id", "volta_b200_dp_ipc_handle", "volta_b200_dp_attach_peers", "volta_b200_optimizer_apply", "volta_b200_gemm",
     "volta_b200_colsum_scratch_floats", "volta_b200_colsum", "volta_b200_colsum_noalloc", "volta_b200_version",
     "volta_b200_checkpoint_new", "volta_b200_checkpoint_free", "volta_b200_checkpoint_add", "volta_b200_checkpoint_save",
-    "volta_b200_checkpoint_load", "volta_b200_checkpoint_count", "volta_b200_checkpoint_entry",
+    "volta_b200_checkpoint_load", "volta_b200_checkpoint_parse", "volta_b200_checkpoint_count", "volta_b200_checkpoint_entry",
     "volta_b200_export_checkpoint", "volta_b200_import_checkpoint",
 ]
 
@@ -98,6 +98,7 @@ def load_library():
         "volta_b200_checkpoint_add": (C.c_int, [vp, C.c_char_p, C.POINTER(i64), i32, fp]),
         "volta_b200_checkpoint_save": (C.c_int, [vp, C.c_char_p, i32]),
         "volta_b200_checkpoint_load": (vp, [C.c_char_p]),
+        "volta_b200_checkpoint_parse": (vp, [C.c_char_p, i64]),
         "volta_b200_checkpoint_count": (i32, [vp]),
         "volta_b200_checkpoint_entry": (C.c_int, [vp, i32, C.POINTER(C.c_char_p), C.POINTER(C.POINTER(i64)),
                                                   C.POINTER(i32), C.POINTER(fp), C.POINTER(i64)]),
