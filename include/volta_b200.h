@@ -39,7 +39,8 @@ enum { VB200_OPT_SGD = 0, VB200_OPT_ADAM = 1, VB200_OPT_ADAMW = 2, VB200_OPT_ADA
        VB200_OPT_SGD_MOMENTUM = 4 };
 
 /* GEMM path selection. AUTO routes each GEMM by shape (tcgen05 kernel for large ones, FFMA with
- * split-K for small ones).  TENSOR_PAIR is the experimental CTA-pair (cta_group::2) tcgen05 kernel
+ * split-K for small ones, and for forward GEMMs of at most 8 rows - single-sample inference - a
+ * kernel whose CTA clusters split the input features and reduce through distributed shared memory).  TENSOR_PAIR is the experimental CTA-pair (cta_group::2) tcgen05 kernel
  * for outputs of at least 256 x 256; other shapes fall back to TENSOR. */
 enum { VB200_GEMM_AUTO = 0, VB200_GEMM_FFMA = 1, VB200_GEMM_TENSOR = 2, VB200_GEMM_TENSOR_PAIR = 3 };
 

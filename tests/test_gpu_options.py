@@ -197,8 +197,9 @@ def test_infer_applies_softmax_and_layernorm_but_never_dropout(act, ln):
     out = g.infer(x)
     assert close(out, o32.get_act(n).reshape(B, -1), o64.get_act(n).reshape(B, -1))
     assert np.array_equal(out, gd.infer(x))
-    part = g.infer(x[:5])
-    assert np.array_equal(part, out[:5])
+    part = g.infer(x[:5])                     # at most 8 rows: another kernel, same values to rounding
+    assert rel_err(part, out[:5]) <= 1e-5
+    assert np.array_equal(g.infer(x[:16]), out[:16])
     g.free()
     gd.free()
 

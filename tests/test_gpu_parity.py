@@ -506,3 +506,51 @@ def test_sgd_folded_into_the_dw_gemm_matches_the_separate_update(layers, B):
     assert hs[1].kernels_per_step <= hs[0].kernels_per_step + 1
     for h in hs:
         h.free()
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("n,k", [(4, 32), (128, 33), (132, 100), (1000, 512), (1024, 4097), (256, 20000)])
+def test_small_row_cluster_gemm_matches_fp64(m, n, k):
+    """Forward GEMM of at most 8 rows (path AUTO): CTA clusters split k and reduce through distributed
+    shared memory; ragged k (not a multiple of the cluster size), column slabs that end inside a
+    128-column block, and the largest staged input."""
+    lib = load_library()
+    rs = np.random.RandomState(m * 1000 + n + k)
+    a = rs.randn(m, k).astype(np.float32)
+    b = rs.randn(k, n).astype(np.float32)
+    da, db = dev(a), dev(b)
+    out = torch.full((m, n), float("nan"), device="cuda")
+    assert lib.volta_b200_gemm(0, 0, out.data_ptr(), da.data_ptr(), db.data_ptr(), m, n, k, None) == 0
+    torch.cuda.synchronize()
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    scale = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
+    assert np.max(np.abs(out.cpu().numpy() - ref) / scale) <= 4e-7
+    out2 = torch.empty_like(out)
+    assert lib.volta_b200_gemm(0, 0, out2.data_ptr(), da.data_ptr(), db.data_ptr(), m, n, k, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)
+
+
+def test_single_row_inference_reads_and_writes_pinned_memory_directly():
+    """One to eight rows from a host buffer take the graph without copy nodes; the result equals the
+    same rows inferred as part of a larger batch (other kernels) to rounding, and training-mode
+    forward of a one-row handle is the same kernel."""
+    layers = [512, 1024, 1024, 512, 256, 1]
+    g = TrainHandle(layers, "relu", "sgd", 64)
+    x = synth.rows("normal", 3, 0, 64, 512)
+    full = g.infer(x)
+    for rows in (1, 2, 7, 8, 9):
+        part = g.infer(np.ascontiguousarray(x[:rows]))
+        assert part.shape == (rows, 1)
+        assert rel_err(part, full[:rows]) <= 1e-5
+        assert np.array_equal(part, g.infer(np.ascontiguousarray(x[:rows])))
+    xd = torch.from_numpy(x[:1]).cuda()               # device input: the copying path
+    assert rel_err(g.infer(xd), full[:1]) <= 1e-5
+    g.free()
+    wide = TrainHandle([64, 96, 12], "tanh", "sgd", 8)   # last layer wider than one: small-row kernel writes the output
+    xs = synth.rows("normal", 4, 0, 8, 64)
+    o = Oracle([64, 96, 12], "tanh", "sgd", 8)
+    o.grad_step(xs, np.zeros((8, 12), np.float32))
+    assert rel_err(wide.infer(xs), o.get_act(2)) <= 1e-5
+    assert rel_err(wide.infer(xs[:3]), o.get_act(2)[:3]) <= 1e-5
+    wide.free()

@@ -224,6 +224,12 @@ void gemm_tc_select_pair(bool on);
 bool gemm_tc_supported(int layout, const float *A, const float *B, long long m, long long n, long long k,
                        const Epilogue &epi);
 
+// Forward GEMM (NN) for at most 8 rows: one pass over W by clusters of CTAs that reduce through
+// distributed shared memory (vb_gemv.cu).  x may live in pinned host memory.
+bool gemv_rows_supported(const float *W, long long m, long long n, long long k);
+cudaError_t launch_gemv_rows(const float *x, const float *W, long long m, long long n, long long k, const Epilogue &epi,
+                             cudaStream_t s);
+
 cudaError_t launch_optimizer(int optimizer, float *p, float *s1, float *s2, const float *g, long long n,
                              long long n_decay, const StepScalars *sc, cudaStream_t s);
 cudaError_t launch_set_scalars(StepScalars *dst, StepScalars v, cudaStream_t s);

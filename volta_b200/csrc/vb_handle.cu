@@ -186,6 +186,8 @@ struct Scope {
 cudaError_t run_gemm(vb200_handle *h, int layout, const float *A, const float *Bm, long long m, long long n,
                      long long k, const Epilogue &epi) {
     const int path = h->cfg.gemm_path;
+    if (layout == GEMM_NN && path == VB200_GEMM_AUTO && gemv_rows_supported(Bm, m, n, k))
+        return launch_gemv_rows(A, Bm, m, n, k, epi, h->stream);
     if (path != VB200_GEMM_FFMA && gemm_tc_supported(layout, A, Bm, m, n, k, epi) &&
         (path == VB200_GEMM_TENSOR || path == VB200_GEMM_TENSOR_PAIR || gemm_prefers_tc(m, n, k))) {
         gemm_tc_select_pair(path == VB200_GEMM_TENSOR_PAIR);
@@ -198,12 +200,14 @@ cudaError_t run_gemm(vb200_handle *h, int layout, const float *A, const float *B
 
 // Forward pass over the first `rows` rows of input slot `slot` (rows <= batch): every layer's GEMM
 // with bias and activation fused.  Used by the training step (rows = batch) and by inference.
-int enqueue_forward(vb200_handle *h, int slot, long long rows, bool training) {
+int enqueue_forward(vb200_handle *h, int slot, long long rows, bool training, const float *in_override = nullptr,
+                    float *out_override = nullptr) {
     const int n = h->n, act = h->cfg.activation;
     const long long B = rows;
     const std::vector<int> &L = h->L;
     cudaStream_t s = h->stream;
-    const float *act0 = h->xin[slot];
+    const float *act0 = in_override ? in_override : h->xin[slot];
+    float *const last_out = out_override ? out_override : h->act[n];
     auto A = [&](int i) -> float * { return i == 0 ? const_cast<float *>(act0) : h->act[i]; };
     char nm[64];
     for (int i = 0; i < n; ++i) {
@@ -214,7 +218,7 @@ int enqueue_forward(vb200_handle *h, int slot, long long rows, bool training) {
         e.bias = h->params + h->off_b[i];
         if (i == n - 1) {
             e.mode = EPI_BIAS;
-            e.out0 = h->act[n];
+            e.out0 = last_out;
         } else if (act == VB200_ACT_SOFTMAX) {
             e.mode = EPI_BIAS;  // the row kernel below turns the pre-activations into their softmax in place
             e.out0 = h->act[i + 1];
@@ -227,7 +231,7 @@ int enqueue_forward(vb200_handle *h, int slot, long long rows, bool training) {
             // width-one output layer: a row-dot, bandwidth-bound on act_i
             snprintf(nm, sizeof nm, "fwd%d_rowdot_%lldx%lld", i, B, r);
             Scope sc(h, nm, 2.0 * B * r, 4.0 * (B * r + r + B));
-            VB_CUDA(h, launch_rowdot(h->act[n], A(i), h->params + h->off_w[i], e.bias, B, r, s));
+            VB_CUDA(h, launch_rowdot(last_out, A(i), h->params + h->off_w[i], e.bias, B, r, s));
             continue;
         }
         snprintf(nm, sizeof nm, "fwd%d_gemm_nn_%lldx%lldx%lld", i, B, c, r);
@@ -1365,9 +1369,23 @@ int volta_b200_infer(vb200_handle *h, const float *in, int64_t in_n, float *out,
             cudaGraph_t g = nullptr;
             const int saved = h->kernels_per_step;
             VB_CUDA(h, cudaStreamBeginCapture(h->stream, cudaStreamCaptureModeThreadLocal));
-            cudaError_t e1 = cudaMemcpyAsync(h->xin[0], h->infer_in, in_bytes, cudaMemcpyHostToDevice, h->stream);
-            int rc = e1 == cudaSuccess ? enqueue_forward(h, 0, rows, false) : VB200_ERR_CUDA;
-            cudaError_t e2 = cudaMemcpyAsync(h->infer_out, h->act[h->n], out_bytes, cudaMemcpyDeviceToHost, h->stream);
+            // A few rows: the first layer reads the pinned input and the last one writes the pinned output
+            // directly (both are mapped into the device's address space), which saves the two copy nodes.
+            // Only when both layers take kernels that use plain loads and stores (never a TMA descriptor
+            // over host memory): the small-row kernel, or the row-dot of a width-one output.
+            const int nl = h->n;
+            const bool first_ok = h->cfg.gemm_path == VB200_GEMM_AUTO &&
+                                  gemv_rows_supported(h->params + h->off_w[0], rows, h->L[1], h->L[0]);
+            const bool last_ok = h->L[nl] == 1 || (h->cfg.gemm_path == VB200_GEMM_AUTO &&
+                                                   gemv_rows_supported(h->params + h->off_w[nl - 1], rows, h->L[nl], h->L[nl - 1]));
+            const bool direct = rows <= 8 && nl >= 2 && first_ok && last_ok;
+            cudaError_t e1 = direct ? cudaSuccess
+                                    : cudaMemcpyAsync(h->xin[0], h->infer_in, in_bytes, cudaMemcpyHostToDevice, h->stream);
+            int rc = e1 != cudaSuccess ? VB200_ERR_CUDA
+                     : direct          ? enqueue_forward(h, 0, rows, false, h->infer_in, h->infer_out)
+                                       : enqueue_forward(h, 0, rows, false);
+            cudaError_t e2 = direct ? cudaSuccess
+                                    : cudaMemcpyAsync(h->infer_out, h->act[h->n], out_bytes, cudaMemcpyDeviceToHost, h->stream);
             cudaError_t e3 = cudaStreamEndCapture(h->stream, &g);
             h->kernels_per_step = saved;
             if (rc || e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess) {
@@ -1485,6 +1503,8 @@ int volta_b200_gemm(int32_t layout, int32_t path, float *C, const float *A, cons
         if (err == cudaSuccess) err = cudaStreamSynchronize(s);
         cudaFree(st);
         if (err == cudaSuccess && hs != 0) return VB200_ERR_DEVICE_WAIT;
+    } else if (path == VB200_GEMM_AUTO && layout == GEMM_NN && gemv_rows_supported(B, m, n, k)) {
+        err = launch_gemv_rows(A, B, m, n, k, e, s);  // as a handle's forward pass routes at most 8 rows
     } else {
         // same split-K decision as inside a training step, with scratch of this call's own
         float *scratch = nullptr;
