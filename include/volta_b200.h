@@ -251,6 +251,63 @@ int volta_b200_colsum(float *out, const float *in, int64_t rows, int64_t cols, f
  * the GPU - different streams without an ordering between them - race on it. */
 int volta_b200_colsum_noalloc(float *out, const float *in, int64_t rows, int64_t cols, void *stream);
 
+/* ---- Runtime-backend slice -------------------------------------------------------------------
+ * What a `B200Backend` for Volta's runtime would bind (trait Backend, src/engine/ir/backend.rs:24-69):
+ *   compile(plan)                      -> volta_b200_program_add per scheduled node + _compile
+ *   execute_value / execute_terminal   -> _bind the context's inputs and parameters, _run, _fetch
+ *   apply_gradients                    -> _update (parameters stay on the device between steps)
+ * Nodes are added in schedule order (ExecutionPlan.schedule.ordered_nodes), each with the ValueId it
+ * defines, the ValueIds it reads and its inferred shape (rank <= 2).  Op kinds mirror the variants of
+ * the reference's Op enum that its MLP training graphs use (src/engine/ir/op.rs:40-135); semantics are
+ * the interpreter's (src/engine/ir/interpreter.rs:680-880): numpy-style broadcasting for Add/Sub/Mul/Div,
+ * the *Backward ops take (activation input, upstream gradient), Softmax runs over the last axis,
+ * ReduceSum/ReduceMean carry attrs {axis (-1 = all), keepdims}, ConstTensor carries its data in attrs,
+ * Reshape (same element count), Identity and Output share their operand's storage.
+ * Everything else is refused with VB200_ERR_UNSUPPORTED.  Values that must stay readable after a run
+ * (operands of Output nodes, gradients, anything fetched) are marked before compiling; other
+ * temporaries share storage. */
+enum { VB200_OP_INPUT = 0, VB200_OP_PARAMETER = 1, VB200_OP_CONST = 2, VB200_OP_ADD = 3, VB200_OP_SUB = 4,
+       VB200_OP_MUL = 5, VB200_OP_DIV = 6, VB200_OP_NEG = 7, VB200_OP_TRANSPOSE = 8, VB200_OP_MATMUL = 9,
+       VB200_OP_RELU = 10, VB200_OP_RELU_BACKWARD = 11, VB200_OP_SIGMOID = 12, VB200_OP_SIGMOID_BACKWARD = 13,
+       VB200_OP_GELU = 14, VB200_OP_GELU_BACKWARD = 15, VB200_OP_SOFTMAX = 16, VB200_OP_LOG = 17, VB200_OP_EXP = 18,
+       VB200_OP_REDUCE_SUM = 19, VB200_OP_REDUCE_MEAN = 20, VB200_OP_IDENTITY = 21, VB200_OP_OUTPUT = 22,
+       VB200_OP_RESHAPE = 23 };
+
+/* CompiledProgram (backend.rs:12-17) plus what the fused lowering did. */
+typedef struct vb200_compiled_program {
+    int64_t schedule_len;    /* nodes given */
+    int64_t launches;        /* kernels the schedule became (Transpose folded into GEMM layouts, bias/activation
+                                and activation-backward folded into GEMM epilogues when fuse != 0) */
+    int64_t peak_bytes;      /* the arena */
+    int64_t unshared_bytes;  /* what it would take without storage reuse */
+    uint64_t fingerprint;    /* identity of the schedule (FNV-1a; not the reference's SipHash) */
+} vb200_compiled_program;
+
+/* OptimizerConfig (src/engine/ir/optimizer.rs:38-80); zero betas/eps/momentum select 0.9 / 0.999 / 1e-8 / 0.9. */
+typedef struct vb200_optimizer_config {
+    int32_t optimizer;       /* VB200_OPT_* */
+    float lr, beta1, beta2, eps, weight_decay, momentum;
+} vb200_optimizer_config;
+
+typedef struct vb200_program vb200_program;
+vb200_program *volta_b200_program_new(void);
+void volta_b200_program_free(vb200_program *p);
+const char *volta_b200_program_error(vb200_program *p);
+int volta_b200_program_add(vb200_program *p, int32_t kind, int32_t value_id, const int32_t *inputs, int32_t n_inputs,
+                           const int64_t *shape, int32_t ndim, const float *attrs, int32_t n_attrs);
+int volta_b200_program_mark_output(vb200_program *p, int32_t value_id);
+/* Plans the arena, lowers and captures the schedule; needs a GPU.  fuse = 0 keeps one kernel per node. */
+int volta_b200_program_compile(vb200_program *p, int32_t fuse, vb200_compiled_program *info);
+/* Inputs and parameters by ValueId (the ExecutionContext); host or device pointer, n floats. */
+int volta_b200_program_bind(vb200_program *p, int32_t value_id, const float *data, int64_t n);
+int volta_b200_program_run(vb200_program *p);
+int volta_b200_program_fetch(vb200_program *p, int32_t value_id, float *out, int64_t n);
+/* apply_gradients (backend.rs:28-41; formulas of src/engine/ir/optimizer.rs:212-244, 329-340, 429-441,
+ * 592-600): updates each parameter in place from its gradient value; moments live with the program.
+ * `step` is the 1-based update count (Adam's bias corrections). */
+int volta_b200_program_update(vb200_program *p, const vb200_optimizer_config *cfg, const int32_t *param_ids,
+                              const int32_t *grad_ids, int32_t count, uint64_t step);
+
 const char *volta_b200_version(void);
 
 #ifdef __cplusplus

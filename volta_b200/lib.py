@@ -25,6 +25,16 @@ class Config(C.Structure):
     ]
 
 
+class CompiledProgram(C.Structure):
+    _fields_ = [("schedule_len", C.c_int64), ("launches", C.c_int64), ("peak_bytes", C.c_int64),
+                ("unshared_bytes", C.c_int64), ("fingerprint", C.c_uint64)]
+
+
+class OptimizerConfig(C.Structure):
+    _fields_ = [("optimizer", C.c_int32), ("lr", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float),
+                ("eps", C.c_float), ("weight_decay", C.c_float), ("momentum", C.c_float)]
+
+
 class KernelRecord(C.Structure):
     _fields_ = [("name", C.c_char * 48), ("ms", C.c_float), ("flops", C.c_double), ("bytes", C.c_double)]
 
@@ -40,6 +50,9 @@ EXPORTS = [
     "volta_b200_checkpoint_new", "volta_b200_checkpoint_free", "volta_b200_checkpoint_add", "volta_b200_checkpoint_save",
     "volta_b200_checkpoint_load", "volta_b200_checkpoint_parse", "volta_b200_checkpoint_count", "volta_b200_checkpoint_entry",
     "volta_b200_export_checkpoint", "volta_b200_import_checkpoint",
+    "volta_b200_program_new", "volta_b200_program_free", "volta_b200_program_error", "volta_b200_program_add",
+    "volta_b200_program_mark_output", "volta_b200_program_compile", "volta_b200_program_bind", "volta_b200_program_run",
+    "volta_b200_program_fetch", "volta_b200_program_update",
 ]
 
 _lib = None
@@ -104,6 +117,16 @@ def load_library():
                                                   C.POINTER(i32), C.POINTER(fp), C.POINTER(i64)]),
         "volta_b200_export_checkpoint": (C.c_int, [vp, vp, i32]),
         "volta_b200_import_checkpoint": (C.c_int, [vp, vp]),
+        "volta_b200_program_new": (vp, []),
+        "volta_b200_program_free": (None, [vp]),
+        "volta_b200_program_error": (C.c_char_p, [vp]),
+        "volta_b200_program_add": (C.c_int, [vp, i32, i32, C.POINTER(i32), i32, C.POINTER(i64), i32, fp, i32]),
+        "volta_b200_program_mark_output": (C.c_int, [vp, i32]),
+        "volta_b200_program_compile": (C.c_int, [vp, i32, C.POINTER(CompiledProgram)]),
+        "volta_b200_program_bind": (C.c_int, [vp, i32, vp, i64]),
+        "volta_b200_program_run": (C.c_int, [vp]),
+        "volta_b200_program_fetch": (C.c_int, [vp, i32, vp, i64]),
+        "volta_b200_program_update": (C.c_int, [vp, C.POINTER(OptimizerConfig), C.POINTER(i32), C.POINTER(i32), i32, C.c_uint64]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
