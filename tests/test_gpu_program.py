@@ -84,7 +84,7 @@ def test_reductions(kind, shape, axis, keep):
     g = GraphBuilder()
     a = g.input(shape)
     out = getattr(g, kind)(a, axis, keep)
-    feed = {a: rs.randn(*shape).astype(np.float32)}
+    feed = {a: np.asarray(rs.randn(*shape), np.float32)}
     got, _ = run_graph(g, feed, [out])
     want = evaluate(g, feed)[out]
     scale = float(np.sum(np.abs(feed[a]), axis=axis).max()) / (1 if kind == "reduce_sum" else max(1, feed[a].size if axis is None else (shape[axis] if shape else 1)))
