@@ -262,7 +262,8 @@ int volta_b200_colsum_noalloc(float *out, const float *in, int64_t rows, int64_t
  * the interpreter's (src/engine/ir/interpreter.rs:680-880): numpy-style broadcasting for Add/Sub/Mul/Div,
  * the *Backward ops take (activation input, upstream gradient), Softmax runs over the last axis,
  * ReduceSum/ReduceMean carry attrs {axis (-1 = all), keepdims}, ConstTensor carries its data in attrs,
- * Reshape (same element count), Identity and Output share their operand's storage.
+ * Reshape (same element count), Identity and Output share their operand's storage, SOFTMAX_XENT is
+ * SoftmaxCrossEntropyLossFromLogits {logits, targets} -> scalar mean over the batch (interpreter.rs:776-815).
  * Everything else is refused with VB200_ERR_UNSUPPORTED.  Values that must stay readable after a run
  * (operands of Output nodes, gradients, anything fetched) are marked before compiling; other
  * temporaries share storage. */
@@ -271,7 +272,7 @@ enum { VB200_OP_INPUT = 0, VB200_OP_PARAMETER = 1, VB200_OP_CONST = 2, VB200_OP_
        VB200_OP_RELU = 10, VB200_OP_RELU_BACKWARD = 11, VB200_OP_SIGMOID = 12, VB200_OP_SIGMOID_BACKWARD = 13,
        VB200_OP_GELU = 14, VB200_OP_GELU_BACKWARD = 15, VB200_OP_SOFTMAX = 16, VB200_OP_LOG = 17, VB200_OP_EXP = 18,
        VB200_OP_REDUCE_SUM = 19, VB200_OP_REDUCE_MEAN = 20, VB200_OP_IDENTITY = 21, VB200_OP_OUTPUT = 22,
-       VB200_OP_RESHAPE = 23 };
+       VB200_OP_RESHAPE = 23, VB200_OP_SOFTMAX_XENT = 24 };
 
 /* CompiledProgram (backend.rs:12-17) plus what the fused lowering did. */
 typedef struct vb200_compiled_program {

@@ -53,6 +53,10 @@ def evaluate(g, feed):
         elif kind in ("reduce_sum", "reduce_mean"):
             axis = None if attrs[0] < 0 else int(attrs[0])
             r = (np.sum if kind == "reduce_sum" else np.mean)(a[0], axis=axis, keepdims=bool(attrs[1]))
+        elif kind == "softmax_xent":
+            m = a[0].max(axis=1, keepdims=True)
+            lse = m + np.log(np.exp(a[0] - m).sum(axis=1, keepdims=True))
+            r = np.mean(-(a[1] * (a[0] - lse)).sum(axis=1))
         elif kind in ("identity", "output"): r = a[0]
         elif kind == "reshape": r = a[0].reshape(shape)
         else: raise NotImplementedError(kind)

@@ -140,6 +140,35 @@ def test_mlp_training_graph_fused_and_unfused_match_numpy(activation, layers, ba
             assert close(fused[grads[2 * i]], gw[i], 1e-5) and close(fused[grads[2 * i + 1]].ravel(), gb[i], 1e-5)
 
 
+@pytest.mark.parametrize("batch,classes", [(6, 5), (64, 10), (700, 1000), (3000, 37)])
+def test_softmax_cross_entropy_loss_and_its_gradient(batch, classes):
+    """SoftmaxCrossEntropyLossFromLogits (interpreter.rs:776-815) with one-hot targets behind a small classifier,
+    and the gradient nodes autograd.rs:467-530 emits for it (Softmax, Sub, Div by the batch size, Mul)."""
+    rs = np.random.RandomState(batch)
+    g = GraphBuilder()
+    x, t = g.input((batch, 24)), g.input((batch, classes))
+    logits, params = g.mlp([24, 48, classes], "relu", x)
+    loss = g.softmax_xent(logits, t)
+    grads = g.backward(loss, params)
+    feed = {x: rs.randn(batch, 24).astype(np.float32), t: np.eye(classes, dtype=np.float32)[rs.randint(0, classes, batch)]}
+    ws, bs = synth.kaiming_uniform_weights([24, 48, classes], 42)
+    for i in range(2):
+        feed[params[2 * i]], feed[params[2 * i + 1]] = ws[i], (rs.randn(1, ws[i].shape[1]) * 0.1).astype(np.float32)
+    want = evaluate(g, feed)
+    got, _ = run_graph(g, feed, [loss] + grads)
+    assert got[loss].shape == () and abs(float(got[loss]) - float(want[loss])) <= 2e-6 * abs(float(want[loss]))
+    for v in grads:
+        assert close(got[v], want[v], 1e-5)
+    import torch
+    tw = [torch.tensor(feed[p_], dtype=torch.float64, requires_grad=True) for p_ in params]
+    h = torch.relu(torch.tensor(feed[x], dtype=torch.float64) @ tw[0] + tw[1]) @ tw[2] + tw[3]
+    ref = torch.nn.functional.cross_entropy(h, torch.tensor(feed[t].argmax(axis=1)))
+    ref.backward()
+    assert abs(float(got[loss]) - float(ref.detach())) <= 1e-5 * abs(float(ref.detach()))
+    for v, w in zip(grads, tw):
+        assert close(got[v], w.grad.numpy(), 1e-5)
+
+
 def fixture_program(activation="relu"):
     g = GraphBuilder()
     B, L = GOLD["batch"], GOLD["layers"]

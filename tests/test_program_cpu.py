@@ -53,6 +53,7 @@ def test_fingerprint_tells_schedules_apart():
     (lambda p: (p.add("input", 0, (), (2, 3)), p.add("reduce_sum", 1, (0,), (2,), (0, 0))), "output shape mismatch"),
     (lambda p: (p.add("input", 0, (), (2, 3)), p.add("reshape", 1, (0,), (4, 2))), "changes the element count"),
     (lambda p: p.add("input", 0, (), (2, 3, 4)), "rank above 2"),
+    (lambda p: (p.add("input", 0, (), (2, 3)), p.add("input", 1, (), (2, 4)), p.add("softmax_xent", 2, (0, 1), ())), "SoftmaxCrossEntropyLossFromLogits"),
     (lambda p: p.add("const", 0, (), (2, 2), (1.0, 2.0)), "does not match its shape"),
     (lambda p: p.add(99, 0, (), (2, 2)), "unsupported op kind"),
     (lambda p: p.mark_output(3), "unknown value"),

@@ -5,7 +5,7 @@
 // The op set is the one the runtime's MLP training graphs use (src/engine/ir/lowering.rs:90-140 forward,
 // src/engine/ir/autograd.rs:119-450 backward): Input, Parameter, ConstTensor, Add, Sub, Mul, Div, Neg,
 // Transpose, MatMul, Relu, ReluBackward, Sigmoid, SigmoidBackward, Gelu, GeluBackward, Softmax, Log, Exp,
-// ReduceSum, ReduceMean, Reshape, Identity, Output - semantics as src/engine/ir/interpreter.rs:680-880 and
+// ReduceSum, ReduceMean, SoftmaxCrossEntropyLossFromLogits, Reshape, Identity, Output - semantics as src/engine/ir/interpreter.rs:680-880 and
 // src/engine/ir/kernels/{activations,reduce,utils}.rs (numpy-style broadcasting of rank <= 2).
 //
 // Where the reference interprets node by node with a host tensor per value (and its CUDA executor moves
@@ -166,6 +166,33 @@ __global__ void __launch_bounds__(256) scale_kernel(float *__restrict__ v, long 
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += stride) v[e] *= scale;
 }
 
+// Per-row softmax cross-entropy from logits (interpreter.rs:776-815): loss[row] = -sum_j t[j] * (x[j] - lse(x)),
+// lse = max + ln(sum exp(x - max)).  One warp per row; the mean over rows follows as a fixed-order sum.
+__global__ void __launch_bounds__(256) xent_rows_kernel(float *__restrict__ row_loss, const float *__restrict__ logits,
+                                                        const float *__restrict__ targets, long long R, long long C) {
+    pdl_wait();
+    pdl_trigger();
+    const int lane = threadIdx.x & 31;
+    const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long row = (((long long)blockIdx.x * blockDim.x) + threadIdx.x) >> 5; row < R; row += warps) {
+        const float *x = logits + row * C, *t = targets + row * C;
+        float mx = -INFINITY;
+        for (long long c = lane; c < C; c += 32) mx = fmaxf(mx, x[c]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float se = 0.0f;
+        for (long long c = lane; c < C; c += 32) se += expf(x[c] - mx);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) se += __shfl_xor_sync(0xffffffffu, se, o);
+        const float lse = mx + logf(se);
+        float acc = 0.0f;
+        for (long long c = lane; c < C; c += 32) acc -= t[c] * (x[c] - lse);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+        if (lane == 0) row_loss[row] = acc;
+    }
+}
+
 int grid_for(long long n) {
     long long want = (n + 255) / 256;
     return (int)std::max<long long>(1, std::min<long long>(want, 148 * 8));
@@ -188,7 +215,7 @@ struct PValue {
     float *dev = nullptr;
 };
 
-enum LaunchKind { L_BINARY, L_UNARY, L_TRANSPOSE, L_GEMM, L_SOFTMAX, L_REDUCE };
+enum LaunchKind { L_BINARY, L_UNARY, L_TRANSPOSE, L_GEMM, L_SOFTMAX, L_REDUCE, L_XENT };
 
 struct Launch {
     LaunchKind kind;
@@ -296,6 +323,10 @@ int check_node(vb200_program *p, const PValue &v) {
     case VB200_OP_IDENTITY: case VB200_OP_OUTPUT:
         if (!need(1) || in(0).shape != v.shape) return p->fail(VB200_ERR_INVALID, "Shape mismatch in " + describe(v));
         return VB200_OK;
+    case VB200_OP_SOFTMAX_XENT:
+        if (!need(2) || in(0).shape.size() != 2 || in(0).shape != in(1).shape || !v.shape.empty())
+            return p->fail(VB200_ERR_INVALID, "Shape mismatch in SoftmaxCrossEntropyLossFromLogits: " + describe(v));
+        return VB200_OK;
     case VB200_OP_RESHAPE:
         if (!need(1) || in(0).count != v.count) return p->fail(VB200_ERR_INVALID, "Reshape changes the element count: " + describe(v));
         return VB200_OK;
@@ -386,6 +417,17 @@ int enqueue(vb200_program *p) {
             VP_CUDA(p, launch_row_forward(dev(l.out), o.R, (int)o.C, rf, p->scalars, s));
             break;
         }
+        case L_XENT: {
+            const PValue &a = p->values[(size_t)l.a];
+            float *rows = p->reduce_scratch, *blocks = p->reduce_scratch + a.R;
+            const long long want = (a.R + 7) / 8, nb = loss_blocks(a.R);
+            VP_CUDA(p, launch_pdl(xent_rows_kernel, dim3((unsigned)std::max<long long>(1, std::min<long long>(want, 148 * 8))), dim3(256),
+                                  0, s, rows, (const float *)dev(l.a), (const float *)dev(l.b), a.R, a.C));
+            VP_CUDA(p, launch_pdl(sum_blocks_kernel, dim3((unsigned)nb), dim3(256), 0, s, blocks, (const float *)rows, a.R));
+            VP_CUDA(p, launch_pdl(sum_final_kernel, dim3(1), dim3(256), 0, s, dev(l.out), (const float *)blocks, nb,
+                                  1.0f / (float)a.R));   // mean over the batch
+            break;
+        }
         case L_REDUCE: {
             const PValue &a = p->values[(size_t)l.a];
             if (l.axis < 0) {  // everything -> one number
@@ -471,6 +513,11 @@ int lower(vb200_program *p) {
         case VB200_OP_SOFTMAX:
             l.kind = L_SOFTMAX;
             l.a = val.in[0];
+            break;
+        case VB200_OP_SOFTMAX_XENT:
+            l.kind = L_XENT;
+            l.a = val.in[0];
+            l.b = val.in[1];
             break;
         case VB200_OP_TRANSPOSE: {
             bool needed = val.keep || users[(size_t)v].empty();
@@ -648,6 +695,10 @@ int volta_b200_program_compile(vb200_program *p, int32_t fuse, vb200_compiled_pr
         if (l.kind == L_REDUCE) {
             const PValue &a = p->values[(size_t)l.a];
             red = std::max(red, l.axis < 0 ? loss_blocks(a.count) : colsum_chunks(a.R, a.C) * a.C);
+        }
+        if (l.kind == L_XENT) {
+            const PValue &a = p->values[(size_t)l.a];
+            red = std::max(red, a.R + loss_blocks(a.R));
         }
         if (l.kind == L_GEMM) gs = std::max(gs, ffma_scratch_floats(l.m, l.n, l.k));
     }

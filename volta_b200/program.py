@@ -20,7 +20,7 @@ from .train import OPTIMIZERS, _ptr
 OPS = {"input": 0, "parameter": 1, "const": 2, "add": 3, "sub": 4, "mul": 5, "div": 6, "neg": 7, "transpose": 8,
        "matmul": 9, "relu": 10, "relu_backward": 11, "sigmoid": 12, "sigmoid_backward": 13, "gelu": 14,
        "gelu_backward": 15, "softmax": 16, "log": 17, "exp": 18, "reduce_sum": 19, "reduce_mean": 20, "identity": 21,
-       "output": 22, "reshape": 23}
+       "output": 22, "reshape": 23, "softmax_xent": 24}
 
 
 class Program:
@@ -151,6 +151,12 @@ class GraphBuilder:
 
     def reshape(self, a, shape): return self._push("reshape", (a,), shape)
 
+    def softmax_xent(self, logits, targets):
+        """SoftmaxCrossEntropyLossFromLogits (lowering.rs:156-170): scalar mean over the batch."""
+        if self.shape[logits] != self.shape[targets] or len(self.shape[logits]) != 2:
+            raise ValueError("Shape mismatch in SoftmaxCrossEntropyLossFromLogits")
+        return self._push("softmax_xent", (logits, targets), ())
+
     def _reduce(self, kind, a, axis, keepdims):
         s = self.shape[a]
         if axis is None:
@@ -232,6 +238,12 @@ class GraphBuilder:
                 acc(ins[0], self.transpose(up))
             elif kind in ("reshape", "identity", "output"):
                 acc(ins[0], up if kind != "reshape" else self.reshape(up, self.shape[ins[0]]))
+            elif kind == "softmax_xent":
+                # autograd.rs:467-530: (softmax(logits) - targets) / batch, times the upstream scalar; no
+                # gradient flows to the targets
+                diff = self.sub(self.softmax(ins[0]), ins[1])
+                bs = self.const(np.float32(self.shape[ins[0]][0]))
+                acc(ins[0], self.mul(self.div(diff, bs), up))
             elif kind == "reduce_mean" and attrs[0] < 0:
                 n = int(np.prod(self.shape[ins[0]]))
                 ones = self.const(np.ones(self.shape[ins[0]], np.float32))
