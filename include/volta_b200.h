@@ -299,7 +299,9 @@ int volta_b200_program_add(vb200_program *p, int32_t kind, int32_t value_id, con
 int volta_b200_program_mark_output(vb200_program *p, int32_t value_id);
 /* Plans the arena, lowers and captures the schedule; needs a GPU.  fuse = 0 keeps one kernel per node. */
 int volta_b200_program_compile(vb200_program *p, int32_t fuse, vb200_compiled_program *info);
-/* Inputs and parameters by ValueId (the ExecutionContext); host or device pointer, n floats. */
+/* Inputs and parameters by ValueId (the ExecutionContext); host or device pointer, n floats.  A host buffer
+ * is consumed before the call returns; a device buffer is copied on the program's stream and must stay
+ * unchanged until the next _fetch (or any other call that waits for the program) has returned. */
 int volta_b200_program_bind(vb200_program *p, int32_t value_id, const float *data, int64_t n);
 int volta_b200_program_run(vb200_program *p);
 int volta_b200_program_fetch(vb200_program *p, int32_t value_id, float *out, int64_t n);

@@ -554,3 +554,20 @@ def test_single_row_inference_reads_and_writes_pinned_memory_directly():
     assert rel_err(wide.infer(xs), o.get_act(2)) <= 1e-5
     assert rel_err(wide.infer(xs[:3]), o.get_act(2)[:3]) <= 1e-5
     wide.free()
+
+
+def test_infer_with_more_row_counts_than_cached_graphs():
+    """Every row count gets its own captured forward graph up to a limit (16); beyond it calls take
+    plain launches.  All of them must agree with the same rows inferred inside the full batch."""
+    layers = [40, 96, 64, 4]
+    g = TrainHandle(layers, "silu", "sgd", 48)
+    x = synth.rows("normal", 8, 0, 48, 40)
+    full = g.infer(x)
+    for rows in list(range(1, 41)) + [3, 17, 40, 1]:
+        part = g.infer(np.ascontiguousarray(x[:rows]))
+        assert part.shape == (rows, 4) and rel_err(part, full[:rows]) <= 1e-5, rows
+    g.step(x, np.zeros((48, 4), np.float32), 0.05)          # weights change; the cached graphs read them afresh
+    after = g.infer(x)
+    assert rel_err(after, full) > 1e-4
+    assert rel_err(g.infer(np.ascontiguousarray(x[:5])), after[:5]) <= 1e-5
+    g.free()

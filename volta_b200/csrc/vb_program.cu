@@ -243,7 +243,7 @@ struct vb200_program {
     StepScalars *scalars = nullptr;
     cudaStream_t stream = nullptr;
     cudaGraphExec_t graph = nullptr;
-    bool compiled = false, fuse = true;
+    bool compiled = false, attempted = false, fuse = true;
     std::map<int, std::pair<float *, float *>> opt_state;   // parameter index -> moments (outside the arena)
     std::string error;
 
@@ -659,7 +659,9 @@ int volta_b200_program_mark_output(vb200_program *p, int32_t value_id) {
 int volta_b200_program_compile(vb200_program *p, int32_t fuse, vb200_compiled_program *info) {
     if (!p) return VB200_ERR_INVALID;
     if (p->compiled) return p->fail(VB200_ERR_INVALID, "compile: already compiled");
+    if (p->attempted) return p->fail(VB200_ERR_INVALID, "compile: an earlier attempt failed; build a new program");
     if (p->values.empty()) return p->fail(VB200_ERR_INVALID, "compile: empty program");
+    p->attempted = true;
     p->fuse = fuse != 0;
     const int nv = (int)p->values.size();
     // operands of Output nodes stay valid, like marked values; a kept alias keeps what it aliases
