@@ -386,21 +386,35 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (tid == 0) pdl_trigger();   // the next kernel's CTAs may take SMs as ours retire
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
-            const long long m = m0 + q * 32 + lane;
+            // Each thread holds one row's 64 sums.  Stored from there, a warp's float4 store would touch 32 rows
+            // (32 half-used sectors); instead the warp passes its 32 x 64 block through shared memory (every ring
+            // slot is idle once the last accumulator set is full: no MMA, of either CTA, reads them any more)
+            // and stores two whole 256-byte row segments per instruction.
+            constexpr int ST_LD = 68;   // floats per staged row: 16-byte aligned, four wavefronts per float4 write
+            float *stage = reinterpret_cast<float *>(smem) + warp * (32 * ST_LD);
+#pragma unroll
+            for (int j = 0; j < 64; j += 4)
+                *reinterpret_cast<float4 *>(stage + lane * ST_LD + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+            __syncwarp();
             const bool vec_ok = ((epi.ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(epi.out0) & 15) == 0) &&
                                 (!epi.out1 || (reinterpret_cast<uintptr_t>(epi.out1) & 15) == 0) &&
                                 (!epi.saved || (reinterpret_cast<uintptr_t>(epi.saved) & 15) == 0) &&
                                 (!epi.bias || (reinterpret_cast<uintptr_t>(epi.bias) & 15) == 0);
-            if (m < M) {
-#pragma unroll
-                for (int j = 0; j < 64; j += 4) {
-                    const long long n = n0 + cg * 64 + j;
+            const int half = lane >> 4, c4 = (lane & 15) * 4;
+            const long long n = n0 + cg * 64 + c4;
+#pragma unroll 4
+            for (int it = 0; it < 16; ++it) {
+                const int r = it * 2 + half;
+                const float4 v = *reinterpret_cast<const float4 *>(stage + r * ST_LD + c4);
+                const long long m = m0 + q * 32 + r;
+                if (m < M) {
                     if (vec_ok && n + 3 < N) {
-                        epi.apply4(m, n, make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]));
+                        epi.apply4(m, n, v);
                     } else {
-#pragma unroll
-                        for (int jj = 0; jj < 4; ++jj)
-                            if (n + jj < N) epi.apply(m, n + jj, acc[j + jj]);
+                        if (n + 0 < N) epi.apply(m, n + 0, v.x);
+                        if (n + 1 < N) epi.apply(m, n + 1, v.y);
+                        if (n + 2 < N) epi.apply(m, n + 2, v.z);
+                        if (n + 3 < N) epi.apply(m, n + 3, v.w);
                     }
                 }
             }
