@@ -47,9 +47,10 @@ def measured_peaks():
 # the ncu capture summarised in profiles/gemm_tc3_pair_c4_batch8192.md (taken at batch 8192; traffic
 # of these GEMMs grows in proportion to the batch, so a full launch is rows x this figure).
 NCU_TRAFFIC_PER_ROW = {
-    "fwd_gemm_nn_Bx4096x4096": (688.751872e6 + 297.116416e6) / 8192,
-    "fwd_gemm_nn_Bx1024x4096": (210.639872e6 + 50.569216e6) / 8192,
-    "dW_gemm_tn_4096x1024xB": (168.156160e6 + 5.256448e6) / 8192,
+    "fwd_gemm_nn_Bx4096x4096": (620.196096e6 + 245.701376e6) / 8192,
+    "fwd_gemm_nn_Bx1024x4096": (200.767232e6 + 44.852224e6) / 8192,
+    "dX_gemm_nt_Bx4096x4096": (754.354176e6 + 131.911168e6) / 8192,
+    "dW_gemm_tn_4096x4096xB": (628.525824e6 + 67.879424e6) / 8192,
 }
 
 
