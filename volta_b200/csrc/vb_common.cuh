@@ -214,12 +214,20 @@ long long ffma_scratch_floats(long long m, long long n, long long k);
 // Shape heuristic: true when the tensor-core kernel is expected to beat the FFMA path.
 bool gemm_prefers_tc(long long m, long long n, long long k);
 // Returns cudaErrorNotSupported when the shape/alignment cannot take the tensor path.
+// `scratch` (gemm_tc_scratch_floats floats, may be null) lets a GEMM whose tiles fill the last wave badly
+// split K over concurrent CTAs; the slabs are then added in split order by launch_splitk_reduce.
 cudaError_t launch_gemm_tc(int layout, const float *A, const float *B, long long m, long long n, long long k,
-                           const Epilogue &epi, unsigned int *status_word, cudaStream_t s);
+                           const Epilogue &epi, unsigned int *status_word, cudaStream_t s, float *scratch = nullptr,
+                           long long scratch_floats = 0);
+int gemm_tc_splits(int layout, long long m, long long n, long long k);
+long long gemm_tc_scratch_floats(int layout, long long m, long long n, long long k);
+// out = epilogue(sum over z of partial[z][m x n]), z ascending
+cudaError_t launch_splitk_reduce(const float *partial, long long m, long long n, int splits, const Epilogue &epi,
+                                 cudaStream_t s);
 cudaError_t launch_gemm_tc2(int layout, const float *A, const float *B, long long m, long long n, long long k,
                             const Epilogue &epi, unsigned int *status_word, cudaStream_t s);
 cudaError_t launch_gemm_tc3(int layout, const float *A, const float *B, long long m, long long n, long long k,
-                            const Epilogue &epi, unsigned int *status_word, cudaStream_t s);
+                            const Epilogue &epi, unsigned int *status_word, cudaStream_t s, int splits = 1);
 void gemm_tc_select_pair(bool on);
 bool gemm_tc_supported(int layout, const float *A, const float *B, long long m, long long n, long long k,
                        const Epilogue &epi);

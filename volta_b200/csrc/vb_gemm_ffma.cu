@@ -158,6 +158,39 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
     }
 }
 
+// Same for four consecutive columns (N a multiple of 4, everything 16-byte aligned).
+__global__ void __launch_bounds__(256) splitk_reduce4_kernel(const float *__restrict__ partial, long long M, long long N,
+                                                             int splits, Epilogue epi) {
+    pdl_wait();
+    pdl_trigger();
+    const long long total4 = (M * N) >> 2;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
+        float4 v = __ldcs(reinterpret_cast<const float4 *>(partial) + i);
+        for (int z = 1; z < splits; ++z) {
+            const float4 w = __ldcs(reinterpret_cast<const float4 *>(partial) + (long long)z * total4 + i);
+            v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+        }
+        const long long idx = i << 2;
+        epi.apply4(idx / N, idx % N, v);
+    }
+}
+
+cudaError_t launch_splitk_reduce(const float *partial, long long m, long long n, int splits, const Epilogue &epi,
+                                 cudaStream_t s) {
+    const long long total = m * n;
+    const bool vec = (n & 3) == 0 && (epi.ld & 3) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(partial) | reinterpret_cast<uintptr_t>(epi.out0) |
+                       reinterpret_cast<uintptr_t>(epi.out1) | reinterpret_cast<uintptr_t>(epi.bias) |
+                       reinterpret_cast<uintptr_t>(epi.saved)) & 15) == 0;
+    if (vec) {
+        const long long want = ((total >> 2) + 255) / 256;
+        return launch_pdl(splitk_reduce4_kernel, dim3((unsigned)(want < 1184 ? (want < 1 ? 1 : want) : 1184)), dim3(256), 0, s, partial,
+                          m, n, splits, epi);
+    }
+    const long long want = (total + 255) / 256;
+    return launch_pdl(splitk_reduce_kernel, dim3((unsigned)(want < 1184 ? want : 1184)), dim3(256), 0, s, partial, m, n, splits, epi);
+}
+
 // How many K splits the FFMA path uses for a shape: enough CTAs to occupy the GPU when the
 // output alone gives too few tiles (the batch-64 configurations), never fewer than 64 k per
 // split.  A function of the shape only, so results are reproducible.

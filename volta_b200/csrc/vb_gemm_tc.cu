@@ -467,9 +467,51 @@ bool gemm_tc_supported(int layout, const float *A, const float *B, long long m, 
     return encode_fn() != nullptr;
 }
 
+namespace {
+bool routes_to_pair(long long m, long long n) {
+    static const int version = env_int("VOLTA_B200_TC_VERSION", 3);
+    const long long pair_ctas = 2 * ((m + 255) / 256) * ((n + 255) / 256);
+    return m >= 256 && n >= 256 && (g_force_pair || (version == 3 && pair_ctas >= 148));
+}
+}  // namespace
+
+// Split K when the output's pair tiles fill the last wave of 74 SM pairs badly (c4's dW: 256 tiles = 3.46 waves,
+// a seventh of the machine idle in the fourth).  The smallest split of 2..4 that brings the waves' occupancy to
+// 95 % is taken, if each split keeps at least 64 k-blocks; a function of the shape alone.
+int gemm_tc_splits(int layout, long long m, long long n, long long k) {
+    (void)layout;
+    static const bool on = env_int("VOLTA_B200_TC_SPLITK", 1) != 0;
+    if (!on || !routes_to_pair(m, n)) return 1;
+    const long long tiles = ((m + 255) / 256) * ((n + 255) / 256), kblocks = (k + 31) / 32;
+    const double units = 74.0;
+    auto occupancy = [&](int s) { const double w = (double)(tiles * s) / units; return w / ceil(w); };
+    if (occupancy(1) >= 0.95) return 1;
+    for (int s = 2; s <= 4; ++s)
+        if (kblocks / s >= 64 && occupancy(s) >= 0.95) return s;
+    return 1;
+}
+
+long long gemm_tc_scratch_floats(int layout, long long m, long long n, long long k) {
+    const int s = gemm_tc_splits(layout, m, n, k);
+    return s > 1 ? (long long)s * m * n : 0;
+}
+
 cudaError_t launch_gemm_tc(int layout, const float *A, const float *B, long long m, long long n, long long k,
-                           const Epilogue &epi, unsigned int *status, cudaStream_t s) {
+                           const Epilogue &epi, unsigned int *status, cudaStream_t s, float *scratch,
+                           long long scratch_floats) {
     if (!gemm_tc_supported(layout, A, B, m, n, k, epi)) return cudaErrorNotSupported;
+    {
+        const int splits = gemm_tc_splits(layout, m, n, k);
+        if (splits > 1 && scratch && scratch_floats >= (long long)splits * m * n) {
+            Epilogue slab{};
+            slab.mode = EPI_STORE;
+            slab.out0 = scratch;
+            slab.ld = n;
+            cudaError_t e = launch_gemm_tc3(layout, A, B, m, n, k, slab, status, s, splits);
+            if (e != cudaSuccess) return e;
+            return launch_splitk_reduce(scratch, m, n, splits, epi, s);
+        }
+    }
     // Kernel generations: 3 = CTA-pair kernel for outputs of at least 256 x 256 (default), 2 = single-CTA
     // kernel with in-place high parts (all other shapes), 1 = the first kernel (kept for comparison).
     static const int version = env_int("VOLTA_B200_TC_VERSION", 3);

@@ -185,7 +185,8 @@ __device__ __forceinline__ void split_tile(const uint8_t *raw, uint8_t *lo_t, in
 template <bool A_KMAJOR, bool B_KMAJOR>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, long long M,
-                long long N, long long K, int tiles_m, int tiles_n, Epilogue epi, unsigned int *status, int CHUNK) {
+                long long N, long long K, int tiles_m, int tiles_n, Epilogue epi, unsigned int *status, int CHUNK,
+                int splits) {
     extern __shared__ uint8_t smem_raw[];
     pdl_wait();   // nothing of the previous kernel's output is touched before this
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -199,7 +200,7 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t rank = cluster_rank();   // 0 = leader of the pair
     int tm, tn;
     {
-        const int t = blockIdx.x >> 1;       // pair index
+        const int t = (int)(blockIdx.x >> 1) % (tiles_m * tiles_n);   // pair index -> tile (split-major grid)
         const int band = t / (GROUP_M * tiles_n);
         const int first = band * GROUP_M;
         const int rows = min(GROUP_M, tiles_m - first);
@@ -210,7 +211,13 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // this CTA's rows of the 256-row pair tile, and its 128 of the 256 columns of B to LOAD
     const long long m0 = (long long)tm * 256 + (long long)rank * 128, n0 = (long long)tn * 256;
     const long long nb0 = n0 + (long long)rank * 128;
-    const int kblocks = (int)((K + BK - 1) / BK);
+    // With split K, pair p works on k-blocks [kb0, kb0 + kblocks) of tile p % tiles and stores its sums as
+    // slab p / tiles of the output buffer (the caller adds the slabs in order afterwards).
+    const int kblocks_all = (int)((K + BK - 1) / BK);
+    const int split = (int)(blockIdx.x >> 1) / (tiles_m * tiles_n);
+    const int kb_per_split = (kblocks_all + splits - 1) / splits;
+    const int kb0 = split * kb_per_split;
+    const int kblocks = max(0, min(kb_per_split, kblocks_all - kb0));
     const int nchunks = (kblocks + CHUNK - 1) / CHUNK;
 
     if (tid == 0) {
@@ -250,7 +257,7 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const uint32_t full = smem_u32(&raw_full[s]);
                 mbar_expect_tx(full, 2 * TILE_BYTES);
                 const uint32_t dst = smem_u32(smem + s * RING_BYTES);
-                const int k0 = kb * BK;
+                const int k0 = (kb0 + kb) * BK;
                 if (A_KMAJOR) {
                     tma_load_2d(dst, &map_a, full, k0, (int)m0);
                 } else {
@@ -392,6 +399,7 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             // and stores two whole 256-byte row segments per instruction.
             constexpr int ST_LD = 68;   // floats per staged row: 16-byte aligned, four wavefronts per float4 write
             float *stage = reinterpret_cast<float *>(smem) + warp * (32 * ST_LD);
+            if (splits > 1) epi.out0 += (long long)split * M * N;   // this pair's slab
 #pragma unroll
             for (int j = 0; j < 64; j += 4)
                 *reinterpret_cast<float4 *>(stage + lane * ST_LD + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
@@ -464,7 +472,7 @@ bool make_map3(CUtensorMap *map, const float *base, long long inner, long long o
 
 template <bool AK, bool BKM>
 cudaError_t launch3(const CUtensorMap &ma, const CUtensorMap &mb, long long m, long long n, long long k, int tiles_m,
-                    int tiles_n, const Epilogue &epi, unsigned int *status, cudaStream_t s) {
+                    int tiles_n, const Epilogue &epi, unsigned int *status, cudaStream_t s, int splits) {
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc3_kernel<AK, BKM>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -472,7 +480,8 @@ cudaError_t launch3(const CUtensorMap &ma, const CUtensorMap &mb, long long m, l
         configured = true;
     }
     static const int chunk = [] { const char *e = getenv("VOLTA_B200_TC_CHUNK"); int v = e ? atoi(e) : DEFAULT_CHUNK; return v < 2 ? 2 : (v > 16 ? 16 : v); }();
-    return launch_pdl(gemm_tc3_kernel<AK, BKM>, dim3(2 * tiles_m * tiles_n), dim3(THREADS), SMEM_BYTES, s, ma, mb, m, n, k, tiles_m, tiles_n, epi, status, chunk);
+    return launch_pdl(gemm_tc3_kernel<AK, BKM>, dim3(2 * tiles_m * tiles_n * splits), dim3(THREADS), SMEM_BYTES, s, ma, mb, m, n, k, tiles_m,
+                      tiles_n, epi, status, chunk, splits);
 }
 
 }  // namespace
@@ -482,7 +491,8 @@ extern "C" void vb_trace3_set(unsigned long long *p) { cudaMemcpyToSymbol(g_trac
 #endif
 
 cudaError_t launch_gemm_tc3(int layout, const float *A, const float *B, long long m, long long n, long long k,
-                            const Epilogue &epi, unsigned int *status, cudaStream_t s) {
+                            const Epilogue &epi, unsigned int *status, cudaStream_t s, int splits) {
+    if (splits < 1 || (splits > 1 && epi.mode != EPI_STORE)) return cudaErrorInvalidValue;
     const bool a_kmajor = (layout != GEMM_TN), b_kmajor = (layout == GEMM_NT);
     CUtensorMap ma, mb;
     bool ok = a_kmajor ? make_map3(&ma, A, k, m, BK, 128, CU_TENSOR_MAP_SWIZZLE_128B)
@@ -491,9 +501,9 @@ cudaError_t launch_gemm_tc3(int layout, const float *A, const float *B, long lon
                          : make_map3(&mb, B, n, k, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
     if (!ok) return cudaErrorNotSupported;
     const int tiles_m = (int)((m + 255) / 256), tiles_n = (int)((n + 255) / 256);  // pair tiles
-    if (a_kmajor && b_kmajor) return launch3<true, true>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s);
-    if (a_kmajor && !b_kmajor) return launch3<true, false>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s);
-    if (!a_kmajor && !b_kmajor) return launch3<false, false>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s);
+    if (a_kmajor && b_kmajor) return launch3<true, true>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s, splits);
+    if (a_kmajor && !b_kmajor) return launch3<true, false>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s, splits);
+    if (!a_kmajor && !b_kmajor) return launch3<false, false>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s, splits);
     return cudaErrorNotSupported;
 }
 

@@ -63,6 +63,7 @@ struct vb200_handle {
     StepScalars *scalars = nullptr;
     unsigned int *status_word = nullptr;
     float *mse_scratch = nullptr, *colsum_scratch = nullptr, *gemm_scratch = nullptr;
+    long long gemm_scratch_floats = 0;
     float *xin[2] = {nullptr, nullptr}, *yin[2] = {nullptr, nullptr};
     std::vector<float *> act, pre, delta;  // act[0] unused (slot dependent)
 
@@ -191,7 +192,8 @@ cudaError_t run_gemm(vb200_handle *h, int layout, const float *A, const float *B
     if (path != VB200_GEMM_FFMA && gemm_tc_supported(layout, A, Bm, m, n, k, epi) &&
         (path == VB200_GEMM_TENSOR || path == VB200_GEMM_TENSOR_PAIR || gemm_prefers_tc(m, n, k))) {
         gemm_tc_select_pair(path == VB200_GEMM_TENSOR_PAIR);
-        cudaError_t e = launch_gemm_tc(layout, A, Bm, m, n, k, epi, h->status_word, h->stream);
+        cudaError_t e = launch_gemm_tc(layout, A, Bm, m, n, k, epi, h->status_word, h->stream, h->gemm_scratch,
+                                       h->gemm_scratch_floats);
         gemm_tc_select_pair(false);
         return e;
     }
@@ -707,6 +709,11 @@ void make_plan(const vb200_config &c, ArenaPlan &pl, PlanIdx &ix, std::vector<in
         gs = std::max(gs, ffma_scratch_floats(B, cc, r));            // forward
         gs = std::max(gs, ffma_scratch_floats(r, cc, B));            // dW
         if (i > 0) gs = std::max(gs, ffma_scratch_floats(B, r, cc)); // dX
+        // slabs of tensor GEMMs that split K to fill their last wave (not with SGD folded into dW: its
+        // epilogue then runs in the slab reduction all the same, so the scratch is needed either way)
+        gs = std::max(gs, gemm_tc_scratch_floats(GEMM_NN, B, cc, r));
+        gs = std::max(gs, gemm_tc_scratch_floats(GEMM_TN, r, cc, B));
+        if (i > 0) gs = std::max(gs, gemm_tc_scratch_floats(GEMM_NT, B, r, cc));
     }
     ix.gs = pl.add("gemm_splitk_scratch", gs * 4, 0, end, true);
     for (int s = 0; s < 2; ++s) {
@@ -810,6 +817,7 @@ int build(vb200_handle *h) {
     h->mse_scratch = at(i_mse);
     h->colsum_scratch = at(i_cs);
     h->gemm_scratch = at(ix.gs);
+    h->gemm_scratch_floats = (long long)(pl.buffers()[(size_t)ix.gs].bytes / 4);
     h->off_params = pl.offset(i_params);
     h->off_grads = pl.offset(i_grads);
     h->off_s1 = pl.offset(i_s1);
@@ -1496,12 +1504,19 @@ int volta_b200_gemm(int32_t layout, int32_t path, float *C, const float *A, cons
         unsigned int *st = nullptr;
         if (cudaMalloc(&st, sizeof(unsigned int)) != cudaSuccess) return VB200_ERR_OOM;
         cudaMemsetAsync(st, 0, sizeof(unsigned int), s);
-        err = launch_gemm_tc(layout, A, B, m, n, k, e, st, s);
+        float *slabs = nullptr;
+        const long long slab_floats = gemm_tc_scratch_floats(layout, m, n, k);
+        if (slab_floats > 0 && cudaMalloc(&slabs, (size_t)slab_floats * 4) != cudaSuccess) {
+            cudaGetLastError();
+            slabs = nullptr;   // no room: the unsplit kernel
+        }
+        err = launch_gemm_tc(layout, A, B, m, n, k, e, st, s, slabs, slabs ? slab_floats : 0);
         gemm_tc_select_pair(false);
         unsigned int hs = 0;
         if (err == cudaSuccess) err = cudaMemcpyAsync(&hs, st, sizeof hs, cudaMemcpyDeviceToHost, s);
         if (err == cudaSuccess) err = cudaStreamSynchronize(s);
         cudaFree(st);
+        if (slabs) cudaFree(slabs);
         if (err == cudaSuccess && hs != 0) return VB200_ERR_DEVICE_WAIT;
     } else if (path == VB200_GEMM_AUTO && layout == GEMM_NN && gemv_rows_supported(B, m, n, k)) {
         err = launch_gemv_rows(A, B, m, n, k, e, s);  // as a handle's forward pass routes at most 8 rows

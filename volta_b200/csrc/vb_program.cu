@@ -239,6 +239,7 @@ struct vb200_program {
     char *arena = nullptr;
     int64_t arena_bytes = 0;
     float *reduce_scratch = nullptr, *gemm_scratch = nullptr;
+    long long gemm_scratch_floats = 0;
     unsigned int *status_word = nullptr;
     StepScalars *scalars = nullptr;
     cudaStream_t stream = nullptr;
@@ -369,7 +370,7 @@ cudaError_t gemm(vb200_program *p, int layout, const float *A, const float *B, l
                  const Epilogue &e) {
     if (layout == GEMM_NN && gemv_rows_supported(B, m, n, k)) return launch_gemv_rows(A, B, m, n, k, e, p->stream);
     if (gemm_tc_supported(layout, A, B, m, n, k, e) && gemm_prefers_tc(m, n, k))
-        return launch_gemm_tc(layout, A, B, m, n, k, e, p->status_word, p->stream);
+        return launch_gemm_tc(layout, A, B, m, n, k, e, p->status_word, p->stream, p->gemm_scratch, p->gemm_scratch_floats);
     return launch_gemm_ffma(layout, A, B, m, n, k, e, p->stream, p->gemm_scratch);
 }
 
@@ -702,7 +703,7 @@ int volta_b200_program_compile(vb200_program *p, int32_t fuse, vb200_compiled_pr
             const PValue &a = p->values[(size_t)l.a];
             red = std::max(red, a.R + loss_blocks(a.R));
         }
-        if (l.kind == L_GEMM) gs = std::max(gs, ffma_scratch_floats(l.m, l.n, l.k));
+        if (l.kind == L_GEMM) gs = std::max(std::max(gs, ffma_scratch_floats(l.m, l.n, l.k)), gemm_tc_scratch_floats(l.layout, l.m, l.n, l.k));
     }
     ArenaPlan &pl = p->plan;
     const int i_sc = pl.add("scalars+status", 1024, 0, end, true);
@@ -761,6 +762,7 @@ int volta_b200_program_compile(vb200_program *p, int32_t fuse, vb200_compiled_pr
     p->status_word = reinterpret_cast<unsigned int *>(reinterpret_cast<char *>(at(i_sc)) + 512);
     p->reduce_scratch = at(i_red);
     p->gemm_scratch = at(i_gs);
+    p->gemm_scratch_floats = (long long)(pl.buffers()[(size_t)i_gs].bytes / 4);
     for (PValue &val : p->values)
         if (val.buf >= 0) {
             val.dev = at(val.buf);
