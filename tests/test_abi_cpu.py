@@ -116,6 +116,15 @@ def test_memory_plan_with_the_optional_stages():
     assert load_library().volta_b200_plan(C.byref(c), None, None, None, 0) == 1
 
 
+def test_plan_holds_the_split_k_slabs_where_a_gemm_needs_them():
+    """c4's 4096 x 4096 weight-gradient GEMMs (256 pair tiles on 74 SM pairs) split K in two: the step's GEMM
+    scratch holds two output slabs.  c5's GEMMs fill their waves: no slabs beyond what the small-shape path wants."""
+    by = {b[0]: b for b in _plan(_cfg(CONFIGS["c4"]))[2]}
+    assert by["gemm_splitk_scratch"][2] >= 2 * 4096 * 4096 * 4
+    by5 = {b[0]: b for b in _plan(_cfg(CONFIGS["c5"]))[2]}
+    assert by5["gemm_splitk_scratch"][2] < 4096 * 4096 * 4
+
+
 def test_plan_rejects_bad_configs():
     lib = load_library()
     c = _cfg(CONFIGS["c1"])
