@@ -382,7 +382,7 @@ int enqueue(vb200_program *p) {
         switch (l.kind) {
         case L_BINARY: {
             const PValue &a = p->values[(size_t)l.a], &b = p->values[(size_t)l.b];
-            long long ar, ac, br, bc;
+            long long ar = 0, ac = 0, br = 0, bc = 0;
             bcast(a.R, a.C, o.R, o.C, &ar, &ac);
             bcast(b.R, b.C, o.R, o.C, &br, &bc);
             VP_CUDA(p, launch_pdl(binary_kernel, dim3(grid_for(o.count)), dim3(256), 0, s, l.op, dev(l.out),
