@@ -27,6 +27,7 @@ def _lib(real: str):
         lib.oracle_set_momentum.argtypes = [C.c_void_p, C.c_double]
         lib.oracle_set_decay_bias.argtypes = [C.c_void_p, C.c_int]
         lib.oracle_set_global_batch.argtypes = [C.c_void_p, C.c_longlong]
+        lib.oracle_set_shard_row0.argtypes = [C.c_void_p, C.c_longlong]
         lib.oracle_grad_step.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]
         lib.oracle_update.argtypes = [C.c_void_p, C.c_float]
         lib.oracle_get_state.argtypes = [C.c_void_p] + [C.POINTER(rp)] * 4
@@ -135,6 +136,10 @@ class Oracle:
         y = np.ascontiguousarray(y, dtype=np.float32)
         assert x.size == self.batch * self.layers[0] and y.size == self.batch * self.layers[-1]
         self.lib.oracle_step(self.h, _fp(x), _fp(y), float(lr))
+
+    def set_shard_row0(self, row0: int):
+        """This handle holds rows [row0, row0 + batch) of the global batch (the dropout stream skips the rest)."""
+        self.lib.oracle_set_shard_row0(self.h, int(row0))
 
     def set_global_batch(self, gb: int):
         """This handle holds one shard of a global batch of gb rows (data parallel)."""

@@ -22,7 +22,7 @@ def inputs(cfg_act="silu"):
     return x, y, ws, bs
 
 
-def oracle_shard_worker(rank, world, port, opt, real, out_dir):
+def oracle_shard_worker(rank, world, port, opt, real, out_dir, act="silu", dropout_p=0.0):
     """One CPU rank: oracle on its row shard, gradients summed over ranks with gloo in rank
     order, identical update everywhere.  Writes its final parameters and loss trace."""
     import torch
@@ -33,8 +33,9 @@ def oracle_shard_worker(rank, world, port, opt, real, out_dir):
     x, y, ws, bs = inputs()
     B = GLOBAL_BATCH // world
     xs, ys = x[rank * B:(rank + 1) * B], y[rank * B:(rank + 1) * B]
-    o = Oracle(LAYERS, "silu", opt, B, real=real)
+    o = Oracle(LAYERS, act, opt, B, real=real, dropout_p=dropout_p)
     o.set_global_batch(GLOBAL_BATCH)
+    o.set_shard_row0(rank * B)      # the mask stream is the single-process one; this rank draws its rows' slice
     for i, (w, b) in enumerate(zip(ws, bs)):
         o.set_params(i, w, b)
     losses = []
