@@ -162,6 +162,7 @@ int volta_b200_checkpoint_save(const vb200_checkpoint *ck, const char *path, int
 vb200_checkpoint *volta_b200_checkpoint_load(const char *path);
 /* The same for the bytes of a checkpoint file held in memory (a file embedded in a library image). */
 vb200_checkpoint *volta_b200_checkpoint_parse(const void *bytes, int64_t n);
+/* Entry i in insertion order; the pointers stay valid until the next _add on, or the _free of, this checkpoint. */
 int32_t volta_b200_checkpoint_count(const vb200_checkpoint *ck);
 int volta_b200_checkpoint_entry(const vb200_checkpoint *ck, int32_t i, const char **name, const int64_t **shape,
                                 int32_t *ndim, const float **data, int64_t *count);
