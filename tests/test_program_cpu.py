@@ -106,3 +106,54 @@ def test_compile_fails_loudly_without_a_gpu():
         p.compile()
     with pytest.raises(VoltaB200Error, match="compile the program first"):
         p.run()
+
+
+def launches(build, outputs, fuse=True):
+    g = GraphBuilder()
+    outs = build(g)
+    return plan(g, [outs[i] for i in outputs] if outputs else [], fuse).launches
+
+
+def test_lowering_corner_cases():
+    """What folds and what does not, read off the number of kernels a schedule becomes."""
+    def both_transposed(g):
+        a, b = g.input((8, 4)), g.input((6, 8))
+        return [g.matmul(g.transpose(a), g.transpose(b))]
+    assert launches(both_transposed, [0]) == 2            # only the right operand folds; the left transpose runs
+    assert launches(both_transposed, [0], fuse=False) == 3
+
+    def add_full_matrix(g):
+        a, w, c = g.input((8, 4)), g.parameter((4, 6)), g.input((8, 6))
+        return [g.add(g.matmul(a, w), c)]
+    assert launches(add_full_matrix, [0]) == 2            # not a row bias: stays an elementwise add
+
+    def kept_matmul(g):
+        a, w, b = g.input((8, 4)), g.parameter((4, 6)), g.parameter((1, 6))
+        mm = g.matmul(a, w)
+        return [mm, g.add(mm, b)]
+    assert launches(kept_matmul, [1]) == 1                # bias rides the GEMM
+    assert launches(kept_matmul, [0, 1]) == 2             # ... unless the raw product itself must stay readable
+
+    def bias_relu_with_pre_reader(g):
+        a, w, b, up = g.input((8, 4)), g.parameter((4, 6)), g.parameter((1, 6)), g.input((8, 6))
+        pre = g.add(g.matmul(a, w), b)
+        return [g.relu(pre), g.relu_backward(pre, up)]
+    assert launches(bias_relu_with_pre_reader, [0, 1]) == 2   # one GEMM writing act and pre, one backward kernel
+
+    def backward_of_a_product(g):
+        x, up, w = g.input((8, 6)), g.input((8, 5)), g.parameter((6, 5))
+        return [g.relu_backward(x, g.matmul(up, g.transpose(w))), g.sigmoid_backward(x, g.matmul(up, g.transpose(w)))]
+    # relu backward rides its GEMM (transpose folded too); sigmoid backward needs sigmoid(x) and stays a kernel
+    assert launches(backward_of_a_product, [0, 1]) == 3
+
+    def bias_defined_late(g):
+        a, w = g.input((8, 4)), g.parameter((4, 6))
+        mm = g.matmul(a, w)
+        b = g.parameter((1, 6))                           # defined after the product: the fused launch could not read it yet
+        return [g.add(mm, b)]
+    assert launches(bias_defined_late, [0]) == 2
+
+    def aliases_cost_nothing(g):
+        a = g.input((4, 6))
+        return [g.output(g.reshape(g.identity(g.neg(a)), (6, 4)))]
+    assert launches(aliases_cost_nothing, [0]) == 1
