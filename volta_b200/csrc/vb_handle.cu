@@ -192,11 +192,15 @@ cudaError_t run_gemm(vb200_handle *h, int layout, const float *A, const float *B
     if (path != VB200_GEMM_FFMA && gemm_tc_supported(layout, A, Bm, m, n, k, epi) &&
         (path == VB200_GEMM_TENSOR || path == VB200_GEMM_TENSOR_PAIR || gemm_prefers_tc(m, n, k))) {
         gemm_tc_select_pair(path == VB200_GEMM_TENSOR_PAIR);
+        // a GEMM that splits K is two launches (the slab reduction follows it): count both
+        const int splits = gemm_tc_splits(layout, m, n, k);
+        if (splits > 1 && h->gemm_scratch_floats >= (long long)splits * m * n) h->kernels_per_step++;
         cudaError_t e = launch_gemm_tc(layout, A, Bm, m, n, k, epi, h->status_word, h->stream, h->gemm_scratch,
                                        h->gemm_scratch_floats);
         gemm_tc_select_pair(false);
         return e;
     }
+    if (h->gemm_scratch && ffma_splits(m, n, k) > 1) h->kernels_per_step++;   // likewise on the FFMA path
     return launch_gemm_ffma(layout, A, Bm, m, n, k, epi, h->stream, h->gemm_scratch);
 }
 
