@@ -38,17 +38,20 @@ enum { VB200_ACT_RELU = 0, VB200_ACT_SIGMOID = 1, VB200_ACT_TANH = 2, VB200_ACT_
 enum { VB200_OPT_SGD = 0, VB200_OPT_ADAM = 1, VB200_OPT_ADAMW = 2, VB200_OPT_ADAGRAD = 3,
        VB200_OPT_SGD_MOMENTUM = 4 };
 
-/* GEMM path selection. AUTO routes each GEMM by shape (tcgen05 kernel for large ones, FFMA with
- * split-K for small ones, and for forward GEMMs of at most 8 rows - single-sample inference - a
- * kernel whose CTA clusters split the input features and reduce through distributed shared memory).  TENSOR_PAIR is the experimental CTA-pair (cta_group::2) tcgen05 kernel
- * for outputs of at least 256 x 256; other shapes fall back to TENSOR. */
+/* GEMM path selection. AUTO routes each GEMM by shape: the tcgen05 kernels for large ones (CTA pairs
+ * with cta_group::2 on 256 x 256 tiles, or single CTAs on 128 x 128 tiles, either with K split over
+ * concurrent CTAs where that fills the GPU better), FFMA with split-K for small ones, and for forward
+ * GEMMs of at most 8 rows - single-sample inference - a kernel whose CTA clusters split the input
+ * features and reduce through distributed shared memory.  FFMA and TENSOR force one family for every
+ * GEMM that can take it; TENSOR_PAIR forces the CTA-pair kernel for outputs of at least 256 x 256
+ * (other shapes go as under TENSOR). */
 enum { VB200_GEMM_AUTO = 0, VB200_GEMM_FFMA = 1, VB200_GEMM_TENSOR = 2, VB200_GEMM_TENSOR_PAIR = 3 };
 
 /* Error codes (0 = success). The reference reports no errors on this path
  * (void functions, mlp_train_rust_codegen.rs:670-699); the replacement never traps and
  * reports through these codes and volta_b200_last_error(). */
 enum { VB200_OK = 0, VB200_ERR_INVALID = 1, VB200_ERR_CUDA = 2, VB200_ERR_OOM = 3, VB200_ERR_NCCL = 4,
-       VB200_ERR_DEVICE_WAIT = 5, VB200_ERR_UNSUPPORTED = 6, VB200_ERR_TOO_LARGE = 7 };
+       VB200_ERR_DEVICE_WAIT = 5, VB200_ERR_UNSUPPORTED = 6, VB200_ERR_TOO_LARGE = 7, VB200_ERR_NONFINITE = 8 };
 
 /* Replaces MlpTopology (mlp_train_rust_codegen.rs:28-39) plus the `batch` argument of
  * volta_train_init.  Hyper-parameters other than lr are fixed in the reference's
@@ -86,7 +89,15 @@ typedef struct vb200_config {
     float clip_grad;                   /* > 0: the template's "clip": when the norm over ALL deltas exceeds this,
                                           the deltas are scaled by clip/norm after the bias gradients were taken,
                                           so dW shrinks and db does not (:936-955) */
-    int32_t reserved[3];
+    int32_t device_wait_ms;            /* how long a data-parallel barrier waits for the other ranks before it gives
+                                          up (the step then applies no update and the handle reports
+                                          VB200_ERR_DEVICE_WAIT); 0 = $VOLTA_B200_WAIT_MS, else 4000 */
+    int32_t check_finite;              /* 1: after every step one more kernel looks for inf/NaN in the loss, the
+                                          gradients, the parameters and the optimizer state, as the reference's
+                                          runtime loop does (src/engine/ir/train.rs:670-773; its generated step has
+                                          no such check); the next call that waits for the step returns
+                                          VB200_ERR_NONFINITE naming the first bad element.  Off by default */
+    int32_t reserved[1];
 } vb200_config;
 
 typedef struct vb200_handle vb200_handle;
@@ -158,6 +169,8 @@ vb200_checkpoint *volta_b200_checkpoint_new(void);
 void volta_b200_checkpoint_free(vb200_checkpoint *ck);
 int volta_b200_checkpoint_add(vb200_checkpoint *ck, const char *name, const int64_t *shape, int32_t ndim,
                               const float *data);
+/* format: 1 = v1 text (nine significant digits), 2 = v2 binary, 3 = v1 text with the reference's own
+ * nine fixed decimals (byte-for-byte what save_checkpoint writes, checkpoint.rs:35; small values lose bits). */
 int volta_b200_checkpoint_save(const vb200_checkpoint *ck, const char *path, int32_t format);
 vb200_checkpoint *volta_b200_checkpoint_load(const char *path);
 /* The same for the bytes of a checkpoint file held in memory (a file embedded in a library image). */
@@ -171,9 +184,26 @@ int volta_b200_checkpoint_entry(const vb200_checkpoint *ck, int32_t i, const cha
  * ".acc" for Adagrad, ".mom" for SGD momentum; same for ".bias") and the counters "meta.adam_step",
  * "meta.dropout_rng" (three floats holding 22 + 22 + 20 bits each as exact integers) - what the
  * reference's checkpoint cannot carry (it stores parameters only).  Import takes every tensor it
- * knows by name, checks its shape, leaves the rest of the handle as it is and ignores other names. */
+ * knows by name, checks its shape, leaves the rest of the handle as it is and ignores other names.
+ *
+ * Volta names a layer's tensors after the layer ("{name}.weight", "{name}.bias" with the user's layer
+ * names, src/engine/model/layers.rs:52-58).  The _named forms take one name per weight layer (a NULL
+ * entry stands for "layer<i>") and use them instead of "layer<i>" for every tensor above.  Without
+ * names, import looks for "layer<i>.*" first and otherwise takes the checkpoint's "<X>.weight" (2-D) +
+ * "<X>.bias" pairs in sorted name order - the order Volta's writer uses - if there are exactly as many
+ * as layers and every shape fits.  A checkpoint in which no parameter tensor is found is refused with
+ * VB200_ERR_INVALID (it used to import nothing and report success); a found tensor of the wrong shape
+ * likewise.  volta_b200_checkpoint_match runs the same name resolution without a handle or a GPU and
+ * returns the number of parameter tensors found (> 0), or minus an error code with the reason in
+ * volta_b200_last_error(NULL). */
 int volta_b200_export_checkpoint(vb200_handle *h, vb200_checkpoint *ck, int32_t with_state);
 int volta_b200_import_checkpoint(vb200_handle *h, const vb200_checkpoint *ck);
+int volta_b200_export_checkpoint_named(vb200_handle *h, vb200_checkpoint *ck, int32_t with_state,
+                                       const char *const *layer_names, int32_t n_names);
+int volta_b200_import_checkpoint_named(vb200_handle *h, const vb200_checkpoint *ck, const char *const *layer_names,
+                                       int32_t n_names);
+int volta_b200_checkpoint_match(const vb200_config *cfg, const vb200_checkpoint *ck, const char *const *layer_names,
+                                int32_t n_names);
 
 /* Error reporting: last error code / message of this handle (or of the last failed
  * create when h is NULL).  The message pointer stays valid until the next call. */
@@ -211,6 +241,13 @@ int volta_b200_profile_step(vb200_handle *h, const float *X, const float *Y, flo
 /* Data-parallel bootstrap: rank 0 obtains an id and hands the same 128 bytes to every
  * rank's config (any host transport).  Uses NCCL, loaded at run time. */
 int volta_b200_dp_unique_id(uint8_t out[128]);
+/* Pre-flight check of that bootstrap, usable before any handle exists: joins a communicator of world_size
+ * ranks as `rank`, sums `count` floats of device_buf over the ranks when count > 0 (every rank must make
+ * the same call), and leaves the communicator again.  VB200_ERR_NCCL with NCCL's own message in
+ * volta_b200_last_error(NULL) when any NCCL call fails (library missing, a rank count that does not
+ * match, a system error).  $VOLTA_B200_NCCL_LIB selects the NCCL library file. */
+int volta_b200_dp_check(const uint8_t id[128], int32_t world_size, int32_t rank, float *device_buf, int64_t count,
+                        void *stream);
 
 /* Fused data parallelism over peer memory (no counterpart in the reference).  After every rank has
  * created its handle (same configuration, world_size > 1), each exports the 64-byte IPC handle of its
@@ -222,6 +259,13 @@ int volta_b200_dp_unique_id(uint8_t out[128]);
  * (save_state is refused). */
 int volta_b200_dp_ipc_handle(vb200_handle *h, uint8_t out[64]);
 int volta_b200_dp_attach_peers(vb200_handle *h, const uint8_t *handles, int32_t count);
+/* Failure detection of that path, checked without failing anything: runs ONE barrier kernel on this
+ * handle alone with a declared world of `declared_world` ranks, every "peer" being the handle's own
+ * arena, so that all flag words but its own are never written.  The kernel gives up after wait_ms,
+ * sets the status bit and returns; the call then reports VB200_ERR_DEVICE_WAIT, the handle refuses
+ * further steps and can still be queried and destroyed.  No counterpart in the reference (it has no
+ * collective and no device-side wait). */
+int volta_b200_dp_wait_selftest(vb200_handle *h, int32_t declared_world, int32_t wait_ms);
 
 /* Stand-alone kernel entry points on device pointers (used by parity tests to check
  * single kernels against the oracle; `stream` is a cudaStream_t or NULL). */
@@ -232,6 +276,11 @@ int volta_b200_optimizer_apply(int32_t optimizer, float *p, float *s1, float *s2
  * 2 = TN (A[k x m], B[k x n]); path is VB200_GEMM_*. */
 int volta_b200_gemm(int32_t layout, int32_t path, float *C, const float *A, const float *B, int64_t m,
                     int64_t n, int64_t k, void *stream);
+/* Which kernel family a GEMM of this shape takes under `path`, and into how many K splits (a function of
+ * the arguments alone; needs no GPU).  Returns VB200_ROUTE_* or minus an error code.  Operands are
+ * assumed 16-byte aligned, as every buffer of a handle is. */
+enum { VB200_ROUTE_FFMA = 0, VB200_ROUTE_TENSOR_SINGLE = 1, VB200_ROUTE_TENSOR_PAIR = 2, VB200_ROUTE_SMALL_ROWS = 3 };
+int volta_b200_gemm_route(int32_t layout, int32_t path, int64_t m, int64_t n, int64_t k, int32_t *splits);
 /* out[j] = sum over rows of in[rows x cols] in a fixed order; scratch must hold
  * volta_b200_colsum_scratch_floats(rows, cols) floats. */
 int64_t volta_b200_colsum_scratch_floats(int64_t rows, int64_t cols);

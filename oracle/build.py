@@ -26,7 +26,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 BUILD = os.path.join(HERE, "_build")
 REF = os.path.join(HERE, "_ref")
-REFERENCE_ROOT = os.environ.get("VOLTA_REFERENCE_ROOT", "/root/reference")
+# The reference checkout: $VOLTA_REFERENCE_ROOT, else a directory named "reference" beside this repository.
+REFERENCE_ROOT = os.environ.get("VOLTA_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 SHIM_SRC = os.path.join(REFERENCE_ROOT, "src", "engine", "ir", "codegen", "gemm_shim.c")
 
 STRICT = ["-O3", "-mavx2", "-fPIC", "-shared", "-std=c11", "-ffp-contract=off", "-fno-fast-math",

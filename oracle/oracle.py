@@ -49,6 +49,8 @@ def _lib(real: str):
         lib.oracle_loss.argtypes = [C.c_void_p]
         lib.oracle_step.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_float]
         lib.oracle_lcg_xavier.argtypes = [C.POINTER(C.c_float), C.c_int64, C.c_int, C.c_int, C.POINTER(C.c_uint64)]
+        lib.oracle_keep_scale.restype = C.c_float
+        lib.oracle_keep_scale.argtypes = [C.c_float]
         lib.oracle_apply_update.argtypes = [C.c_int, rp, rp, rp, rp, C.c_int64, C.c_double, C.c_double,
                                             C.c_double, C.c_uint64]
         _libs[real] = (lib, rp)
@@ -76,7 +78,7 @@ class Oracle:
                                         self.batch)
         if not self.h:
             raise ValueError("oracle_create rejected the topology")
-        self.lib.oracle_set_momentum(self.h, float(momentum))
+        self.lib.oracle_set_momentum(self.h, float(np.float32(momentum)))   # an f32 hyper-parameter, in both builds
         if dropout_p or use_layernorm or clip_grad:
             self.lib.oracle_set_options(self.h, float(dropout_p), int(bool(use_layernorm)), float(clip_grad))
         self._shim = None
@@ -220,3 +222,9 @@ def apply_update(optimizer: str, p, g, s1=None, s2=None, lr=0.01, wd=0.01, momen
     lib.oracle_apply_update(OPTIMIZERS[optimizer], cast(p), cast(s1), cast(s2), cast(g), p.size, float(lr),
                             float(wd), float(momentum), int(t))
     return p, s1, s2
+
+
+def keep_scale(p: float) -> float:
+    """The dropout rescale 1/(1-p) exactly as the generated step holds it (f32 arithmetic)."""
+    lib, _ = _lib("f32")
+    return float(lib.oracle_keep_scale(float(p)))

@@ -7,7 +7,7 @@ the fixture inputs (dataset, initial parameters, learning rates) defined in the 
 (examples/pytorch_parity.py:613-857), so that the oracle can be pinned where no
 checkout is available.
 
-Usage:  python tests/golden/make_golden.py [/path/to/reference]
+Usage:  python tests/golden/make_golden.py /path/to/reference
 """
 import importlib.util
 import json
@@ -16,7 +16,9 @@ import sys
 
 import torch
 
-ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: python tests/golden/make_golden.py /path/to/reference")
+ref_root = sys.argv[1]
 spec = importlib.util.spec_from_file_location("pytorch_parity", os.path.join(ref_root, "examples", "pytorch_parity.py"))
 pp = importlib.util.module_from_spec(spec)
 spec.loader.exec_module(pp)

@@ -84,7 +84,7 @@ def test_missing_file_and_unwritable_names(tmp_path):
     with pytest.raises(VoltaB200Error, match="cannot be written"):
         ck.save(tmp_path / "x.txt")
     with pytest.raises(VoltaB200Error, match="unknown checkpoint format"):
-        sample().save(tmp_path / "y.txt", 3)
+        sample().save(tmp_path / "y.txt", 4)
 
 
 def hard_values():
@@ -157,3 +157,90 @@ def test_binary_written_elsewhere_loads_and_real_deflate_is_refused(tmp_path):
     p.write_bytes(good[:8 + 9])                                               # cut inside the first block
     with pytest.raises(VoltaB200Error):
         Checkpoint.load(p)
+
+
+def test_fixed_nine_decimals_are_the_reference_writers_bytes(tmp_path):
+    """Format 3 prints `{v:.9}` as save_checkpoint does (checkpoint.rs:35), so a file of ours and a file of
+    Volta's with the same tensors are the same bytes but for the writer line; small values then lose bits,
+    which is why nine significant digits stay the default."""
+    ck = Checkpoint()
+    ck.add("fc1.weight", np.array([[1.0, -2.5, 1.2345678e-7]], np.float32))
+    ck.add("fc1.bias", np.array([0.25], np.float32))
+    p = tmp_path / "f.txt"
+    ck.save(p, 3)
+    assert p.read_text().splitlines()[2:] == ["fc1.bias|1|0.250000000", "fc1.weight|1,3|1.000000000,-2.500000000,0.000000123"]
+    back = Checkpoint.load(p).tensors()
+    assert back["fc1.weight"][0, 2] == np.float32(0.000000123)         # lossy, as in the reference
+    ck.save(p, TEXT_V1)
+    assert np.array_equal(Checkpoint.load(p).tensors()["fc1.weight"].view(np.uint32),
+                          np.array([[1.0, -2.5, 1.2345678e-7]], np.float32).view(np.uint32))
+
+
+@pytest.mark.parametrize("token", ["0x1p3", " 1.0", "1.0 ", "1_000", "1e", ".", "", "+-1", "1.0f"])
+def test_reader_takes_only_what_rust_parses_as_f32(tmp_path, token):
+    """The reference parses every value with f32::from_str (checkpoint.rs:141): no hexadecimal floats,
+    no blanks inside a value.  A file accepted here must also load in Volta."""
+    p = tmp_path / "bad.txt"
+    p.write_text("#volta-checkpoint:v1\nw|3|1.0,%s,2.0" % token)   # in the middle: line ends are trimmed, as in the reference
+    with pytest.raises(VoltaB200Error, match="Invalid data value|Invalid tensor"):
+        Checkpoint.load(p)
+
+
+@pytest.mark.parametrize("token,value", [("1.", 1.0), (".5", 0.5), ("+2", 2.0), ("-1e-3", -1e-3), ("3E2", 300.0),
+                                         ("inf", np.inf), ("-Infinity", -np.inf)])
+def test_reader_accepts_rusts_other_spellings(tmp_path, token, value):
+    p = tmp_path / "ok.txt"
+    p.write_text("w|1|%s" % token)
+    assert Checkpoint.load(p).tensors()["w"][0] == np.float32(value)
+    p.write_text("w|1|NaN")
+    assert np.isnan(Checkpoint.load(p).tensors()["w"][0])
+
+
+def _match(layers, ck, names=None):
+    import ctypes as C
+    from volta_b200 import load_library
+    from volta_b200.lib import Config
+    lib = load_library()
+    cfg = Config()
+    cfg.n_sizes = len(layers)
+    for i, v in enumerate(layers):
+        cfg.layers[i] = v
+    cfg.batch = 4
+    arr, n = (None, 0) if names is None else ((C.c_char_p * len(names))(*[None if v is None else v.encode() for v in names]), len(names))
+    rc = lib.volta_b200_checkpoint_match(C.byref(cfg), ck.h, arr, n)
+    return rc, lib.volta_b200_last_error(None).decode()
+
+
+def test_layer_names_of_a_volta_model_are_found(tmp_path):
+    """Volta names tensors after the layers ("{name}.weight", "{name}.bias", model/layers.rs:52-58).  A file
+    written the way its save_checkpoint writes one (sorted by name, nine decimals) resolves onto a 3-4-2
+    topology without the caller naming the layers, and with explicit names in any order."""
+    p = tmp_path / "volta.txt"
+    w1, w2 = np.arange(12, dtype=np.float32).reshape(3, 4), np.arange(8, dtype=np.float32).reshape(4, 2)
+    rows = {"fc1.weight": w1, "fc1.bias": np.zeros(4, np.float32), "fc2.weight": w2, "fc2.bias": np.ones(2, np.float32)}
+    lines = ["#volta-checkpoint:v1", "#writer:train_api"]
+    for name in sorted(rows):
+        t = rows[name]
+        lines.append("%s|%s|%s" % (name, ",".join(map(str, t.shape)), ",".join("%.9f" % v for v in t.ravel())))
+    p.write_text("\n".join(lines))
+    ck = Checkpoint.load(p)
+    assert _match([3, 4, 2], ck)[0] == 4                                  # two weights + two biases
+    assert _match([3, 4, 2], ck, ["fc1", "fc2"])[0] == 4
+    rc, why = _match([3, 4, 2], ck, ["fc2", "fc1"])
+    assert rc == -1 and "wrong shape" in why
+    rc, why = _match([3, 4, 2], ck, ["encoder", "head"])
+    assert rc == -1 and "no '<name>.weight'" in why
+    rc, why = _match([3, 4, 4, 2], ck)                                    # three layers, two pairs in the file
+    assert rc == -1 and "pass the layer names" in why
+    rc, why = _match([3, 5, 2], ck)
+    assert rc == -1 and "wrong shape" in why
+
+
+def test_a_checkpoint_without_any_known_parameter_is_refused():
+    ck = Checkpoint()
+    ck.add("something.else", np.zeros(3, np.float32))
+    rc, why = _match([3, 4, 2], ck)
+    assert rc == -1 and why
+    own = Checkpoint()
+    own.add("layer1.bias", np.zeros(2, np.float32))                       # a partial file of this library's names
+    assert _match([3, 4, 2], own)[0] == 1

@@ -365,3 +365,41 @@ def test_clip_scales_the_deltas_not_the_bias_gradients():
     c.grad_step(x, y)
     for u, v in zip(aw, c.get_grads()[0]):
         assert np.array_equal(u, v)
+
+
+def test_dropout_keep_scale_is_computed_in_f32():
+    """The template evaluates 1.0 / (1.0 - dropout_p) on f32 values (mlp_train_rust_codegen.rs:775, 890);
+    a double-precision quotient rounded afterwards differs from it by one ulp for some p."""
+    from oracle.oracle import keep_scale
+    differs = 0
+    for p in np.linspace(0.01, 0.95, 1901).astype(np.float32):
+        want = np.float32(1.0) / (np.float32(1.0) - p)
+        assert np.float32(keep_scale(float(p))).view(np.uint32) == want.view(np.uint32), p
+        differs += int(np.float32(1.0 / (1.0 - float(p))).view(np.uint32) != want.view(np.uint32))
+    assert differs > 0   # the sweep does contain values where the two roundings part
+
+
+@pytest.mark.parametrize("act", ["relu", "sigmoid", "tanh", "leaky_relu", "silu", "gelu"])
+@pytest.mark.parametrize("opt", ["sgd", "sgd_momentum", "adam", "adamw", "adagrad"])
+def test_torch_fp64_helper_matches_the_oracle(act, opt):
+    """tests/torch_fp64.py is the arbiter of the large-shape GPU tests; here it is pinned on the C oracle's
+    fp64 build: losses, gradients, parameters over four steps."""
+    from tests.torch_fp64 import TorchMlp64
+    rs = np.random.RandomState(11)
+    layers, B, lr = [7, 10, 9, 4], 6, 0.02
+    x = rs.randn(B, layers[0]).astype(np.float32)
+    y = rs.randn(B, layers[-1]).astype(np.float32)
+    o = Oracle(layers, act, opt, B, real="f64")
+    ws = [w.astype(np.float32) for w in o.get_params()[0]]
+    bs = [(rs.randn(c) * 0.1).astype(np.float32) for c in layers[1:]]
+    for i in range(len(ws)):
+        o.set_params(i, ws[i], bs[i])
+    t = TorchMlp64(layers, act, opt, ws, bs)
+    for _ in range(4):
+        o.step(x, y, lr)
+        t.step(x, y, lr)
+        assert abs(o.loss() - t.loss()) <= 1e-12 * max(1.0, abs(o.loss()))
+        for a, b in zip(sum(o.get_grads(), []), t.grads()):
+            np.testing.assert_allclose(a, b, rtol=1e-9, atol=1e-12)
+    for a, b in zip(sum(o.get_params(), []), t.params()):
+        np.testing.assert_allclose(a, b, rtol=1e-9, atol=1e-12)

@@ -3,6 +3,7 @@
 #include "vb_checkpoint.h"
 
 #include <algorithm>
+#include <cctype>
 #include <cerrno>
 #include <cstdio>
 #include <cstdlib>
@@ -64,9 +65,19 @@ std::vector<const CheckpointEntry *> sorted(const Checkpoint &ck) {
 }
 
 // ---- v1 text ---------------------------------------------------------------------------------
-std::string to_text(const Checkpoint &ck) {
+// One value as the reference writes it, `{v:.9}` (checkpoint.rs:35): fixed notation, nine decimals.
+// That form loses small magnitudes (1.2345678e-7 becomes 0.000000123); the default writer therefore
+// prints nine SIGNIFICANT digits, which every fp32 value survives bit for bit and which the
+// reference's reader parses the same way.
+void print_value(char *buf, size_t cap, float v, bool fixed9) {
+    if (v != v) { snprintf(buf, cap, "NaN"); return; }                        // Rust prints NaN, C prints nan
+    if (fixed9 && (v - v) != 0.0f) { snprintf(buf, cap, v < 0 ? "-inf" : "inf"); return; }
+    snprintf(buf, cap, fixed9 ? "%.9f" : "%.9g", (double)v);
+}
+
+std::string to_text(const Checkpoint &ck, bool fixed9) {
     std::string out = std::string(kHeaderPrefix) + "v1\n#writer:volta_b200";
-    char num[48];
+    char num[64];
     for (const CheckpointEntry *e : sorted(ck)) {
         out += "\n" + e->name + "|";
         for (size_t i = 0; i < e->shape.size(); ++i) {
@@ -75,7 +86,8 @@ std::string to_text(const Checkpoint &ck) {
         }
         out += "|";
         for (size_t i = 0; i < e->data.size(); ++i) {
-            snprintf(num, sizeof num, "%s%.9g", i ? "," : "", (double)e->data[i]);
+            if (i) out += ",";
+            print_value(num, sizeof num, e->data[i], fixed9);
             out += num;
         }
     }
@@ -91,6 +103,33 @@ bool header_line(const std::string &line, size_t line_no, bool *is_header, std::
     if (version != "v1")
         return fail(err, "Unsupported checkpoint version '" + version + "' at line " + std::to_string(line_no + 1));
     return true;
+}
+
+// The grammar of Rust's f32::from_str, which the reference's reader applies to every value
+// (checkpoint.rs:141): optional sign, then inf / infinity / nan in any case, or decimal digits with
+// an optional point and an optional decimal exponent.  No whitespace, no hexadecimal floats, no
+// digit separators; strtof alone would accept the first two.
+bool is_rust_f32(const std::string &t) {
+    size_t i = 0;
+    if (i < t.size() && (t[i] == '+' || t[i] == '-')) ++i;
+    std::string rest = t.substr(i);
+    for (char &c : rest) c = (char)tolower((unsigned char)c);
+    if (rest == "inf" || rest == "infinity" || rest == "nan") return true;
+    size_t digits = 0;
+    while (i < t.size() && isdigit((unsigned char)t[i])) { ++i; ++digits; }
+    if (i < t.size() && t[i] == '.') {
+        ++i;
+        while (i < t.size() && isdigit((unsigned char)t[i])) { ++i; ++digits; }
+    }
+    if (digits == 0) return false;
+    if (i < t.size() && (t[i] == 'e' || t[i] == 'E')) {
+        ++i;
+        if (i < t.size() && (t[i] == '+' || t[i] == '-')) ++i;
+        size_t ed = 0;
+        while (i < t.size() && isdigit((unsigned char)t[i])) { ++i; ++ed; }
+        if (ed == 0) return false;
+    }
+    return i == t.size();
 }
 
 bool parse_entry(const std::string &line, size_t line_no, CheckpointEntry *e, std::string *err) {
@@ -121,7 +160,7 @@ bool parse_entry(const std::string &line, size_t line_no, CheckpointEntry *e, st
         const std::string tok = data.substr(p, q - p);
         char *end = nullptr;
         float v = strtof(tok.c_str(), &end);
-        if (tok.empty() || *end || tok[0] == ' ') return fail(err, "Invalid data value '" + tok + "'" + at);
+        if (!is_rust_f32(tok) || *end) return fail(err, "Invalid data value '" + tok + "'" + at);
         e->data.push_back(v);
         p = q + 1;
     }
@@ -306,14 +345,15 @@ bool checkpoint_save(const Checkpoint &ck, const std::string &path, int format, 
             return fail(err, "entry name '" + e.name + "' cannot be written");
         if (!product_matches(e.shape, e.data.size())) return fail(err, "entry '" + e.name + "': shape does not match its data");
     }
-    if (format == 1) return write_file(path, to_text(ck), err);
+    if (format == 1) return write_file(path, to_text(ck, false), err);
+    if (format == 3) return write_file(path, to_text(ck, true), err);
     if (format == 2) {
         std::string e2;
         std::string bytes = to_binary(ck, &e2);
         if (bytes.empty()) return fail(err, e2);
         return write_file(path, bytes, err);
     }
-    return fail(err, "unknown checkpoint format (1 = v1 text, 2 = v2 binary)");
+    return fail(err, "unknown checkpoint format (1 = v1 text, 2 = v2 binary, 3 = v1 text with the reference's nine fixed decimals)");
 }
 
 bool checkpoint_parse(Checkpoint *ck, const std::string &raw, std::string *err) {

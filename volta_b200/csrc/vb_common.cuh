@@ -45,6 +45,38 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
 }
 
 // ---------------------------------------------------------------------------------------
+// Per-device state.  A process may hold handles on several GPUs: function attributes (the
+// dynamic shared-memory limit) are set per device, and SM counts differ between devices, so
+// neither may be cached per process.
+// ---------------------------------------------------------------------------------------
+constexpr int kMaxDevices = 64;
+inline int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); dev = 0; }
+    return (dev >= 0 && dev < kMaxDevices) ? dev : 0;
+}
+// Raises a kernel's dynamic shared-memory limit once per device.
+template <typename K>
+cudaError_t set_smem_once(K kernel, int bytes, bool (&done)[kMaxDevices]) {
+    const int dev = current_device();
+    if (done[dev]) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) done[dev] = true;
+    return e;
+}
+// Number of SMs of the current device (148 on B200).
+inline int device_sm_count() {
+    static int sms[kMaxDevices] = {};
+    const int dev = current_device();
+    if (sms[dev] <= 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) cudaGetLastError();
+        sms[dev] = v > 0 ? v : 148;
+    }
+    return sms[dev];
+}
+
+// ---------------------------------------------------------------------------------------
 // Activation math, following the reference's generated helpers
 // (src/engine/ir/codegen/mlp_train_rust_codegen.rs:563-596, 725-743, 894-916).
 // ---------------------------------------------------------------------------------------
@@ -216,19 +248,21 @@ bool gemm_prefers_tc(long long m, long long n, long long k);
 // Returns cudaErrorNotSupported when the shape/alignment cannot take the tensor path.
 // `scratch` (gemm_tc_scratch_floats floats, may be null) lets a GEMM whose tiles fill the last wave badly
 // split K over concurrent CTAs; the slabs are then added in split order by launch_splitk_reduce.
+// `force_pair` restricts the choice to the CTA-pair kernel (outputs of at least 256 x 256).  Kernel and
+// split count are functions of (m, n, k, force_pair) alone.
 cudaError_t launch_gemm_tc(int layout, const float *A, const float *B, long long m, long long n, long long k,
                            const Epilogue &epi, unsigned int *status_word, cudaStream_t s, float *scratch = nullptr,
-                           long long scratch_floats = 0);
-int gemm_tc_splits(int layout, long long m, long long n, long long k);
-long long gemm_tc_scratch_floats(int layout, long long m, long long n, long long k);
+                           long long scratch_floats = 0, bool force_pair = false);
+int gemm_tc_splits(int layout, long long m, long long n, long long k, bool force_pair = false);
+bool gemm_tc_uses_pair(int layout, long long m, long long n, long long k, bool force_pair = false);
+long long gemm_tc_scratch_floats(int layout, long long m, long long n, long long k, bool force_pair = false);
 // out = epilogue(sum over z of partial[z][m x n]), z ascending
 cudaError_t launch_splitk_reduce(const float *partial, long long m, long long n, int splits, const Epilogue &epi,
                                  cudaStream_t s);
 cudaError_t launch_gemm_tc2(int layout, const float *A, const float *B, long long m, long long n, long long k,
-                            const Epilogue &epi, unsigned int *status_word, cudaStream_t s);
+                            const Epilogue &epi, unsigned int *status_word, cudaStream_t s, int splits = 1);
 cudaError_t launch_gemm_tc3(int layout, const float *A, const float *B, long long m, long long n, long long k,
                             const Epilogue &epi, unsigned int *status_word, cudaStream_t s, int splits = 1);
-void gemm_tc_select_pair(bool on);
 bool gemm_tc_supported(int layout, const float *A, const float *B, long long m, long long n, long long k,
                        const Epilogue &epi);
 
@@ -241,6 +275,10 @@ cudaError_t launch_gemv_rows(const float *x, const float *W, long long m, long l
 cudaError_t launch_optimizer(int optimizer, float *p, float *s1, float *s2, const float *g, long long n,
                              long long n_decay, const StepScalars *sc, cudaStream_t s);
 cudaError_t launch_set_scalars(StepScalars *dst, StepScalars v, cudaStream_t s);
+// first_bad[0..3] = min(first_bad[r], smallest index of an inf/NaN in g[0..n_grads), p, s1, s2 [0..n));
+// null regions are skipped; the caller presets the four words to all ones.
+cudaError_t launch_finite_guard(const float *p, const float *g, const float *s1, const float *s2, long long n,
+                                long long n_grads, unsigned long long *first_bad, cudaStream_t s);
 
 // ---- fused data-parallel update over peer memory (vb_dp_fused.cu)
 constexpr int kMaxPeers = 8;
@@ -248,17 +286,21 @@ struct PeerTable {
     char *base[kMaxPeers];   // every rank's arena, mapped into this process (own arena at [rank])
 };
 // One barrier among the ranks: write `*epoch * stride + index` into slot `rank` of every peer's flag
-// array, then wait (bounded) until all of this rank's slots have reached it.
+// array, then wait until all of this rank's slots have reached it - for at most wait_ns, after which
+// the DP-barrier bit is set in *status.  Once that bit is set (by this or an earlier launch) the
+// kernel returns at once without touching a peer: the missing rank's memory may be gone.
 cudaError_t launch_dp_barrier(const PeerTable &peers, long long flags_off, int world, int rank,
                               const StepScalars *scalars, unsigned stride, unsigned index, unsigned int *status,
-                              cudaStream_t s);
+                              unsigned long long wait_ns, cudaStream_t s);
 // For the floats [seg_begin, seg_begin + seg_len) of the flat layout: this rank sums its 1/world share
 // of every rank's gradients in rank order, applies the optimizer to its share of the parameters, and
-// writes the new parameters into every rank's arena.
+// writes the new parameters into every rank's arena.  Does nothing once the DP-barrier bit of *status
+// is set: after a barrier gave up, some rank's gradients are missing or stale and its arena may be gone.
 cudaError_t launch_dp_reduce_update(int optimizer, const PeerTable &peers, long long params_off, long long grads_off,
                                     long long s1_off, long long s2_off, long long seg_begin, long long seg_len,
                                     long long n_decay, int world, int rank, const StepScalars *scalars,
-                                    long long loss_off, cudaStream_t s);
+                                    long long loss_off, const unsigned int *status, cudaStream_t s);
+constexpr unsigned kStatusDpBarrier = 64u;   // status-word bit: a data-parallel barrier wait ran out
 
 long long colsum_chunks(long long rows, long long cols);
 // out[j] = sum_rows in[row, j] * (row_weight ? row_weight[row] : 1), fixed order

@@ -32,11 +32,20 @@ Api *api() {
     static Api a;
     static std::once_flag once;
     std::call_once(once, [] {
-        // Prefer a copy the process has already loaded (e.g. the one bundled with torch).
+        // $VOLTA_B200_NCCL_LIB names the library to use (a site's own build; the failure-path tests point it
+        // at a stand-in whose calls return NCCL error codes).  Otherwise prefer a copy the process has
+        // already loaded (e.g. the one bundled with torch).
         const char *names[] = {"libnccl.so.2", "libnccl.so"};
+        if (const char *own = getenv("VOLTA_B200_NCCL_LIB")) {
+            a.lib = dlopen(own, RTLD_NOW | RTLD_LOCAL);
+            if (!a.lib) {
+                a.why = std::string("VOLTA_B200_NCCL_LIB: ") + dlerror();
+                return;
+            }
+        }
         for (const char *nm : names) {
-            a.lib = dlopen(nm, RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);
             if (a.lib) break;
+            a.lib = dlopen(nm, RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);
         }
         if (!a.lib)
             for (const char *nm : names) {
@@ -69,13 +78,19 @@ std::string describe(Api *a, const char *what, int rc) {
 
 }  // namespace
 
-int DpComm::unique_id(uint8_t out[128]) {
+int DpComm::unique_id(uint8_t out[128], std::string *why) {
     Api *a = api();
-    if (!a->lib) return 1;
+    if (!a->lib) {
+        if (why) *why = a->why;
+        return 1;
+    }
     NcclId id;
     memset(&id, 0, sizeof id);
     int rc = a->get_unique_id(&id);
-    if (rc) return rc;
+    if (rc) {
+        if (why) *why = describe(a, "ncclGetUniqueId", rc);
+        return rc;
+    }
     memcpy(out, id.internal, 128);
     return 0;
 }

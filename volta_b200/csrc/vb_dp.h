@@ -19,7 +19,7 @@ public:
     // In-place sum over ranks of `count` floats, enqueued on `stream` (capturable).
     int all_reduce_sum(float *buf, int64_t count, cudaStream_t stream);
     const std::string &error() const { return err_; }
-    static int unique_id(uint8_t out[128]);
+    static int unique_id(uint8_t out[128], std::string *why = nullptr);
 
 private:
     void *comm_ = nullptr;

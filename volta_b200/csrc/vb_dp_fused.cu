@@ -11,8 +11,11 @@
 // Ordering between ranks uses flag words in each arena: before a bucket's kernel every rank announces
 // "my backward for this layer is done" and waits for all others (so nobody's weights are overwritten
 // while it still reads them, and every gradient is final); one more barrier at the end of the step
-// makes all updates visible before the next forward.  Waits are bounded (~4 s): on expiry a status
-// bit is set and the kernel carries on, so a missing rank never hangs the GPU.
+// makes all updates visible before the next forward.  Waits are bounded (4 s unless the handle's
+// configuration says otherwise): on expiry a status bit is set, and from then on every barrier and
+// every reduce-update kernel of the handle returns at once without reading or writing any rank's
+// memory - a missing rank neither hangs the GPU nor gets a partial sum applied, and the host
+// refuses further steps with VB200_ERR_DEVICE_WAIT.
 // The reference has no collective of any kind; parity target is the full-batch CPU oracle.
 #include "vb_common.cuh"
 #include "vb_optimizer.cuh"
@@ -20,7 +23,7 @@
 namespace vb {
 namespace {
 
-constexpr unsigned ST_DP_BARRIER = 64u;
+constexpr unsigned ST_DP_BARRIER = kStatusDpBarrier;
 
 __device__ __forceinline__ unsigned long long dp_global_ns() {
     unsigned long long t;
@@ -30,10 +33,12 @@ __device__ __forceinline__ unsigned long long dp_global_ns() {
 
 __global__ void dp_barrier_kernel(PeerTable peers, long long flags_off, int world, int rank,
                                   const StepScalars *__restrict__ scalars, unsigned stride, unsigned index,
-                                  unsigned int *status) {
+                                  unsigned int *status, unsigned long long wait_ns) {
     pdl_wait();
     const int t = threadIdx.x;
     if (t >= world) return;
+    // an earlier barrier of this handle gave up: some rank is missing, leave every peer alone
+    if (*reinterpret_cast<volatile unsigned int *>(status) & ST_DP_BARRIER) return;
     const unsigned value = scalars->epoch * stride + index;
     __threadfence_system();   // everything this GPU wrote before the barrier is visible to its peers
     volatile unsigned *theirs = reinterpret_cast<volatile unsigned *>(peers.base[t] + flags_off) + rank;
@@ -45,7 +50,7 @@ __global__ void dp_barrier_kernel(PeerTable peers, long long flags_off, int worl
         if ((it & 1023u) == 1023u) {
             unsigned long long now = dp_global_ns();
             if (t0 == 0) t0 = now;
-            if (now - t0 > 4000000000ull) {
+            if (now - t0 > wait_ns) {
                 atomicOr(status, ST_DP_BARRIER);
                 break;
             }
@@ -58,8 +63,12 @@ template <int OPT>
 __global__ void __launch_bounds__(256) dp_reduce_update_kernel(PeerTable peers, long long params_off, long long grads_off,
                                                                long long s1_off, long long s2_off, long long seg_begin,
                                                                long long seg_len, long long n_decay, int world, int rank,
-                                                               const StepScalars *__restrict__ scp, long long loss_off) {
+                                                               const StepScalars *__restrict__ scp, long long loss_off,
+                                                               const unsigned int *__restrict__ status) {
     pdl_wait();
+    // the barrier before this kernel gave up: gradients are partial or stale and a peer's arena may be
+    // gone, so nothing is read from or written to any rank and the parameters stay as they were
+    if (*reinterpret_cast<const volatile unsigned int *>(status) & ST_DP_BARRIER) return;
     const StepScalars sc = *scp;
     constexpr bool HAS1 = (OPT != VB200_OPT_SGD);
     constexpr bool HAS2 = (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW);
@@ -107,21 +116,22 @@ __global__ void __launch_bounds__(256) dp_reduce_update_kernel(PeerTable peers, 
 
 cudaError_t launch_dp_barrier(const PeerTable &peers, long long flags_off, int world, int rank,
                               const StepScalars *scalars, unsigned stride, unsigned index, unsigned int *status,
-                              cudaStream_t s) {
-    return launch_pdl(dp_barrier_kernel, dim3(1), dim3(32), 0, s, peers, flags_off, world, rank, scalars, stride, index, status);
+                              unsigned long long wait_ns, cudaStream_t s) {
+    return launch_pdl(dp_barrier_kernel, dim3(1), dim3(32), 0, s, peers, flags_off, world, rank, scalars, stride, index, status,
+                      wait_ns);
 }
 
 cudaError_t launch_dp_reduce_update(int optimizer, const PeerTable &peers, long long params_off, long long grads_off,
                                     long long s1_off, long long s2_off, long long seg_begin, long long seg_len,
                                     long long n_decay, int world, int rank, const StepScalars *scalars,
-                                    long long loss_off, cudaStream_t s) {
+                                    long long loss_off, const unsigned int *status, cudaStream_t s) {
     if (seg_len <= 0 || (seg_len & 3) || (seg_begin & 3)) return cudaErrorInvalidValue;
     const long long per = ((seg_len >> 2) + world - 1) / world;
     long long want = (per + 255) / 256;
     int blocks = (int)(want < 1 ? 1 : (want > 148 * 4 ? 148 * 4 : want));
 #define VB_DP_LAUNCH(O)                                                                                              \
     return launch_pdl(dp_reduce_update_kernel<O>, dim3(blocks), dim3(256), 0, s, peers, params_off, grads_off, s1_off, \
-                      s2_off, seg_begin, seg_len, n_decay, world, rank, scalars, loss_off)
+                      s2_off, seg_begin, seg_len, n_decay, world, rank, scalars, loss_off, status)
     switch (optimizer) {
     case VB200_OPT_SGD: VB_DP_LAUNCH(VB200_OPT_SGD);
     case VB200_OPT_ADAM: VB_DP_LAUNCH(VB200_OPT_ADAM);

@@ -65,16 +65,7 @@ __global__ void __launch_bounds__(256) optimizer_kernel(float *__restrict__ p, f
     }
 }
 
-static int g_sm_count = 0;
-static int sm_count() {
-    if (!g_sm_count) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (g_sm_count <= 0) g_sm_count = 148;
-    }
-    return g_sm_count;
-}
+static int sm_count() { return device_sm_count(); }
 
 cudaError_t launch_optimizer(int optimizer, float *p, float *s1, float *s2, const float *g, long long n,
                              long long n_decay, const StepScalars *sc, cudaStream_t s) {
@@ -96,6 +87,55 @@ cudaError_t launch_optimizer(int optimizer, float *p, float *s1, float *s2, cons
     default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------
+// Non-finite guard.  The reference's runtime loop fails fast on a non-finite loss, gradient,
+// parameter or optimizer-state element and names the first one (src/engine/ir/train.rs:670-773,
+// "Non-finite {stage} {label} at element {index}"); its generated step has no such check.  One
+// pass over the four flat regions finds, per region, the smallest index holding an inf or a NaN
+// (all ones = none): a minimum, so the answer does not depend on the order the blocks finish in.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) finite_guard_kernel(const float *__restrict__ p, const float *__restrict__ g,
+                                                           const float *__restrict__ s1, const float *__restrict__ s2,
+                                                           long long n, long long n_grads,
+                                                           unsigned long long *__restrict__ first_bad) {
+    __shared__ unsigned long long sm[4][8];
+    pdl_wait();
+    pdl_trigger();
+    const float *reg[4] = {g, p, s1, s2};
+    unsigned long long mine[4] = {~0ULL, ~0ULL, ~0ULL, ~0ULL};
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (int r = 0; r < 4; ++r) {
+        if (!reg[r]) continue;
+        const long long cnt = r == 0 ? n_grads : n;   // the gradient region carries the loss sum behind it
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < cnt; i += stride) {
+            const unsigned int bits = __float_as_uint(reg[r][i]);
+            if ((bits & 0x7F800000u) == 0x7F800000u) { mine[r] = (unsigned long long)i; break; }
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int r = 0; r < 4; ++r) {
+        unsigned long long v = mine[r];
+        for (int o = 16; o; o >>= 1) {
+            const unsigned long long w = __shfl_xor_sync(0xffffffffu, v, o);
+            v = w < v ? w : v;
+        }
+        if (lane == 0) sm[r][warp] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < 4) {
+        unsigned long long v = ~0ULL;
+        for (int w = 0; w < 8; ++w) v = sm[threadIdx.x][w] < v ? sm[threadIdx.x][w] : v;
+        if (v != ~0ULL) atomicMin(first_bad + threadIdx.x, v);
+    }
+}
+
+cudaError_t launch_finite_guard(const float *p, const float *g, const float *s1, const float *s2, long long n,
+                                long long n_grads, unsigned long long *first_bad, cudaStream_t s) {
+    long long want = (n + 255) / 256, cap = (long long)sm_count() * 8;
+    int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+    return launch_pdl(finite_guard_kernel, dim3(blocks), dim3(256), 0, s, p, g, s1, s2, n, n_grads, first_bad);
 }
 
 __global__ void set_scalars_kernel(StepScalars *dst, StepScalars v) { *dst = v; }

@@ -1,6 +1,7 @@
-// Tensor-core GEMM, second generation: same contract as vb_gemm_tc.cu (3xTF32 on tcgen05 with TMA
-// operands and TMEM accumulators, fused epilogues), restructured around the two things the first
-// kernel's profile showed:
+// Tensor-core GEMM, single-CTA version: C = op(A).op(B) in fp32 accuracy as 3xTF32 on tcgen05 with TMA
+// operands and TMEM accumulators and the fused epilogues of vb_common.cuh; one CTA per 128 x 128 tile.
+// Built around two facts measured on an earlier kernel that split every operand into explicit hi and
+// lo tiles and kept one accumulator for the whole K range:
 //
 //  * Shared-memory bandwidth binds.  The raw fp32 tile is now used IN PLACE as the high part: the
 //    tensor core reads only the top 19 bits of an operand, i.e. hi = trunc_tf32(x) for free.  The
@@ -17,7 +18,8 @@
 //    set the split warps add the other into fp32 registers with round-to-nearest.  The error no
 //    longer depends on K.
 //
-// Every mbarrier wait is bounded (~4 s), as in the first kernel.
+// Outputs of few tiles may split K over concurrent CTAs (slabs added in order by a second kernel).
+// Every mbarrier wait is bounded (~4 s).
 #include <cuda.h>
 
 #include <mutex>
@@ -25,13 +27,6 @@
 #include "vb_common.cuh"
 
 namespace vb {
-#ifdef VB_TRACE
-__device__ unsigned long long *g_trace = nullptr;  // [role][kb] timestamps of CTA 0, experiments only
-#define TRACE(role, kb) do { if (blockIdx.x == 0 && g_trace && (kb) < 256) g_trace[(role) * 256 + (kb)] = global_ns_(); } while (0)
-__device__ __forceinline__ unsigned long long global_ns_() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#else
-#define TRACE(role, kb) do {} while (0)
-#endif
 namespace {
 
 constexpr int BM = 128, BN = 128, BK = 32;
@@ -162,7 +157,7 @@ __device__ __forceinline__ void split_tile(const uint8_t *raw, uint8_t *lo_t, in
 template <bool A_KMAJOR, bool B_KMAJOR>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, long long M,
-                long long N, long long K, int tiles_m, int tiles_n, Epilogue epi, unsigned int *status) {
+                long long N, long long K, int tiles_m, int tiles_n, Epilogue epi, unsigned int *status, int splits) {
     extern __shared__ uint8_t smem_raw[];
     pdl_wait();   // nothing of the previous kernel's output is touched before this
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -173,10 +168,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid == 0) TRACE(5, 0);
     int tm, tn;
     {
-        const int t = blockIdx.x;
+        const int t = (int)blockIdx.x % (tiles_m * tiles_n);   // split-major grid
         const int band = t / (GROUP_M * tiles_n);
         const int first = band * GROUP_M;
         const int rows = min(GROUP_M, tiles_m - first);
@@ -185,7 +179,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         tn = local / rows;
     }
     const long long m0 = (long long)tm * BM, n0 = (long long)tn * BN;
-    const int kblocks = (int)((K + BK - 1) / BK);
+    // With split K, CTA b works on k-blocks [kb0, kb0 + kblocks) of tile b % tiles and stores its sums as
+    // slab b / tiles of the output buffer (the caller adds the slabs in order afterwards).
+    const int kblocks_all = (int)((K + BK - 1) / BK);
+    const int split = (int)blockIdx.x / (tiles_m * tiles_n);
+    const int kb_per_split = (kblocks_all + splits - 1) / splits;
+    const int kb0 = split * kb_per_split;
+    const int kblocks = max(0, min(kb_per_split, kblocks_all - kb0));
     const int nchunks = (kblocks + CHUNK - 1) / CHUNK;
 
     if (tid == 0) {
@@ -211,7 +211,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    if (tid == 0) TRACE(5, 1);
 
     if (warp == TMA_WARP) {
         if (lane == 0) {
@@ -221,12 +220,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const uint32_t ph = (uint32_t)((kb / RAW_STAGES) & 1);
                 // slot s was last read by the MMAs of k-block kb - RAW_STAGES
                 if (!mbar_wait(smem_u32(&mma_done[s]), ph ^ 1u, abort_flag, status, ST_STAGE_FREE)) break;
-                TRACE(4, kb);  // slot seen free by the producer
-                TRACE(0, kb);  // TMA issue
                 const uint32_t full = smem_u32(&raw_full[s]);
                 mbar_expect_tx(full, 2 * TILE_BYTES);
                 const uint32_t dst = smem_u32(smem + s * RING_BYTES);
-                const int k0 = kb * BK;
+                const int k0 = (kb0 + kb) * BK;
                 if (A_KMAJOR) {
                     tma_load_2d(dst, &map_a, full, k0, (int)m0);
                 } else {
@@ -270,7 +267,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         break;
                     }
                     tc_fence_after();
-                    TRACE(3, kb);  // MMA start
                     const uint32_t st = smem_u32(smem + s * RING_BYTES), sl = smem_u32(lo_ring + l * RING_BYTES);
 #pragma unroll
                     for (int j = 0; j < BK / 8; ++j) {
@@ -338,7 +334,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 ok = false;
                 break;
             }
-            if (tid == 0) TRACE(1, kb);  // raw tile seen by the split warps
             const uint8_t *st = smem + s * RING_BYTES;
             uint8_t *dl = lo_ring + l * RING_BYTES;
             split_tile(st, dl, tid);
@@ -346,14 +341,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&lo_full[l]));
-            if (tid == 0) TRACE(2, kb);  // split done
         }
-        if (tid == 0) TRACE(5, 2);
         while (ok && next_drain < nchunks) {
             ok = drain(next_drain);
             ++next_drain;
         }
-        if (tid == 0) TRACE(5, 3);
         if (tid == 0) pdl_trigger();   // the next kernel's CTAs may take SMs as ours retire
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
@@ -363,6 +355,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             // per instruction.
             constexpr int ST_LD = 68;   // floats per staged row: 16-byte aligned, four wavefronts per float4 write
             float *stage = reinterpret_cast<float *>(smem) + warp * (32 * ST_LD);
+            if (splits > 1) epi.out0 += (long long)split * M * N;   // this CTA's slab
 #pragma unroll
             for (int j = 0; j < 64; j += 4)
                 *reinterpret_cast<float4 *>(stage + lane * ST_LD + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
@@ -391,10 +384,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
         }
     }
-    if (tid == 0) TRACE(5, 4);
     tc_fence_before();
     __syncthreads();
-    if (tid == 0) TRACE(5, 5);
     if (warp == MMA_WARP) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
@@ -436,24 +427,20 @@ bool make_map2(CUtensorMap *map, const float *base, long long inner, long long o
 
 template <bool AK, bool BKM>
 cudaError_t launch2(const CUtensorMap &ma, const CUtensorMap &mb, long long m, long long n, long long k, int tiles_m,
-                    int tiles_n, const Epilogue &epi, unsigned int *status, cudaStream_t s) {
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel<AK, BKM>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
-    return launch_pdl(gemm_tc2_kernel<AK, BKM>, dim3(tiles_m * tiles_n), dim3(THREADS), SMEM_BYTES, s, ma, mb, m, n, k, tiles_m, tiles_n, epi, status);
+                    int tiles_n, const Epilogue &epi, unsigned int *status, cudaStream_t s, int splits) {
+    static bool configured[kMaxDevices] = {};
+    cudaError_t e = set_smem_once(gemm_tc2_kernel<AK, BKM>, SMEM_BYTES, configured);
+    if (e != cudaSuccess) return e;
+    return launch_pdl(gemm_tc2_kernel<AK, BKM>, dim3(tiles_m * tiles_n * splits), dim3(THREADS), SMEM_BYTES, s, ma, mb, m, n, k,
+                      tiles_m, tiles_n, epi, status, splits);
 }
 
 }  // namespace
 
-#ifdef VB_TRACE
-extern "C" void vb_trace_set(unsigned long long *p) { cudaMemcpyToSymbol(g_trace, &p, sizeof p); }
-#endif
 
 cudaError_t launch_gemm_tc2(int layout, const float *A, const float *B, long long m, long long n, long long k,
-                            const Epilogue &epi, unsigned int *status, cudaStream_t s) {
+                            const Epilogue &epi, unsigned int *status, cudaStream_t s, int splits) {
+    if (splits < 1 || (splits > 1 && epi.mode != EPI_STORE)) return cudaErrorInvalidValue;
     const bool a_kmajor = (layout != GEMM_TN), b_kmajor = (layout == GEMM_NT);
     CUtensorMap ma, mb;
     bool ok = a_kmajor ? make_map2(&ma, A, k, m, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B)
@@ -462,9 +449,9 @@ cudaError_t launch_gemm_tc2(int layout, const float *A, const float *B, long lon
                          : make_map2(&mb, B, n, k, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
     if (!ok) return cudaErrorNotSupported;
     const int tiles_m = (int)((m + BM - 1) / BM), tiles_n = (int)((n + BN - 1) / BN);
-    if (a_kmajor && b_kmajor) return launch2<true, true>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s);
-    if (a_kmajor && !b_kmajor) return launch2<true, false>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s);
-    if (!a_kmajor && !b_kmajor) return launch2<false, false>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s);
+    if (a_kmajor && b_kmajor) return launch2<true, true>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s, splits);
+    if (a_kmajor && !b_kmajor) return launch2<true, false>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s, splits);
+    if (!a_kmajor && !b_kmajor) return launch2<false, false>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s, splits);
     return cudaErrorNotSupported;
 }
 

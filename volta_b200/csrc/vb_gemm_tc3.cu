@@ -18,13 +18,6 @@
 #include "vb_common.cuh"
 
 namespace vb {
-#ifdef VB_TRACE
-__device__ unsigned long long *g_trace3 = nullptr;  // [cta][role][kb] timestamps of the first pair, experiments only
-__device__ __forceinline__ unsigned long long global_ns3_() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define TRACE(role, kb) do { if (blockIdx.x < 2 && g_trace3 && (kb) < 256) g_trace3[(blockIdx.x * 8 + (role)) * 256 + (kb)] = global_ns3_(); } while (0)
-#else
-#define TRACE(role, kb) do {} while (0)
-#endif
 namespace {
 
 constexpr int BM = 128, BN = 256, BK = 32;  // per CTA: 128 rows x 256 columns; the pair covers 256 x 256
@@ -253,7 +246,6 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const uint32_t ph = (uint32_t)((kb / RAW_STAGES) & 1);
                 // slot s was last read by the MMAs of k-block kb - RAW_STAGES
                 if (!mbar_wait(smem_u32(&mma_done[s]), ph ^ 1u, abort_flag, status, ST_STAGE_FREE)) break;
-                TRACE(0, kb);
                 const uint32_t full = smem_u32(&raw_full[s]);
                 mbar_expect_tx(full, 2 * TILE_BYTES);
                 const uint32_t dst = smem_u32(smem + s * RING_BYTES);
@@ -301,7 +293,6 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         break;
                     }
                     tc_fence_after();
-                    TRACE(3, kb);
                     const uint32_t st = smem_u32(smem + s * RING_BYTES), sl = smem_u32(lo_ring + l * RING_BYTES);
 #pragma unroll
                     for (int j = 0; j < BK / 8; ++j) {
@@ -337,10 +328,8 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         int next_drain = 0;
         auto drain = [&](int c) -> bool {
             const int set = c & 1;
-            if (tid == 0) TRACE(5, c);
             if (!mbar_wait(smem_u32(&acc_full[set]), (uint32_t)((c >> 1) & 1), abort_flag, status, ST_ACC_FULL)) return false;
             tc_fence_after();
-            if (tid == 0) TRACE(6, c);
 #pragma unroll
             for (int h = 0; h < 4; ++h) {
                 uint32_t v[16];
@@ -351,7 +340,6 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(lead_acc_empty0 + (uint32_t)set * 8u);
-            if (tid == 0) TRACE(7, c);
             return true;
         };
         for (int kb = 0; kb < kblocks; ++kb) {
@@ -376,7 +364,6 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 ok = false;
                 break;
             }
-            if (tid == 0) TRACE(1, kb);
             const uint8_t *st = smem + s * RING_BYTES;
             uint8_t *dl = lo_ring + l * RING_BYTES;
             split_tile(st, dl, tid);
@@ -384,7 +371,6 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(lead_lo_full0 + (uint32_t)l * 8u);
-            if (tid == 0) TRACE(2, kb);
         }
         while (ok && next_drain < nchunks) {
             ok = drain(next_drain);
@@ -473,12 +459,9 @@ bool make_map3(CUtensorMap *map, const float *base, long long inner, long long o
 template <bool AK, bool BKM>
 cudaError_t launch3(const CUtensorMap &ma, const CUtensorMap &mb, long long m, long long n, long long k, int tiles_m,
                     int tiles_n, const Epilogue &epi, unsigned int *status, cudaStream_t s, int splits) {
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc3_kernel<AK, BKM>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static bool configured[kMaxDevices] = {};
+    cudaError_t e = set_smem_once(gemm_tc3_kernel<AK, BKM>, SMEM_BYTES, configured);
+    if (e != cudaSuccess) return e;
     static const int chunk = [] { const char *e = getenv("VOLTA_B200_TC_CHUNK"); int v = e ? atoi(e) : DEFAULT_CHUNK; return v < 2 ? 2 : (v > 16 ? 16 : v); }();
     return launch_pdl(gemm_tc3_kernel<AK, BKM>, dim3(2 * tiles_m * tiles_n * splits), dim3(THREADS), SMEM_BYTES, s, ma, mb, m, n, k, tiles_m,
                       tiles_n, epi, status, chunk, splits);
@@ -486,9 +469,6 @@ cudaError_t launch3(const CUtensorMap &ma, const CUtensorMap &mb, long long m, l
 
 }  // namespace
 
-#ifdef VB_TRACE
-extern "C" void vb_trace3_set(unsigned long long *p) { cudaMemcpyToSymbol(g_trace3, &p, sizeof p); }
-#endif
 
 cudaError_t launch_gemm_tc3(int layout, const float *A, const float *B, long long m, long long n, long long k,
                             const Epilogue &epi, unsigned int *status, cudaStream_t s, int splits) {

@@ -15,6 +15,7 @@
 #include <math.h>
 #include <string.h>
 
+#include <algorithm>
 #include <map>
 #include <mutex>
 #include <string>
@@ -86,6 +87,10 @@ struct vb200_handle {
     float *mirror_params = nullptr, *mirror_grads = nullptr;  // pinned
     float *host_loss = nullptr;                               // pinned, one float per slot
     unsigned int *host_status = nullptr;                      // pinned
+    // non-finite guard (config check_finite): smallest bad index per region [grads+loss, params, state1, state2]
+    bool check_finite = false;
+    unsigned long long *first_bad = nullptr, *host_first_bad = nullptr;   // device (arena) / pinned
+    unsigned long long wait_ns = 4000000000ull;               // limit of the data-parallel barrier waits
     uint64_t adam_step = 0;
     uint64_t steps_done = 0;
     int last_slot = 0;
@@ -191,14 +196,12 @@ cudaError_t run_gemm(vb200_handle *h, int layout, const float *A, const float *B
         return launch_gemv_rows(A, Bm, m, n, k, epi, h->stream);
     if (path != VB200_GEMM_FFMA && gemm_tc_supported(layout, A, Bm, m, n, k, epi) &&
         (path == VB200_GEMM_TENSOR || path == VB200_GEMM_TENSOR_PAIR || gemm_prefers_tc(m, n, k))) {
-        gemm_tc_select_pair(path == VB200_GEMM_TENSOR_PAIR);
+        const bool force_pair = path == VB200_GEMM_TENSOR_PAIR;
         // a GEMM that splits K is two launches (the slab reduction follows it): count both
-        const int splits = gemm_tc_splits(layout, m, n, k);
+        const int splits = gemm_tc_splits(layout, m, n, k, force_pair);
         if (splits > 1 && h->gemm_scratch_floats >= (long long)splits * m * n) h->kernels_per_step++;
-        cudaError_t e = launch_gemm_tc(layout, A, Bm, m, n, k, epi, h->status_word, h->stream, h->gemm_scratch,
-                                       h->gemm_scratch_floats);
-        gemm_tc_select_pair(false);
-        return e;
+        return launch_gemm_tc(layout, A, Bm, m, n, k, epi, h->status_word, h->stream, h->gemm_scratch,
+                              h->gemm_scratch_floats, force_pair);
     }
     if (h->gemm_scratch && ffma_splits(m, n, k) > 1) h->kernels_per_step++;   // likewise on the FFMA path
     return launch_gemm_ffma(layout, A, Bm, m, n, k, epi, h->stream, h->gemm_scratch);
@@ -397,10 +400,10 @@ int enqueue_step(vb200_handle *h, int slot) {
             VB_CUDA(h, cudaStreamWaitEvent(h->comm_stream, h->ev_bucket[i], 0));
             h->kernels_per_step += 2;
             VB_CUDA(h, launch_dp_barrier(h->peers, h->off_flags, h->world, h->rank, h->scalars, (unsigned)(n + 2),
-                                         (unsigned)(n - i), h->status_word, h->comm_stream));
+                                         (unsigned)(n - i), h->status_word, h->wait_ns, h->comm_stream));
             VB_CUDA(h, launch_dp_reduce_update(h->cfg.optimizer, h->peers, h->off_params, h->off_grads, h->off_s1, h->off_s2,
                                                h->off_w[i], pad64(r * c), h->n_weights_padded, h->world, h->rank,
-                                               h->scalars, -1, h->comm_stream));
+                                               h->scalars, -1, h->status_word, h->comm_stream));
         }
     }
     if (two_sweeps) {
@@ -440,12 +443,13 @@ int enqueue_step(vb200_handle *h, int slot) {
         VB_CUDA(h, cudaStreamWaitEvent(h->comm_stream, h->ev_bucket[n], 0));
         h->kernels_per_step += 3;
         VB_CUDA(h, launch_dp_barrier(h->peers, h->off_flags, h->world, h->rank, h->scalars, (unsigned)(n + 2),
-                                     (unsigned)(n + 1), h->status_word, h->comm_stream));
+                                     (unsigned)(n + 1), h->status_word, h->wait_ns, h->comm_stream));
         VB_CUDA(h, launch_dp_reduce_update(h->cfg.optimizer, h->peers, h->off_params, h->off_grads, h->off_s1, h->off_s2,
                                            h->n_weights_padded, h->n_params_padded - h->n_weights_padded,
-                                           h->n_weights_padded, h->world, h->rank, h->scalars, h->off_loss, h->comm_stream));
+                                           h->n_weights_padded, h->world, h->rank, h->scalars, h->off_loss, h->status_word,
+                                           h->comm_stream));
         VB_CUDA(h, launch_dp_barrier(h->peers, h->off_flags, h->world, h->rank, h->scalars, (unsigned)(n + 2),
-                                     (unsigned)(n + 2), h->status_word, h->comm_stream));
+                                     (unsigned)(n + 2), h->status_word, h->wait_ns, h->comm_stream));
         VB_CUDA(h, cudaEventRecord(h->ev_join, h->comm_stream));
         VB_CUDA(h, cudaStreamWaitEvent(s, h->ev_join, 0));
     }
@@ -491,6 +495,17 @@ int enqueue_step(vb200_handle *h, int slot) {
             VB_CUDA(h, launch_optimizer(VB200_OPT_SGD, h->ln_params, nullptr, nullptr, h->ln_grads, h->ln_floats, 0,
                                         h->scalars, s));
         }
+    }
+    if (h->check_finite) {
+        const int opt = h->cfg.optimizer;
+        const bool has1 = opt != VB200_OPT_SGD, has2 = (opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW);
+        Scope sc(h, "finite_guard", 0.0, 4.0 * h->n_params_padded * (2 + (has1 ? 1 : 0) + (has2 ? 1 : 0)));
+        VB_CUDA(h, cudaMemsetAsync(h->first_bad, 0xFF, 4 * sizeof(unsigned long long), s));
+        // the gradient region carries the loss sum right behind it (one more float, or two when the fused
+        // data-parallel path keeps the all-rank total beside the local sum)
+        VB_CUDA(h, launch_finite_guard(h->params, h->grads, has1 ? h->s1 : nullptr, has2 ? h->s2 : nullptr,
+                                       h->n_params_padded, h->n_params_padded + (h->dp_fused ? 2 : 1), h->first_bad, s));
+        VB_CUDA(h, cudaMemcpyAsync(h->host_first_bad, h->first_bad, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s));
     }
     VB_CUDA(h, cudaMemcpyAsync(&h->host_loss[slot], h->dp_fused ? h->loss_sum + 1 : h->loss_sum, sizeof(float),
                                cudaMemcpyDeviceToHost, s));
@@ -557,8 +572,58 @@ int copy_inputs(vb200_handle *h, int slot, const float *X, const float *Y, bool 
     return VB200_OK;
 }
 
+// Name of the tensor that holds flat index `idx` of the parameter layout, and the index inside it.
+std::string flat_name(const vb200_handle *h, unsigned long long idx, unsigned long long *local) {
+    for (int i = 0; i < h->n; ++i) {
+        const unsigned long long w0 = (unsigned long long)h->off_w[i], wn = (unsigned long long)h->L[i] * h->L[i + 1];
+        if (idx >= w0 && idx < w0 + wn) { *local = idx - w0; return "'layer" + std::to_string(i) + ".weight'"; }
+        const unsigned long long b0 = (unsigned long long)h->off_b[i], bn = (unsigned long long)h->L[i + 1];
+        if (idx >= b0 && idx < b0 + bn) { *local = idx - b0; return "'layer" + std::to_string(i) + ".bias'"; }
+    }
+    *local = idx;
+    return "(padding)";
+}
+
+// What the last finished step left in pinned memory: the status word of the device-side waits and,
+// under check_finite, the first non-finite element per region (message as the reference's
+// ensure_finite_tensor, src/engine/ir/train.rs:681-701).
+int check_device_status(vb200_handle *h) {
+    if (h->host_status && *h->host_status != 0) {
+        char buf[160];
+        snprintf(buf, sizeof buf, "a device-side wait gave up (status word 0x%08x%s)", *h->host_status,
+                 (*h->host_status & kStatusDpBarrier) ? ": a data-parallel rank did not reach a barrier in time; no update was applied" : "");
+        return h->fail(VB200_ERR_DEVICE_WAIT, buf);
+    }
+    if (h->check_finite && h->host_first_bad) {
+        static const char *kind[4] = {"gradient", "parameter", "optimizer_state.1", "optimizer_state.2"};
+        for (int r = 0; r < 4; ++r) {
+            const unsigned long long idx = h->host_first_bad[r];
+            if (idx == ~0ULL) continue;
+            std::string msg;
+            if (r == 0 && idx >= (unsigned long long)h->n_params_padded) {
+                msg = "Non-finite train loss";
+            } else {
+                unsigned long long local = 0;
+                const std::string name = flat_name(h, idx, &local);
+                msg = std::string("Non-finite train ") + kind[r] + " " + name + " at element " + std::to_string(local);
+            }
+            return h->fail(VB200_ERR_NONFINITE, msg + " (step " + std::to_string((unsigned long long)h->steps_done) + ")");
+        }
+    }
+    return VB200_OK;
+}
+
 int do_step(vb200_handle *h, const float *X, const float *Y, float lr, bool profile) {
     if (!X || !Y) return h->reject(VB200_ERR_INVALID, "volta_b200_step: null input pointer");
+    // A handle that failed (a device-side wait that ran out, a CUDA or NCCL error, a non-finite value
+    // under check_finite) takes no further steps: its state is no longer one the reference could reach,
+    // and after a data-parallel wait gave up a peer may be gone.  The status word of the last finished
+    // step sits in pinned memory, so looking costs nothing.
+    if (h->status != VB200_OK) return h->status;
+    {
+        int rc0 = check_device_status(h);
+        if (rc0) return rc0;
+    }
     const int slot = profile ? 0 : (int)(h->steps_done & 1);
     bool host_wait = false;
     int rc = copy_inputs(h, slot, X, Y, &host_wait);
@@ -584,14 +649,6 @@ int do_step(vb200_handle *h, const float *X, const float *Y, float lr, bool prof
     return VB200_OK;
 }
 
-int check_device_status(vb200_handle *h) {
-    if (h->host_status && *h->host_status != 0) {
-        char buf[96];
-        snprintf(buf, sizeof buf, "a device-side wait gave up (status word 0x%08x)", *h->host_status);
-        return h->fail(VB200_ERR_DEVICE_WAIT, buf);
-    }
-    return VB200_OK;
-}
 
 void destroy(vb200_handle *h) {
     if (!h) return;
@@ -627,6 +684,7 @@ void destroy(vb200_handle *h) {
     if (h->mirror_grads) cudaFreeHost(h->mirror_grads);
     if (h->host_loss) cudaFreeHost(h->host_loss);
     if (h->host_status) cudaFreeHost(h->host_status);
+    if (h->host_first_bad) cudaFreeHost(h->host_first_bad);
     if (h->stream) cudaStreamDestroy(h->stream);
     if (h->copy_stream) cudaStreamDestroy(h->copy_stream);
     if (h->comm_stream) cudaStreamDestroy(h->comm_stream);
@@ -651,6 +709,8 @@ int validate(const vb200_config *c, std::string *why) {
     if (c->rank < 0 || c->rank >= world) { *why = "rank out of range"; return VB200_ERR_INVALID; }
     if (c->global_batch != 0 && c->global_batch < c->batch) { *why = "global_batch smaller than batch"; return VB200_ERR_INVALID; }
     if (c->gemm_path < VB200_GEMM_AUTO || c->gemm_path > VB200_GEMM_TENSOR_PAIR) { *why = "unknown gemm_path"; return VB200_ERR_INVALID; }
+    if (c->device_wait_ms < 0) { *why = "device_wait_ms must not be negative"; return VB200_ERR_INVALID; }
+    if (c->check_finite != 0 && c->check_finite != 1) { *why = "check_finite must be 0 or 1"; return VB200_ERR_INVALID; }
     return VB200_OK;
 }
 
@@ -715,9 +775,10 @@ void make_plan(const vb200_config &c, ArenaPlan &pl, PlanIdx &ix, std::vector<in
         if (i > 0) gs = std::max(gs, ffma_scratch_floats(B, r, cc)); // dX
         // slabs of tensor GEMMs that split K to fill their last wave (not with SGD folded into dW: its
         // epilogue then runs in the slab reduction all the same, so the scratch is needed either way)
-        gs = std::max(gs, gemm_tc_scratch_floats(GEMM_NN, B, cc, r));
-        gs = std::max(gs, gemm_tc_scratch_floats(GEMM_TN, r, cc, B));
-        if (i > 0) gs = std::max(gs, gemm_tc_scratch_floats(GEMM_NT, B, r, cc));
+        const bool fp = c.gemm_path == VB200_GEMM_TENSOR_PAIR;
+        gs = std::max(gs, gemm_tc_scratch_floats(GEMM_NN, B, cc, r, fp));
+        gs = std::max(gs, gemm_tc_scratch_floats(GEMM_TN, r, cc, B, fp));
+        if (i > 0) gs = std::max(gs, gemm_tc_scratch_floats(GEMM_NT, B, r, cc, fp));
     }
     ix.gs = pl.add("gemm_splitk_scratch", gs * 4, 0, end, true);
     for (int s = 0; s < 2; ++s) {
@@ -827,6 +888,14 @@ int build(vb200_handle *h) {
     h->off_s1 = pl.offset(i_s1);
     h->off_s2 = pl.offset(i_s2);
     h->off_flags = pl.offset(i_sc) + 768;   // 8 barrier words behind the scalars (offset 0) and the status word (512)
+    h->first_bad = reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(at(i_sc)) + 832);
+    h->check_finite = c.check_finite == 1;
+    {
+        // limit of the data-parallel barrier waits: the configuration, else VOLTA_B200_WAIT_MS, else 4 s
+        long long ms = c.device_wait_ms;
+        if (ms <= 0) { const char *e = getenv("VOLTA_B200_WAIT_MS"); ms = e ? atoll(e) : 0; }
+        if (ms > 0) h->wait_ns = (unsigned long long)ms * 1000000ull;
+    }
     h->off_loss = h->off_grads + P * 4;
 
     for (int s = 0; s < 2; ++s) { h->xin[s] = at(i_x[s]); h->yin[s] = at(i_y[s]); }
@@ -848,6 +917,8 @@ int build(vb200_handle *h) {
     VB_CUDA(h, cudaMallocHost(&h->mirror_params, (size_t)P * 4));
     VB_CUDA(h, cudaMallocHost(&h->host_loss, 2 * sizeof(float)));
     VB_CUDA(h, cudaMallocHost(&h->host_status, sizeof(unsigned int)));
+    VB_CUDA(h, cudaMallocHost(&h->host_first_bad, 4 * sizeof(unsigned long long)));
+    for (int r = 0; r < 4; ++r) h->host_first_bad[r] = ~0ULL;
     h->host_loss[0] = h->host_loss[1] = 0.0f;
     *h->host_status = 0;
     memset(h->mirror_params, 0, (size_t)P * 4);
@@ -1067,6 +1138,68 @@ const char *state1_suffix(int opt) {
     }
     return nullptr;
 }
+
+// Which checkpoint entries feed layer i: "<base[i]>.weight" [in, out] and "<base[i]>.bias" [out].
+// The reference names a layer's tensors after the layer's user-chosen name
+// (src/engine/model/layers.rs:52-58: "{name}.weight", "{name}.bias"), so the bases are
+//   1. the caller's names, where given (a null entry stands for "layer<i>");
+//   2. else "layer<i>", the names this library writes, if the checkpoint holds any of them;
+//   3. else the prefixes X of all entries "X.weight" (2-D) that have an "X.bias", in the sorted order
+//      the reference's writer uses, provided there are exactly n of them and their shapes are the
+//      topology's, layer by layer.
+// Returns how many parameter tensors (weights and biases) were found with the right shape; 0 or a
+// wrong shape fills *why.
+int resolve_layer_names(const std::vector<int> &L, const vb::Checkpoint &ck, const char *const *names, int32_t n_names,
+                        std::vector<std::string> *base, std::string *why) {
+    const int n = (int)L.size() - 1;
+    base->assign((size_t)n, std::string());
+    auto count_matches = [&](bool *bad_shape) -> int {
+        int found = 0;
+        for (int i = 0; i < n; ++i) {
+            const int64_t r = L[(size_t)i], c = L[(size_t)i + 1];
+            if (const vb::CheckpointEntry *e = ck.find((*base)[(size_t)i] + ".weight")) {
+                if (e->shape != std::vector<int64_t>{r, c}) { *bad_shape = true; *why = "'" + e->name + "' has the wrong shape"; return 0; }
+                ++found;
+            }
+            if (const vb::CheckpointEntry *e = ck.find((*base)[(size_t)i] + ".bias")) {
+                if (e->shape != std::vector<int64_t>{c}) { *bad_shape = true; *why = "'" + e->name + "' has the wrong shape"; return 0; }
+                ++found;
+            }
+        }
+        return found;
+    };
+    bool bad = false;
+    if (names) {
+        if (n_names != n) { *why = "need one layer name per weight layer"; return 0; }
+        for (int i = 0; i < n; ++i) (*base)[(size_t)i] = names[i] ? std::string(names[i]) : "layer" + std::to_string(i);
+        const int found = count_matches(&bad);
+        if (!found && !bad) *why = "the checkpoint holds no '<name>.weight' or '<name>.bias' for the given layer names";
+        return found;
+    }
+    for (int i = 0; i < n; ++i) (*base)[(size_t)i] = "layer" + std::to_string(i);
+    int found = count_matches(&bad);
+    if (found || bad) return found;
+    std::vector<std::string> prefixes;
+    for (const vb::CheckpointEntry &e : ck.entries) {
+        const std::string sfx = ".weight";
+        if (e.name.size() > sfx.size() && e.name.compare(e.name.size() - sfx.size(), sfx.size(), sfx) == 0 &&
+            e.shape.size() == 2) {
+            const std::string p = e.name.substr(0, e.name.size() - sfx.size());
+            if (ck.find(p + ".bias")) prefixes.push_back(p);
+        }
+    }
+    std::sort(prefixes.begin(), prefixes.end());
+    if ((int)prefixes.size() != n) {
+        *why = "no tensor is named 'layer<i>.weight' / 'layer<i>.bias', and the checkpoint's " +
+               std::to_string(prefixes.size()) + " '<name>.weight' + '<name>.bias' pairs do not number the topology's " +
+               std::to_string(n) + " layers: pass the layer names";
+        return 0;
+    }
+    *base = prefixes;
+    found = count_matches(&bad);
+    if (bad) *why += " (layers taken in sorted name order; pass the layer names to choose another order)";
+    return found;
+}
 }  // namespace
 
 vb200_checkpoint *volta_b200_checkpoint_new(void) { return new vb200_checkpoint(); }
@@ -1134,8 +1267,36 @@ int volta_b200_checkpoint_entry(const vb200_checkpoint *ck, int32_t i, const cha
     return VB200_OK;
 }
 
+int volta_b200_checkpoint_match(const vb200_config *cfg, const vb200_checkpoint *ck, const char *const *layer_names,
+                                int32_t n_names) {
+    std::string why;
+    int rc = validate(cfg, &why);
+    if (rc == VB200_OK && !ck) { rc = VB200_ERR_INVALID; why = "null checkpoint"; }
+    if (rc != VB200_OK) {
+        set_global_error(rc, why);
+        return -rc;
+    }
+    std::vector<std::string> base;
+    const int found = resolve_layer_names(std::vector<int>(cfg->layers, cfg->layers + cfg->n_sizes), ck->ck, layer_names,
+                                          n_names, &base, &why);
+    if (!found) {
+        set_global_error(VB200_ERR_INVALID, why);
+        return -VB200_ERR_INVALID;
+    }
+    return found;
+}
+
 int volta_b200_export_checkpoint(vb200_handle *h, vb200_checkpoint *ck, int32_t with_state) {
+    return volta_b200_export_checkpoint_named(h, ck, with_state, nullptr, 0);
+}
+
+int volta_b200_export_checkpoint_named(vb200_handle *h, vb200_checkpoint *ck, int32_t with_state,
+                                       const char *const *layer_names, int32_t n_names) {
     if (!h || !ck) return VB200_ERR_INVALID;
+    if (layer_names && n_names != h->n) return h->reject(VB200_ERR_INVALID, "export_checkpoint: need one layer name per weight layer");
+    auto base_of = [&](int i) -> std::string {
+        return (layer_names && layer_names[i]) ? std::string(layer_names[i]) : "layer" + std::to_string(i);
+    };
     if (with_state && h->dp_fused)
         return h->reject(VB200_ERR_UNSUPPORTED, "export_checkpoint: optimizer state is sharded over the ranks in fused data-parallel mode");
     const int opt = h->cfg.optimizer;
@@ -1146,7 +1307,7 @@ int volta_b200_export_checkpoint(vb200_handle *h, vb200_checkpoint *ck, int32_t 
         VB_CUDA(h, cudaMemcpy(host.data(), dev, (size_t)P * 4, cudaMemcpyDeviceToHost));
         for (int i = 0; i < h->n; ++i) {
             const int64_t r = h->L[i], c = h->L[i + 1];
-            const std::string base = "layer" + std::to_string(i);
+            const std::string base = base_of(i);
             ck->ck.put(base + wsuffix, {r, c}, host.data() + h->off_w[i], (size_t)(r * c));
             ck->ck.put(base + bsuffix, {c}, host.data() + h->off_b[i], (size_t)c);
         }
@@ -1159,8 +1320,8 @@ int volta_b200_export_checkpoint(vb200_handle *h, vb200_checkpoint *ck, int32_t 
         VB_CUDA(h, cudaMemcpy(ln.data(), h->ln_params, ln.size() * 4, cudaMemcpyDeviceToHost));
         for (int k = 0; k + 1 < h->n; ++k) {
             const int64_t c = h->L[k + 1];
-            ck->ck.put("layer" + std::to_string(k) + ".ln_gamma", {c}, ln.data() + h->off_ln[k], (size_t)c);
-            ck->ck.put("layer" + std::to_string(k) + ".ln_beta", {c}, ln.data() + h->off_ln[k] + c, (size_t)c);
+            ck->ck.put(base_of(k) + ".ln_gamma", {c}, ln.data() + h->off_ln[k], (size_t)c);
+            ck->ck.put(base_of(k) + ".ln_beta", {c}, ln.data() + h->off_ln[k] + c, (size_t)c);
         }
     }
     if (with_state) {
@@ -1186,7 +1347,19 @@ int volta_b200_export_checkpoint(vb200_handle *h, vb200_checkpoint *ck, int32_t 
 }
 
 int volta_b200_import_checkpoint(vb200_handle *h, const vb200_checkpoint *ck) {
+    return volta_b200_import_checkpoint_named(h, ck, nullptr, 0);
+}
+
+int volta_b200_import_checkpoint_named(vb200_handle *h, const vb200_checkpoint *ck, const char *const *layer_names,
+                                       int32_t n_names) {
     if (!h || !ck) return VB200_ERR_INVALID;
+    std::vector<std::string> bases;
+    {
+        // a checkpoint that names none of this topology's parameters is an error, not a silent no-op
+        std::string why;
+        if (!resolve_layer_names(h->L, ck->ck, layer_names, n_names, &bases, &why))
+            return h->reject(VB200_ERR_INVALID, "import_checkpoint: " + why);
+    }
     const int opt = h->cfg.optimizer;
     const int64_t P = h->n_params_padded;
     VB_CUDA(h, cudaStreamSynchronize(h->stream));
@@ -1197,7 +1370,7 @@ int volta_b200_import_checkpoint(vb200_handle *h, const vb200_checkpoint *ck) {
         bool any = false;
         for (int i = 0; i < h->n; ++i) {
             const int64_t r = h->L[i], c = h->L[i + 1];
-            const std::string base = "layer" + std::to_string(i);
+            const std::string &base = bases[(size_t)i];
             if (const vb::CheckpointEntry *e = ck->ck.find(base + wsuffix)) {
                 if (e->shape != std::vector<int64_t>{r, c})
                     return h->reject(VB200_ERR_INVALID, "import_checkpoint: '" + e->name + "' has the wrong shape");
@@ -1221,8 +1394,8 @@ int volta_b200_import_checkpoint(vb200_handle *h, const vb200_checkpoint *ck) {
         VB_CUDA(h, cudaMemcpy(ln.data(), h->ln_params, ln.size() * 4, cudaMemcpyDeviceToHost));
         for (int k = 0; k + 1 < h->n; ++k) {
             const int64_t c = h->L[k + 1];
-            const vb::CheckpointEntry *g = ck->ck.find("layer" + std::to_string(k) + ".ln_gamma");
-            const vb::CheckpointEntry *b = ck->ck.find("layer" + std::to_string(k) + ".ln_beta");
+            const vb::CheckpointEntry *g = ck->ck.find(bases[(size_t)k] + ".ln_gamma");
+            const vb::CheckpointEntry *b = ck->ck.find(bases[(size_t)k] + ".ln_beta");
             for (const vb::CheckpointEntry *e : {g, b})
                 if (e && e->shape != std::vector<int64_t>{c})
                     return h->reject(VB200_ERR_INVALID, "import_checkpoint: '" + e->name + "' has the wrong shape");
@@ -1473,7 +1646,47 @@ int volta_b200_dp_attach_peers(vb200_handle *h, const uint8_t *handles, int32_t 
     return VB200_OK;
 }
 
-int volta_b200_dp_unique_id(uint8_t out[128]) { return DpComm::unique_id(out) ? VB200_ERR_NCCL : VB200_OK; }
+int volta_b200_dp_wait_selftest(vb200_handle *h, int32_t declared_world, int32_t wait_ms) {
+    if (!h) return VB200_ERR_INVALID;
+    if (declared_world < 2 || declared_world > kMaxPeers || wait_ms <= 0 || wait_ms > 10000)
+        return h->reject(VB200_ERR_INVALID, "dp_wait_selftest: world must lie in 2..8 and wait_ms in 1..10000");
+    if (h->dp_fused) return h->reject(VB200_ERR_INVALID, "dp_wait_selftest: not on a handle attached to peers");
+    // every "peer" is this handle's own arena: slot 0 of the flag words gets written, the others never do
+    PeerTable self{};
+    for (int q = 0; q < kMaxPeers; ++q) self.base[q] = h->arena;
+    VB_CUDA(h, cudaStreamSynchronize(h->stream));
+    VB_CUDA(h, launch_dp_barrier(self, h->off_flags, declared_world, 0, h->scalars, 1u, 0x7ffffff0u, h->status_word,
+                                 (unsigned long long)wait_ms * 1000000ull, h->stream));
+    VB_CUDA(h, cudaMemcpyAsync(h->host_status, h->status_word, sizeof(unsigned int), cudaMemcpyDeviceToHost, h->stream));
+    VB_CUDA(h, cudaStreamSynchronize(h->stream));
+    return check_device_status(h);
+}
+
+int volta_b200_dp_unique_id(uint8_t out[128]) {
+    if (!out) return VB200_ERR_INVALID;
+    std::string why;
+    if (DpComm::unique_id(out, &why)) {
+        set_global_error(VB200_ERR_NCCL, why);
+        return VB200_ERR_NCCL;
+    }
+    return VB200_OK;
+}
+
+int volta_b200_dp_check(const uint8_t id[128], int32_t world_size, int32_t rank, float *device_buf, int64_t count,
+                        void *stream) {
+    if (!id || world_size < 1 || rank < 0 || rank >= world_size || count < 0 || (count > 0 && !device_buf)) {
+        set_global_error(VB200_ERR_INVALID, "dp_check: bad argument");
+        return VB200_ERR_INVALID;
+    }
+    DpComm comm;
+    int rc = comm.init(id, world_size, rank);
+    if (!rc && count > 0) rc = comm.all_reduce_sum(device_buf, count, (cudaStream_t)stream);
+    if (rc) {
+        set_global_error(VB200_ERR_NCCL, comm.error());
+        return VB200_ERR_NCCL;
+    }
+    return VB200_OK;
+}
 
 // ---- stand-alone kernel entry points ------------------------------------------------------
 int volta_b200_optimizer_apply(int32_t optimizer, float *p, float *s1, float *s2, const float *g, int64_t n,
@@ -1504,18 +1717,17 @@ int volta_b200_gemm(int32_t layout, int32_t path, float *C, const float *A, cons
     cudaError_t err;
     if (path == VB200_GEMM_TENSOR || path == VB200_GEMM_TENSOR_PAIR) {
         if (!gemm_tc_supported(layout, A, B, m, n, k, e)) return VB200_ERR_UNSUPPORTED;
-        gemm_tc_select_pair(path == VB200_GEMM_TENSOR_PAIR);
+        const bool force_pair = path == VB200_GEMM_TENSOR_PAIR;
         unsigned int *st = nullptr;
         if (cudaMalloc(&st, sizeof(unsigned int)) != cudaSuccess) return VB200_ERR_OOM;
         cudaMemsetAsync(st, 0, sizeof(unsigned int), s);
         float *slabs = nullptr;
-        const long long slab_floats = gemm_tc_scratch_floats(layout, m, n, k);
+        const long long slab_floats = gemm_tc_scratch_floats(layout, m, n, k, force_pair);
         if (slab_floats > 0 && cudaMalloc(&slabs, (size_t)slab_floats * 4) != cudaSuccess) {
             cudaGetLastError();
             slabs = nullptr;   // no room: the unsplit kernel
         }
-        err = launch_gemm_tc(layout, A, B, m, n, k, e, st, s, slabs, slabs ? slab_floats : 0);
-        gemm_tc_select_pair(false);
+        err = launch_gemm_tc(layout, A, B, m, n, k, e, st, s, slabs, slabs ? slab_floats : 0, force_pair);
         unsigned int hs = 0;
         if (err == cudaSuccess) err = cudaMemcpyAsync(&hs, st, sizeof hs, cudaMemcpyDeviceToHost, s);
         if (err == cudaSuccess) err = cudaStreamSynchronize(s);
@@ -1536,6 +1748,24 @@ int volta_b200_gemm(int32_t layout, int32_t path, float *C, const float *A, cons
         }
     }
     return err == cudaSuccess ? VB200_OK : VB200_ERR_CUDA;
+}
+
+int volta_b200_gemm_route(int32_t layout, int32_t path, int64_t m, int64_t n, int64_t k, int32_t *splits) {
+    if (splits) *splits = 1;
+    if (m <= 0 || n <= 0 || k <= 0 || layout < GEMM_NN || layout > GEMM_TN) return -VB200_ERR_INVALID;
+    // alignment aside (operands of a handle are 1 KiB aligned), the same decisions as run_gemm above
+    const long long a_inner = (layout == GEMM_TN) ? m : k, b_inner = (layout == GEMM_NT) ? k : n;
+    const bool tc_shape = !((a_inner | b_inner) & 3) && m <= 0x7fffffffLL && n <= 0x7fffffffLL && k <= 0x7fffffffLL;
+    if (layout == GEMM_NN && path == VB200_GEMM_AUTO && m <= 8 && gemv_rows_supported(reinterpret_cast<const float *>(uintptr_t(1024)), m, n, k))
+        return VB200_ROUTE_SMALL_ROWS;
+    if (path != VB200_GEMM_FFMA && tc_shape &&
+        (path == VB200_GEMM_TENSOR || path == VB200_GEMM_TENSOR_PAIR || gemm_prefers_tc(m, n, k))) {
+        const bool fp = path == VB200_GEMM_TENSOR_PAIR;
+        if (splits) *splits = gemm_tc_splits(layout, m, n, k, fp);
+        return gemm_tc_uses_pair(layout, m, n, k, fp) ? VB200_ROUTE_TENSOR_PAIR : VB200_ROUTE_TENSOR_SINGLE;
+    }
+    if (splits) *splits = ffma_splits(m, n, k);
+    return VB200_ROUTE_FFMA;
 }
 
 int64_t volta_b200_colsum_scratch_floats(int64_t rows, int64_t cols) {

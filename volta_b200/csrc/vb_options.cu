@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(ROW_THREADS) row_forward_kernel(float *__restr
             // the mask stream is sequential: every thread takes a contiguous share of the row,
             // jumps the generator to its first draw and steps from there
             __syncthreads();
-            const float keep_scale = (float)(1.0 / (1.0 - (double)o.dropout_p));
+            const float keep_scale = __fdiv_rn(1.0f, __fsub_rn(1.0f, o.dropout_p));   // f32 throughout, as :775
             const int chunk = (cols + ROW_THREADS - 1) / ROW_THREADS;
             const int j0 = t * chunk;
             int j1 = j0 + chunk;
@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(ROW_THREADS) row_backward_kernel(float *__rest
     pdl_trigger();
     const int t = threadIdx.x;
     const float fc = (float)cols;
-    const float keep_scale = o.dropout_p > 0.0f ? (float)(1.0 / (1.0 - (double)o.dropout_p)) : 1.0f;
+    const float keep_scale = o.dropout_p > 0.0f ? __fdiv_rn(1.0f, __fsub_rn(1.0f, o.dropout_p)) : 1.0f;   // f32, as :890
     for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
         float *g = delta + r * cols;
         const float *a1 = o.a1 + r * cols;
@@ -276,16 +276,7 @@ __global__ void __launch_bounds__(256) clip_scale_kernel(float *__restrict__ v, 
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) v[i] = __fmul_rn(v[i], scale);
 }
 
-int g_sms = 0;
-int sms() {
-    if (!g_sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
-        if (g_sms <= 0) g_sms = 148;
-    }
-    return g_sms;
-}
+int sms() { return device_sm_count(); }
 
 // CTAs for a one-row-per-CTA kernel with `smem` bytes each: as many as stay resident, at most one per row
 int row_grid(long long rows, size_t smem) {

@@ -21,7 +21,8 @@ class Config(C.Structure):
         ("rank", C.c_int32), ("nccl_unique_id", C.c_uint8 * 128), ("momentum", C.c_float),
         ("weight_decay", C.c_float), ("gemm_path", C.c_int32), ("use_graph", C.c_int32),
         ("force_dp", C.c_int32), ("fuse_sgd", C.c_int32), ("use_layernorm", C.c_int32), ("dropout_p", C.c_float),
-        ("clip_grad", C.c_float), ("reserved", C.c_int32 * 3),
+        ("clip_grad", C.c_float), ("device_wait_ms", C.c_int32), ("check_finite", C.c_int32),
+        ("reserved", C.c_int32 * 1),
     ]
 
 
@@ -49,7 +50,9 @@ EXPORTS = [
     "volta_b200_colsum_scratch_floats", "volta_b200_colsum", "volta_b200_colsum_noalloc", "volta_b200_version",
     "volta_b200_checkpoint_new", "volta_b200_checkpoint_free", "volta_b200_checkpoint_add", "volta_b200_checkpoint_save",
     "volta_b200_checkpoint_load", "volta_b200_checkpoint_parse", "volta_b200_checkpoint_count", "volta_b200_checkpoint_entry",
-    "volta_b200_export_checkpoint", "volta_b200_import_checkpoint",
+    "volta_b200_export_checkpoint", "volta_b200_import_checkpoint", "volta_b200_export_checkpoint_named",
+    "volta_b200_import_checkpoint_named", "volta_b200_checkpoint_match", "volta_b200_dp_wait_selftest", "volta_b200_dp_check",
+    "volta_b200_gemm_route",
     "volta_b200_program_new", "volta_b200_program_free", "volta_b200_program_error", "volta_b200_program_add",
     "volta_b200_program_mark_output", "volta_b200_program_compile", "volta_b200_program_bind", "volta_b200_program_run",
     "volta_b200_program_fetch", "volta_b200_program_update",
@@ -117,6 +120,12 @@ def load_library():
                                                   C.POINTER(i32), C.POINTER(fp), C.POINTER(i64)]),
         "volta_b200_export_checkpoint": (C.c_int, [vp, vp, i32]),
         "volta_b200_import_checkpoint": (C.c_int, [vp, vp]),
+        "volta_b200_export_checkpoint_named": (C.c_int, [vp, vp, i32, C.POINTER(C.c_char_p), i32]),
+        "volta_b200_import_checkpoint_named": (C.c_int, [vp, vp, C.POINTER(C.c_char_p), i32]),
+        "volta_b200_checkpoint_match": (C.c_int, [C.POINTER(Config), vp, C.POINTER(C.c_char_p), i32]),
+        "volta_b200_dp_wait_selftest": (C.c_int, [vp, i32, i32]),
+        "volta_b200_dp_check": (C.c_int, [C.c_char_p, i32, i32, vp, i64, vp]),
+        "volta_b200_gemm_route": (C.c_int, [i32, i32, i64, i64, i64, C.POINTER(i32)]),
         "volta_b200_program_new": (vp, []),
         "volta_b200_program_free": (None, [vp]),
         "volta_b200_program_error": (C.c_char_p, [vp]),

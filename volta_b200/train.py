@@ -53,7 +53,8 @@ class TrainHandle:
 
     def __init__(self, layers, activation="relu", optimizer="sgd", batch=1, *, global_batch=0, world_size=1, rank=0,
                  unique_id: bytes | None = None, momentum=0.0, weight_decay=0.0, gemm_path="auto", use_graph=True,
-                 force_dp=False, fuse_sgd=False, dropout_p=0.0, use_layernorm=False, clip_grad=0.0):
+                 force_dp=False, fuse_sgd=False, dropout_p=0.0, use_layernorm=False, clip_grad=0.0, device_wait_ms=0,
+                 check_finite=False):
         act = activation.lower()
         opt = optimizer.lower()
         if act not in ACTIVATIONS:
@@ -91,6 +92,8 @@ class TrainHandle:
         cfg.dropout_p = float(dropout_p)
         cfg.use_layernorm = 1 if use_layernorm else 0
         cfg.clip_grad = float(clip_grad)
+        cfg.device_wait_ms = int(device_wait_ms)
+        cfg.check_finite = 1 if check_finite else 0
         self.dropout_p = float(dropout_p)
         self._cfg = cfg
         h = C.c_void_p()
@@ -213,16 +216,31 @@ class TrainHandle:
                     buf[base + ob[i]: base + ob[i] + bs[i].size] = np.asarray(bs[i], np.float32).ravel()
         self.load_state(buf[:n], step)
 
-    def export_checkpoint(self, with_state: bool = True):
-        """Parameters (and, with_state, optimizer moments and counters) as a named-tensor Checkpoint."""
+    def _names(self, layer_names):
+        if layer_names is None:
+            return None, 0
+        arr = (C.c_char_p * len(layer_names))(*[None if v is None else str(v).encode() for v in layer_names])
+        return arr, len(layer_names)
+
+    def export_checkpoint(self, with_state: bool = True, layer_names=None):
+        """Parameters (and, with_state, optimizer moments and counters) as a named-tensor Checkpoint.
+        layer_names: one name per weight layer (Volta names tensors "{layer name}.weight"); default "layer<i>"."""
         from .checkpoint import Checkpoint
         ck = Checkpoint()
-        self._check(self.lib.volta_b200_export_checkpoint(self.h, ck.h, 1 if with_state else 0))
+        arr, n = self._names(layer_names)
+        self._check(self.lib.volta_b200_export_checkpoint_named(self.h, ck.h, 1 if with_state else 0, arr, n))
         return ck
 
-    def import_checkpoint(self, ck):
-        """Take every tensor the checkpoint names for this topology; other names are ignored."""
-        self._check(self.lib.volta_b200_import_checkpoint(self.h, ck.h))
+    def import_checkpoint(self, ck, layer_names=None):
+        """Take every tensor the checkpoint names for this topology; other names are ignored.  Without
+        layer_names: "layer<i>.*", else the checkpoint's "<X>.weight"/"<X>.bias" pairs in sorted order.
+        A checkpoint in which no parameter tensor is found raises."""
+        arr, n = self._names(layer_names)
+        self._check(self.lib.volta_b200_import_checkpoint_named(self.h, ck.h, arr, n))
+
+    def dp_wait_selftest(self, declared_world: int = 2, wait_ms: int = 50):
+        """One barrier kernel whose peers never answer: raises VoltaB200Error (device wait) after wait_ms."""
+        self._check(self.lib.volta_b200_dp_wait_selftest(self.h, int(declared_world), int(wait_ms)))
 
     def ipc_handle(self) -> bytes:
         """64-byte handle of this rank's arena, to be exchanged among the data-parallel ranks."""
