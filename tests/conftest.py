@@ -24,3 +24,21 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture
+def parity_report(request):
+    """Records achieved errors: report(kind, **numbers) prints one line per record and, when
+    $VOLTA_B200_PARITY_REPORT names a file, appends it there as JSON (the tables of achieved parity in the
+    design notes are made from such a file)."""
+    import json
+
+    def report(kind, **numbers):
+        rec = dict(test=request.node.name, kind=kind, **numbers)
+        print("parity:", json.dumps(rec))
+        path = os.environ.get("VOLTA_B200_PARITY_REPORT")
+        if path:
+            with open(path, "a") as f:
+                f.write(json.dumps(rec) + "\n")
+
+    return report

@@ -88,3 +88,57 @@ def gpu_shard_worker(rank, world, port, opt, out_dir, repeat, fused=False, act="
         h.free()
         dist.barrier()
     dist.destroy_process_group()
+
+
+def gpu_missing_rank_worker(rank, world, port, out_dir, wait_ms=200):
+    """Two ranks on the fused peer-memory path take two steps together; then rank 1 sits a step out (alive,
+    its arena still mapped, nothing of its own in flight) while rank 0 steps alone with a short wait limit.
+    Rank 0 records what it saw: the error code, and its parameters before and after the lonely step."""
+    import ctypes as C
+    import torch
+    import torch.distributed as dist
+    from volta_b200 import TrainHandle, VoltaB200Error
+    from volta_b200.train import dp_unique_id
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+    x, y, ws, bs = inputs()
+    B = GLOBAL_BATCH // world
+    xs, ys = np.ascontiguousarray(x[rank * B:(rank + 1) * B]), np.ascontiguousarray(y[rank * B:(rank + 1) * B])
+    box = [dp_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    h = TrainHandle(LAYERS, "silu", "adam", B, global_batch=GLOBAL_BATCH, world_size=world, rank=rank, unique_id=box[0],
+                    device_wait_ms=wait_ms)
+    handles = [None] * world
+    dist.all_gather_object(handles, h.ipc_handle())
+    h.attach_peers(handles)
+    for i, (w, b) in enumerate(zip(ws, bs)):
+        h.set_params(i, w, b)
+    for _ in range(2):
+        h.step(xs, ys, 0.01)
+        h.loss()
+    before = sum(h.get_params(), [])
+    dist.barrier()                       # both ranks idle, nothing in flight
+    if rank == 0:
+        code, msg = 0, ""
+        h.step(xs, ys, 0.01)             # rank 1 never joins this one
+        try:
+            h.loss()
+        except VoltaB200Error as e:
+            code, msg = e.code, str(e)
+        fp = C.POINTER(C.c_float)
+        wo, bo = (fp * h.n)(), (fp * h.n)()
+        rc = h.lib.volta_b200_get_params(h.h, wo, bo)
+        after = [np.ctypeslib.as_array(wo[i], shape=(LAYERS[i], LAYERS[i + 1])).copy() for i in range(h.n)] + \
+                [np.ctypeslib.as_array(bo[i], shape=(LAYERS[i + 1],)).copy() for i in range(h.n)]
+        refused = 0
+        try:
+            h.step(xs, ys, 0.01)
+        except VoltaB200Error as e:
+            refused = e.code
+        np.savez(os.path.join(out_dir, "rank0.npz"), code=code, msg=msg, get_params_rc=rc, refused=refused,
+                 **{"before%d" % i: a for i, a in enumerate(before)}, **{"after%d" % i: a for i, a in enumerate(after)})
+    dist.barrier()                       # rank 1 learns on the host that the step is over
+    h.free()
+    dist.barrier()
+    dist.destroy_process_group()

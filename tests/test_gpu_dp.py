@@ -72,11 +72,12 @@ def test_fused_peer_memory_update_on_a_single_rank_matches_the_plain_path(opt):
         assert np.array_equal(a, b)
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("mode", ["nccl", "fused"])
 @pytest.mark.parametrize("opt", ["sgd_momentum", "adam"])
-def test_two_gpu_ranks_match_the_full_batch_oracle(opt, mode):
-    world = 2
+def test_gpu_ranks_match_the_full_batch_oracle(opt, mode, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
     out = tempfile.mkdtemp()
     mp.spawn(dpc.gpu_shard_worker, args=(world, _free_port(), opt, out, 2, mode == "fused"), nprocs=world, join=True)
     x, y, ws, bs = dpc.inputs()
@@ -143,3 +144,20 @@ def test_two_gpu_ranks_with_the_optional_stages_match_the_full_batch_oracle():
     for i in range(len(pw)):
         assert np.array_equal(runs[0][0]["w%d" % i], runs[1][0]["w%d" % i])
     assert np.array_equal(runs[0][0]["losses"], runs[1][0]["losses"])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_a_rank_that_sits_a_step_out_is_detected_and_no_update_is_applied(monkeypatch):
+    """Failure detection on the fused peer-memory path, made on the host: rank 1 stays alive with its arena
+    mapped but does not take the third step.  Rank 0's barrier gives up after its limit (200 ms), the
+    reduce + update kernels then touch no rank's memory, the step reports VB200_ERR_DEVICE_WAIT, rank 0's
+    parameters are bit-identical to before the step and further steps are refused.  No rank is killed."""
+    monkeypatch.setenv("NCCL_NVLS_ENABLE", "0")
+    out = tempfile.mkdtemp()
+    mp.spawn(dpc.gpu_missing_rank_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    r = np.load("%s/rank0.npz" % out)
+    assert int(r["code"]) == 5 and "did not reach a barrier" in str(r["msg"])
+    assert int(r["get_params_rc"]) == 5 and int(r["refused"]) == 5
+    n = sum(1 for k in r.files if k.startswith("before"))
+    for i in range(n):
+        assert np.array_equal(r["before%d" % i].view(np.uint32), r["after%d" % i].view(np.uint32)), i
