@@ -97,7 +97,9 @@ typedef struct vb200_config {
                                           runtime loop does (src/engine/ir/train.rs:670-773; its generated step has
                                           no such check); the next call that waits for the step returns
                                           VB200_ERR_NONFINITE naming the first bad element.  Off by default */
-    int32_t reserved[1];
+    int32_t step_kernel;               /* the whole step as ONE persistent kernel (one GPU, batch <= 64, widths up to
+                                          64 x SMs/4, none of the optional stages): 0 = wherever that applies and
+                                          gemm_path is AUTO, 1 = never, 2 = required (create fails otherwise) */
 } vb200_config;
 
 typedef struct vb200_handle vb200_handle;
@@ -122,7 +124,7 @@ int volta_b200_step(vb200_handle *h, const float *X, const float *Y, float lr);
 float volta_b200_loss(vb200_handle *h);
 
 /* volta_train_set_params(h, li, w, b) (mlp_train_rust_codegen.rs:670-675).
- * Host pointers; an out-of-range li is ignored, as in the reference. */
+ * Host or device pointers; an out-of-range li is ignored, as in the reference. */
 int volta_b200_set_params(vb200_handle *h, int32_t li, const float *w, const float *b);
 
 /* volta_train_get_params(h, wo, bo) (mlp_train_rust_codegen.rs:678-684).
@@ -228,7 +230,10 @@ int32_t volta_b200_kernels_per_step(vb200_handle *h);
 
 /* Runs one step as plain launches with a CUDA event pair around every kernel and
  * returns up to `max` records: name (<= 47 chars), milliseconds, algorithmic flops and
- * bytes of that launch. Returns the number of records, or a negative error code. */
+ * bytes of that launch. Returns the number of records, or a negative error code.
+ * Under NCCL data parallelism every rank must make the call (it is a step); the record
+ * "wait_for_gradient_exchange" is then the part of the all-reduces that the backward GEMMs did
+ * not hide.  Not available with the fused peer-memory exchange. */
 typedef struct vb200_kernel_record {
     char name[48];
     float ms;

@@ -93,7 +93,7 @@ class TorchMlp64:
             self.db[i] = delta.sum(dim=0)
             if i > 0:
                 delta = (delta @ self.w[i].T) * _dact(self.act, pres[i - 1], acts[i])
-        self.acts = acts
+        self.acts, self.pres = acts, pres
 
     def update(self, lr: float):
         lr = float(np.float32(lr))   # the step takes lr as an f32 (volta_train_step's signature)
@@ -144,3 +144,18 @@ class TorchMlp64:
         resid_rms = max(self.loss_value, 1e-300) ** 0.5
         amplify = max(1.0, out_max / resid_rms)
         return [v * amplify for v in sw + sb]
+
+    def fragile_units(self, band: float = 1e-5):
+        """Hidden units whose pre-activation lies inside the fp32 noise of its own sum, |pre| <= band * (|act| . |W|
+        + |b|): for relu / leaky_relu their derivative (0 or 1) may come out differently in two correct fp32
+        evaluations.  Returns, per hidden layer i, the sorted column indices with at least one such row, and the total
+        count of (row, column) cases.  Empty for smooth activations."""
+        cols, total = [], 0
+        if self.act not in ("relu", "leaky_relu"):
+            return [np.zeros(0, np.int64) for _ in range(self.n - 1)], 0
+        for i in range(self.n - 1):
+            bound = self.acts[i].abs() @ self.w[i].abs() + self.b[i].abs()
+            frag = self.pres[i].abs() <= band * bound
+            total += int(frag.sum())
+            cols.append(torch.nonzero(frag.any(dim=0)).reshape(-1).numpy())
+        return cols, total

@@ -302,6 +302,35 @@ cudaError_t launch_dp_reduce_update(int optimizer, const PeerTable &peers, long 
                                     long long loss_off, const unsigned int *status, cudaStream_t s);
 constexpr unsigned kStatusDpBarrier = 64u;   // status-word bit: a data-parallel barrier wait ran out
 
+// ---- the whole step as one persistent kernel, batches of at most 64 rows (vb_step_small.cu)
+constexpr int kSmallStepMaxLayers = 16;
+struct SmallStepLayer {
+    int r, c;                  // W is [r x c]
+    long long off_w, off_b;    // floats from the start of the flat parameter / gradient / state regions
+    const float *act_in;       // [B x r]
+    float *act_out;            // [B x c]
+    float *pre_out;            // [B x c] or null: the pre-activation, where backward needs it
+    float *delta;              // [B x c]
+    const float *saved_prev;   // [B x r]: what the previous layer's activation derivative takes; null for layer 0
+    float *delta_prev;         // [B x r]; null for layer 0
+};
+struct SmallStepArgs {
+    int n, B, act, opt;
+    int forward_only;          // 1: stop after the last layer's outputs (inference); B is then the row count
+    float *params, *grads, *s1, *s2;
+    long long n_params_padded;
+    const float *y;            // [B x L_n]
+    float *loss_sum, *loss_partials;   // one float; one float per CTA
+    float nt_global;
+    const StepScalars *scalars;
+    unsigned int *barrier;     // {arrivals, generation, abort}
+    unsigned int *status;
+    SmallStepLayer L[kSmallStepMaxLayers];
+};
+bool small_step_shape_ok(const int *layers, int n_sizes, int batch, int clusters);
+int small_step_grid(int optimizer, int *cluster);
+cudaError_t launch_small_step(const SmallStepArgs &args, int grid, int cluster, cudaStream_t s);
+
 long long colsum_chunks(long long rows, long long cols);
 // out[j] = sum_rows in[row, j] * (row_weight ? row_weight[row] : 1), fixed order
 cudaError_t launch_colsum(float *out, const float *in, long long rows, long long cols, float *scratch, cudaStream_t s,
@@ -341,6 +370,10 @@ cudaError_t launch_sumsq_partials(float *partial, const float *v, long long n, c
 cudaError_t launch_sum_partials(float *out, const float *partial, long long nblocks, cudaStream_t s);
 // v *= clip/sqrt(*norm_sq) when sqrt(*norm_sq) > clip, else untouched
 cudaError_t launch_clip_scale(float *v, long long n, const float *norm_sq, float clip, cudaStream_t s);
+
+// out[row, k] = delta[row] * w[k] * f'(saved[row, k])  (saved may be null: no derivative factor)
+cudaError_t launch_rank1_dx(float *out, const float *delta, const float *w, const float *saved, int act, long long rows,
+                            long long cols, cudaStream_t s);
 
 long long loss_blocks(long long nt);
 // delta[k] = 2*(out[k]-y[k])/nt_global ; *loss_sum = sum_k (out[k]-y[k])^2 (fixed order)

@@ -273,6 +273,54 @@ cudaError_t launch_rowdot(float *out, const float *in, const float *w, const flo
 }
 
 // ---------------------------------------------------------------------------------------
+// dX of a width-one layer (the output layer of every benchmark model): delta . W^T with W an [r x 1]
+// column is the outer product delta[row] * w[k], times the previous layer's activation derivative
+// (mlp_train_rust_codegen.rs:894-929).  One streaming pass: reads `saved`, writes the result, 8 bytes per
+// element, against a GEMM that would pad the single column to a tile.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) rank1_dx_kernel(float *__restrict__ out, const float *__restrict__ delta,
+                                                       const float *__restrict__ w, const float *__restrict__ saved, int act,
+                                                       long long rows, long long cols, int vec) {
+    pdl_wait();
+    pdl_trigger();
+    const long long stride = (long long)gridDim.x * blockDim.x, t0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (vec) {
+        const long long c4 = cols >> 2, total = rows * c4;
+        for (long long i = t0; i < total; i += stride) {
+            const long long row = i / c4, k = (i - row * c4) << 2;
+            const float d = delta[row];
+            const float4 wv = __ldg(reinterpret_cast<const float4 *>(w + k));
+            float4 o = make_float4(d * wv.x, d * wv.y, d * wv.z, d * wv.w);
+            if (saved) {
+                const float4 sv = __ldcs(reinterpret_cast<const float4 *>(saved + row * cols + k));
+                o.x *= act_backward(act, sv.x); o.y *= act_backward(act, sv.y);
+                o.z *= act_backward(act, sv.z); o.w *= act_backward(act, sv.w);
+            }
+            *reinterpret_cast<float4 *>(out + row * cols + k) = o;
+        }
+    } else {
+        const long long total = rows * cols;
+        for (long long i = t0; i < total; i += stride) {
+            const long long row = i / cols, k = i - row * cols;
+            float o = delta[row] * w[k];
+            if (saved) o *= act_backward(act, saved[i]);
+            out[i] = o;
+        }
+    }
+}
+
+cudaError_t launch_rank1_dx(float *out, const float *delta, const float *w, const float *saved, int act, long long rows,
+                            long long cols, cudaStream_t s) {
+    if (rows <= 0 || cols <= 0) return cudaErrorInvalidValue;
+    const int vec = (cols & 3) == 0 && ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(w) |
+                                         reinterpret_cast<uintptr_t>(saved)) & 15) == 0;
+    const long long work = vec ? rows * (cols >> 2) : rows * cols;
+    long long want = (work + 255) / 256, cap = (long long)sm_count() * 8;
+    int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+    return launch_pdl(rank1_dx_kernel, dim3(blocks), dim3(256), 0, s, out, delta, w, saved, act, rows, cols, vec);
+}
+
+// ---------------------------------------------------------------------------------------
 // MSE loss and seed gradient (mlp_train_rust_codegen.rs:793-798):
 //   d = out - y ; delta = (2*d)/nt ; loss = (sum d*d)/nt     (division by nt on the host)
 // nt is the GLOBAL element count under data parallelism, so that shard gradients add up.

@@ -21,14 +21,16 @@ namespace vb {
 namespace {
 
 constexpr int BM = 128, BN = 256, BK = 32;  // per CTA: 128 rows x 256 columns; the pair covers 256 x 256
-constexpr int RAW_STAGES = 4, LO_STAGES = 2;   // raw tiles stay from load to MMA, low parts only from split to MMA
+constexpr int RAW_STAGES = 4;   // raw tiles stay from the TMA load until the MMAs that read them retire
+// Low parts stay only from the split to the same MMAs: 2 slots by default, 3 (all 227 KB of shared memory) with
+// VOLTA_B200_TC_LO=3, which lets the split warps run one k-block further ahead of the tensor pipe.
 constexpr int SPLIT_WARPS = 16, SPLIT_THREADS = SPLIT_WARPS * 32;
 constexpr int TMA_WARP = SPLIT_WARPS, MMA_WARP = SPLIT_WARPS + 1;
 constexpr int THREADS = (SPLIT_WARPS + 2) * 32;
 constexpr int TILE_BYTES = 128 * BK * 4;        // 16 KiB
 constexpr int RING_BYTES = 2 * TILE_BYTES;      // one ring slot: A tile + this CTA's half of the B tile
-constexpr int SMEM_TILES = (RAW_STAGES + LO_STAGES) * RING_BYTES;
-constexpr int SMEM_BYTES = SMEM_TILES + 256 + 1024;
+constexpr int smem_tiles(int lo_stages) { return (RAW_STAGES + lo_stages) * RING_BYTES; }
+constexpr int smem_bytes(int lo_stages) { return smem_tiles(lo_stages) + 256 + 1024; }
 constexpr int TMEM_COLS = 512;                  // 2 accumulator sets x 256 columns
 constexpr int DEFAULT_CHUNK = 4;                // k-blocks per accumulator drain (48 additions per accumulator)
                     // drain chunk c-1 when about to split k-block c*CHUNK + LAG
@@ -175,7 +177,7 @@ __device__ __forceinline__ void split_tile(const uint8_t *raw, uint8_t *lo_t, in
     }
 }
 
-template <bool A_KMAJOR, bool B_KMAJOR>
+template <bool A_KMAJOR, bool B_KMAJOR, int LO_STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, long long M,
                 long long N, long long K, int tiles_m, int tiles_n, Epilogue epi, unsigned int *status, int CHUNK,
@@ -183,6 +185,7 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     extern __shared__ uint8_t smem_raw[];
     pdl_wait();   // nothing of the previous kernel's output is touched before this
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int SMEM_TILES = smem_tiles(LO_STAGES);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + SMEM_TILES);
     uint64_t *raw_full = bars, *lo_full = bars + 8, *mma_done = bars + 16, *acc_full = bars + 24, *acc_empty = bars + 26;
     uint8_t *lo_ring = smem + RAW_STAGES * RING_BYTES;
@@ -456,15 +459,23 @@ bool make_map3(CUtensorMap *map, const float *base, long long inner, long long o
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+template <bool AK, bool BKM, int LO>
+cudaError_t launch3lo(const CUtensorMap &ma, const CUtensorMap &mb, long long m, long long n, long long k, int tiles_m,
+                      int tiles_n, const Epilogue &epi, unsigned int *status, cudaStream_t s, int splits) {
+    static bool configured[kMaxDevices] = {};
+    cudaError_t e = set_smem_once(gemm_tc3_kernel<AK, BKM, LO>, smem_bytes(LO), configured);
+    if (e != cudaSuccess) return e;
+    static const int chunk = [] { const char *e = getenv("VOLTA_B200_TC_CHUNK"); int v = e ? atoi(e) : DEFAULT_CHUNK; return v < 2 ? 2 : (v > 16 ? 16 : v); }();
+    return launch_pdl(gemm_tc3_kernel<AK, BKM, LO>, dim3(2 * tiles_m * tiles_n * splits), dim3(THREADS), smem_bytes(LO), s, ma, mb, m, n, k,
+                      tiles_m, tiles_n, epi, status, chunk, splits);
+}
+
 template <bool AK, bool BKM>
 cudaError_t launch3(const CUtensorMap &ma, const CUtensorMap &mb, long long m, long long n, long long k, int tiles_m,
                     int tiles_n, const Epilogue &epi, unsigned int *status, cudaStream_t s, int splits) {
-    static bool configured[kMaxDevices] = {};
-    cudaError_t e = set_smem_once(gemm_tc3_kernel<AK, BKM>, SMEM_BYTES, configured);
-    if (e != cudaSuccess) return e;
-    static const int chunk = [] { const char *e = getenv("VOLTA_B200_TC_CHUNK"); int v = e ? atoi(e) : DEFAULT_CHUNK; return v < 2 ? 2 : (v > 16 ? 16 : v); }();
-    return launch_pdl(gemm_tc3_kernel<AK, BKM>, dim3(2 * tiles_m * tiles_n * splits), dim3(THREADS), SMEM_BYTES, s, ma, mb, m, n, k, tiles_m,
-                      tiles_n, epi, status, chunk, splits);
+    static const int lo = [] { const char *e = getenv("VOLTA_B200_TC_LO"); return (e && atoi(e) == 3) ? 3 : 2; }();
+    if (lo == 3) return launch3lo<AK, BKM, 3>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s, splits);
+    return launch3lo<AK, BKM, 2>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s, splits);
 }
 
 }  // namespace

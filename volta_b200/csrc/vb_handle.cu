@@ -105,6 +105,11 @@ struct vb200_handle {
     std::map<long long, cudaGraphExec_t> infer_graphs;
     bool use_graph = true;
     bool fuse_sgd = false;   // plain SGD on one GPU: dW GEMMs update W in their epilogue
+    // the whole step as one persistent kernel (batches of at most 64 rows on one GPU; vb_step_small.cu)
+    bool small_step = false;
+    bool ss_forward = false;   // the same kernel, forward only, serves inference of 9..64 rows
+    int ss_grid = 0, ss_cluster = 0;
+    unsigned int *grid_barrier = nullptr;   // {arrivals, generation, abort} in the arena
     int kernels_per_step = 0;
 
     DpComm *dp = nullptr;
@@ -172,8 +177,9 @@ void lcg_xavier(float *w, int64_t n, int r, int c, uint64_t *rng) {
 struct Scope {
     vb200_handle *h;
     bool on;
-    Scope(vb200_handle *h_, const char *name, double flops, double bytes) : h(h_), on(h_->profiling) {
-        h->kernels_per_step++;
+    // is_kernel = false: a timed wait (for the gradient exchange), not one of this library's launches
+    Scope(vb200_handle *h_, const char *name, double flops, double bytes, bool is_kernel = true) : h(h_), on(h_->profiling) {
+        if (is_kernel) h->kernels_per_step++;
         if (!on) return;
         KernelRecord r;
         r.name = name;
@@ -207,6 +213,8 @@ cudaError_t run_gemm(vb200_handle *h, int layout, const float *A, const float *B
     return launch_gemm_ffma(layout, A, Bm, m, n, k, epi, h->stream, h->gemm_scratch);
 }
 
+int enqueue_small_step(vb200_handle *h, int slot, int rows = 0);
+
 // Forward pass over the first `rows` rows of input slot `slot` (rows <= batch): every layer's GEMM
 // with bias and activation fused.  Used by the training step (rows = batch) and by inference.
 int enqueue_forward(vb200_handle *h, int slot, long long rows, bool training, const float *in_override = nullptr,
@@ -219,6 +227,14 @@ int enqueue_forward(vb200_handle *h, int slot, long long rows, bool training, co
     float *const last_out = out_override ? out_override : h->act[n];
     auto A = [&](int i) -> float * { return i == 0 ? const_cast<float *>(act0) : h->act[i]; };
     char nm[64];
+    // inference of 9..64 rows: the persistent kernel's forward half, one launch (fewer rows take the
+    // cluster kernel below, layer by layer, straight from and to pinned memory)
+    if (!training && h->ss_forward && rows > 8 && rows <= 64 && !in_override && !out_override) {
+        const int saved = h->kernels_per_step;
+        int rc = enqueue_small_step(h, slot, (int)rows);
+        h->kernels_per_step = saved;
+        return rc;
+    }
     for (int i = 0; i < n; ++i) {
         const long long r = L[i], c = L[i + 1];
         Epilogue e{};
@@ -269,7 +285,77 @@ int enqueue_forward(vb200_handle *h, int slot, long long rows, bool training, co
 }
 
 // Enqueue one whole step on h->stream reading inputs from `slot`.
+// Tail of every step: the optional non-finite guard, then loss and status word to pinned memory.
+int enqueue_step_tail(vb200_handle *h, int slot) {
+    cudaStream_t s = h->stream;
+    if (h->check_finite) {
+        const int opt = h->cfg.optimizer;
+        const bool has1 = opt != VB200_OPT_SGD, has2 = (opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW);
+        Scope sc(h, "finite_guard", 0.0, 4.0 * h->n_params_padded * (2 + (has1 ? 1 : 0) + (has2 ? 1 : 0)));
+        VB_CUDA(h, cudaMemsetAsync(h->first_bad, 0xFF, 4 * sizeof(unsigned long long), s));
+        // the gradient region carries the loss sum right behind it (one more float, or two when the fused
+        // data-parallel path keeps the all-rank total beside the local sum)
+        VB_CUDA(h, launch_finite_guard(h->params, h->grads, has1 ? h->s1 : nullptr, has2 ? h->s2 : nullptr,
+                                       h->n_params_padded, h->n_params_padded + (h->dp_fused ? 2 : 1), h->first_bad, s));
+        VB_CUDA(h, cudaMemcpyAsync(h->host_first_bad, h->first_bad, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s));
+    }
+    VB_CUDA(h, cudaMemcpyAsync(&h->host_loss[slot], h->dp_fused ? h->loss_sum + 1 : h->loss_sum, sizeof(float),
+                               cudaMemcpyDeviceToHost, s));
+    VB_CUDA(h, cudaMemcpyAsync(h->host_status, h->status_word, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
+    return VB200_OK;
+}
+
+// One launch for the whole step: forward, loss, backward and update inside one persistent kernel
+// (rows = batch), or for the forward pass alone (inference of `rows` rows).
+int enqueue_small_step(vb200_handle *h, int slot, int rows) {
+    const int n = h->n, B = rows > 0 ? rows : h->B;
+    const std::vector<int> &L = h->L;
+    if (rows == 0) h->kernels_per_step = 0;
+    SmallStepArgs a{};
+    a.n = n;
+    a.B = B;
+    a.forward_only = rows > 0 ? 1 : 0;
+    a.act = h->cfg.activation;
+    a.opt = h->cfg.optimizer;
+    a.params = h->params;
+    a.grads = h->grads;
+    a.s1 = h->s1;
+    a.s2 = h->s2;
+    a.n_params_padded = h->n_params_padded;
+    a.y = h->yin[slot];
+    a.loss_sum = h->loss_sum;
+    a.loss_partials = h->mse_scratch;
+    a.nt_global = (float)h->global_nt;
+    a.scalars = h->scalars;
+    a.barrier = h->grid_barrier;
+    a.status = h->status_word;
+    double flops = 0.0;
+    for (int i = 0; i < n; ++i) {
+        SmallStepLayer &l = a.L[i];
+        l.r = L[i];
+        l.c = L[i + 1];
+        l.off_w = h->off_w[i];
+        l.off_b = h->off_b[i];
+        l.act_in = i == 0 ? h->xin[slot] : h->act[i];
+        l.act_out = h->act[i + 1];
+        l.pre_out = (i < n - 1 && h->keep_pre) ? h->pre[i] : nullptr;
+        l.delta = h->delta[i];
+        l.saved_prev = i == 0 ? nullptr : (h->keep_pre ? h->pre[i - 1] : h->act[i]);
+        l.delta_prev = i == 0 ? nullptr : h->delta[i - 1];
+        flops += 2.0 * B * L[i] * L[i + 1] * (i == 0 ? 2.0 : 3.0);
+    }
+    const int opt = h->cfg.optimizer;
+    const double bpp = opt == VB200_OPT_SGD ? 16.0 : (opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW) ? 32.0 : 24.0;
+    {
+        // compulsory traffic: W read forward, then W / state read and W / state / gradient written once
+        Scope sc(h, rows > 0 ? "small_forward" : "small_step", flops, bpp * h->n_params_padded);
+        VB_CUDA(h, launch_small_step(a, h->ss_grid, h->ss_cluster, h->stream));
+    }
+    return rows > 0 ? VB200_OK : enqueue_step_tail(h, slot);
+}
+
 int enqueue_step(vb200_handle *h, int slot) {
+    if (h->small_step) return enqueue_small_step(h, slot);
     const int n = h->n, B = h->B, act = h->cfg.activation;
     const std::vector<int> &L = h->L;
     cudaStream_t s = h->stream;
@@ -333,6 +419,14 @@ int enqueue_step(vb200_handle *h, int slot) {
         } else {
             e.mode = EPI_DACT;
             e.saved = h->keep_pre ? h->pre[i - 1] : h->act[i];
+        }
+        if (c == 1 && h->cfg.gemm_path == VB200_GEMM_AUTO) {
+            // width-one layer: the product is an outer product, one streaming pass
+            snprintf(nm, sizeof nm, "dX%d_rank1_%lldx%lld", i, (long long)B, r);
+            Scope sc(h, nm, 2.0 * B * r, 4.0 * (B + r + 2.0 * B * r));
+            VB_CUDA(h, launch_rank1_dx(e.out0, h->delta[i], h->params + h->off_w[i], e.mode == EPI_DACT ? e.saved : nullptr, act,
+                                       B, r, s));
+            return VB200_OK;
         }
         snprintf(nm, sizeof nm, "dX%d_gemm_nt_%lldx%lldx%lld", i, (long long)B, r, c);
         Scope sc(h, nm, 2.0 * B * r * c, 4.0 * (B * c + r * c + 2.0 * B * r));
@@ -462,6 +556,8 @@ int enqueue_step(vb200_handle *h, int slot) {
         int rc = h->dp->all_reduce_sum(h->grads + h->n_weights_padded, cnt, h->comm_stream);
         if (rc) return h->fail(VB200_ERR_NCCL, h->dp->error());
         VB_CUDA(h, cudaEventRecord(h->ev_join, h->comm_stream));
+        // what of the exchange is NOT hidden under the backward GEMMs shows up as this wait
+        Scope sc(h, "wait_for_gradient_exchange", 0.0, 0.0, false);
         VB_CUDA(h, cudaStreamWaitEvent(s, h->ev_join, 0));
     }
     // update
@@ -496,21 +592,7 @@ int enqueue_step(vb200_handle *h, int slot) {
                                         h->scalars, s));
         }
     }
-    if (h->check_finite) {
-        const int opt = h->cfg.optimizer;
-        const bool has1 = opt != VB200_OPT_SGD, has2 = (opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW);
-        Scope sc(h, "finite_guard", 0.0, 4.0 * h->n_params_padded * (2 + (has1 ? 1 : 0) + (has2 ? 1 : 0)));
-        VB_CUDA(h, cudaMemsetAsync(h->first_bad, 0xFF, 4 * sizeof(unsigned long long), s));
-        // the gradient region carries the loss sum right behind it (one more float, or two when the fused
-        // data-parallel path keeps the all-rank total beside the local sum)
-        VB_CUDA(h, launch_finite_guard(h->params, h->grads, has1 ? h->s1 : nullptr, has2 ? h->s2 : nullptr,
-                                       h->n_params_padded, h->n_params_padded + (h->dp_fused ? 2 : 1), h->first_bad, s));
-        VB_CUDA(h, cudaMemcpyAsync(h->host_first_bad, h->first_bad, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s));
-    }
-    VB_CUDA(h, cudaMemcpyAsync(&h->host_loss[slot], h->dp_fused ? h->loss_sum + 1 : h->loss_sum, sizeof(float),
-                               cudaMemcpyDeviceToHost, s));
-    VB_CUDA(h, cudaMemcpyAsync(h->host_status, h->status_word, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
-    return VB200_OK;
+    return enqueue_step_tail(h, slot);
 }
 
 int capture_graphs(vb200_handle *h) {
@@ -711,6 +793,7 @@ int validate(const vb200_config *c, std::string *why) {
     if (c->gemm_path < VB200_GEMM_AUTO || c->gemm_path > VB200_GEMM_TENSOR_PAIR) { *why = "unknown gemm_path"; return VB200_ERR_INVALID; }
     if (c->device_wait_ms < 0) { *why = "device_wait_ms must not be negative"; return VB200_ERR_INVALID; }
     if (c->check_finite != 0 && c->check_finite != 1) { *why = "check_finite must be 0 or 1"; return VB200_ERR_INVALID; }
+    if (c->step_kernel < 0 || c->step_kernel > 2) { *why = "step_kernel must be 0, 1 or 2"; return VB200_ERR_INVALID; }
     return VB200_OK;
 }
 
@@ -754,7 +837,7 @@ void make_plan(const vb200_config &c, ArenaPlan &pl, PlanIdx &ix, std::vector<in
     ix.s1 = pl.add("opt_state1", has1 ? P * 4 : 4, 0, end, true);
     ix.s2 = pl.add("opt_state2", has2 ? P * 4 : 4, 0, end, true);
     ix.sc = pl.add("scalars+status", 1024, 0, end, true);
-    long long mse = loss_blocks((long long)B * L[n]);
+    long long mse = std::max<long long>(loss_blocks((long long)B * L[n]), 256);   // >= one loss partial per CTA of the persistent step
     if (clip) {  // block partials of every delta's sum of squares
         long long all = 0;
         for (int i = 0; i < n; ++i) all += loss_blocks((long long)B * L[i + 1]);
@@ -889,6 +972,7 @@ int build(vb200_handle *h) {
     h->off_s2 = pl.offset(i_s2);
     h->off_flags = pl.offset(i_sc) + 768;   // 8 barrier words behind the scalars (offset 0) and the status word (512)
     h->first_bad = reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(at(i_sc)) + 832);
+    h->grid_barrier = reinterpret_cast<unsigned int *>(reinterpret_cast<char *>(at(i_sc)) + 896);
     h->check_finite = c.check_finite == 1;
     {
         // limit of the data-parallel barrier waits: the configuration, else VOLTA_B200_WAIT_MS, else 4 s
@@ -947,8 +1031,40 @@ int build(vb200_handle *h) {
         if (h->dp->all_reduce_sum(h->loss_sum, 64, h->comm_stream)) return h->fail(VB200_ERR_NCCL, h->dp->error());
         VB_CUDA(h, cudaStreamSynchronize(h->comm_stream));
     }
+    // Batches of at most 64 rows on one GPU, without the optional row stages: the whole step as one
+    // persistent kernel (vb_step_small.cu).  step_kernel: 0 = where it applies, 1 = never, 2 = required.
+    {
+        static const bool env_on = [] { const char *e = getenv("VOLTA_B200_SMALL_STEP"); return !(e && e[0] == '0'); }();
+        const bool wanted = c.step_kernel == 2 || (c.step_kernel == 0 && env_on && c.gemm_path == VB200_GEMM_AUTO);
+        const bool plain = h->world == 1 && c.force_dp != 1 && !h->row_opts && h->clip == 0.0f;
+        if (wanted && plain && n <= kSmallStepMaxLayers) {
+            int cl = 0;
+            const int grid = small_step_grid(c.optimizer, &cl);
+            if (grid > 0 && small_step_shape_ok(c.layers, c.n_sizes, 1, grid / cl)) {
+                h->ss_grid = grid;
+                h->ss_cluster = cl;
+                h->ss_forward = true;
+                if (B <= 64) {
+                    h->small_step = true;
+                    h->fuse_sgd = false;
+                }
+            }
+        }
+        if (c.step_kernel == 2 && !h->small_step)
+            return h->fail(VB200_ERR_UNSUPPORTED, "step_kernel = 2: the persistent step takes one GPU, at most 64 rows, at most 16 "
+                                                  "layers of width <= 64 x (SMs / 4), and none of softmax / LayerNorm / dropout / clip");
+    }
     if (h->use_graph) {
         int rc = capture_graphs(h);
+        if (rc && h->small_step && c.step_kernel != 2) {
+            // the device refused the cooperative cluster launch: the per-kernel schedule instead
+            cudaGetLastError();
+            h->small_step = false;
+            h->ss_forward = false;
+            h->status = VB200_OK;
+            h->error.clear();
+            rc = capture_graphs(h);
+        }
         if (rc) return rc;
     } else {
         // count the launches of one step without running it: the schedule is fixed
@@ -1026,8 +1142,9 @@ int volta_b200_set_params(vb200_handle *h, int32_t li, const float *w, const flo
     if (!w || !b) return h->reject(VB200_ERR_INVALID, "set_params: null pointer");
     const size_t wn = (size_t)h->L[li] * h->L[li + 1], bn = (size_t)h->L[li + 1];
     VB_CUDA(h, cudaStreamSynchronize(h->stream));
-    VB_CUDA(h, cudaMemcpy(h->params + h->off_w[li], w, wn * 4, cudaMemcpyHostToDevice));
-    VB_CUDA(h, cudaMemcpy(h->params + h->off_b[li], b, bn * 4, cudaMemcpyHostToDevice));
+    // w and b may be host or device pointers (unified addressing tells which)
+    VB_CUDA(h, cudaMemcpy(h->params + h->off_w[li], w, wn * 4, cudaMemcpyDefault));
+    VB_CUDA(h, cudaMemcpy(h->params + h->off_b[li], b, bn * 4, cudaMemcpyDefault));
     return VB200_OK;
 }
 
@@ -1497,10 +1614,7 @@ int32_t volta_b200_kernels_per_step(vb200_handle *h) { return h ? h->kernels_per
 int volta_b200_profile_step(vb200_handle *h, const float *X, const float *Y, float lr, vb200_kernel_record *out,
                             int32_t max) {
     if (!h) return -VB200_ERR_INVALID;
-    if (h->dp) {
-        h->fail(VB200_ERR_UNSUPPORTED, "profile_step is single-GPU only");
-        return -VB200_ERR_UNSUPPORTED;
-    }
+    if (h->dp_fused) return -h->reject(VB200_ERR_UNSUPPORTED, "profile_step: not with the fused peer-memory exchange");
     for (auto &r : h->records) { cudaEventDestroy(r.e0); cudaEventDestroy(r.e1); }
     h->records.clear();
     int rc = do_step(h, X, Y, lr, true);

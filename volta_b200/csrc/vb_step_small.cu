@@ -1,0 +1,606 @@
+// The whole training step as ONE persistent kernel, for batches of at most 64 rows.
+//
+// At batch 64 the step of the reference (src/engine/ir/codegen/mlp_train_rust_codegen.rs:699-994) is
+// a chain of small dependent products whose cost on a GPU is launch and memory latency, not
+// arithmetic: two dozen kernels of a few microseconds each.  Here one cooperative grid (one CTA per
+// SM, grouped into thread-block clusters of S CTAs) walks the same fixed schedule
+//     forward 0..n-1  ->  MSE + seed gradient  ->  backward n-1..0 (dW, db, update, dX)
+// with a grid-wide barrier between phases, so that a step is one launch.
+//
+// Work split.  Forward layer i (act[B x r] . W[r x c]): cluster j owns a slab of output columns, its S
+// CTAs split the r input features; each CTA multiplies its [B x r/S] slice by its [r/S x cols] block,
+// and the S partial results are added in rank order through distributed shared memory by the CTA
+// that owns the rows (bias, activation, and for the last layer the loss and the seed gradient are
+// applied there).  Backward layer i: cluster j owns a slab of W's ROWS, its CTAs split the columns;
+// a CTA computes its block of dW = act^T . delta (the sum over the batch is local), applies the
+// optimizer to exactly that block of W, m and v (streamed once), and computes its partial of
+// dX = delta . W^T from the same block of (pre-update) W; the partials over the column split are
+// again added in rank order through distributed shared memory, times the activation derivative.
+// Cluster 0 also sums the bias gradients.  Nothing is reduced through global memory, there are no
+// atomics on data, and every sum has a fixed order: results are bit-identical from run to run.
+//
+// Memory.  Parameters and optimizer state are cold in HBM when a step starts; every CTA first asks
+// for its share of the flat parameter, m and v regions to be prefetched into L2
+// (cp.async.bulk.prefetch.L2), so that HBM streams them once, at full speed, underneath the forward
+// phases.  Activations and deltas live in L2.  Everything another CTA wrote is read with loads that
+// bypass L1 (cp.async.cg / ld.global.cg).
+//
+// Every wait is bounded: a grid barrier that does not complete within ~2 s sets a status bit and an
+// abort word, after which no CTA waits again; the kernel then runs to its end (all cluster
+// barriers are still executed) and the host reports VB200_ERR_DEVICE_WAIT.
+//
+// With forward_only set the kernel stops after the last layer's outputs: the reference's volta_infer
+// (src/engine/ir/codegen/inner.rs:183-406) for up to 64 rows in one launch.
+#include <cooperative_groups.h>
+
+#include "vb_common.cuh"
+#include "vb_optimizer.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace vb {
+namespace {
+
+constexpr int T = 256;          // threads per CTA
+constexpr int BM = 64;          // rows of the batch at most
+constexpr int KT = 128;         // depth of one staged tile (input features forward, columns backward)
+constexpr int LD = KT + 4;      // shared-memory pitch of a [.. x KT] tile (conflict-free float4 reads)
+constexpr int WMAX = 64;        // widest slab of W one cluster owns (columns forward, rows backward)
+constexpr int LDW = WMAX + 4;   // pitch of a [.. x WMAX] tile
+constexpr int BUF_A = BM * LD;          // activation / delta tile [BM][LD]
+constexpr int BUF_B = KT * LDW;         // W tile: forward [KT][LDW]; backward [WMAX][LD] (8448 <= 8704)
+constexpr int PART = T * 16;            // every thread's 4 x 4 partial sums
+constexpr int SMEM_FLOATS = 2 * BUF_A + 2 * BUF_B + BM * LDW + PART + 64;
+constexpr unsigned ST_GRID_BARRIER = 128u;
+
+#ifdef VB_STEP_DEBUG
+// Debug builds: every CTA's thread 0 leaves (phase << 8 | stage) in a host-mapped array, so that the host can
+// see where each CTA stands while the kernel runs.
+__device__ unsigned *g_step_progress = nullptr;
+#define CRUMB(phase, stage) do { if (threadIdx.x == 0 && g_step_progress) { *reinterpret_cast<volatile unsigned *>(g_step_progress + blockIdx.x) = ((unsigned)(phase) << 8) | (unsigned)(stage); } } while (0)
+#else
+#define CRUMB(phase, stage) do {} while (0)
+#endif
+
+__device__ __forceinline__ int round4(int v) { return (v + 3) & ~3; }
+__device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+__device__ __forceinline__ void cp_async16(float *dst_smem, const float *src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst_smem);
+    const int bytes = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// dst[rows_pad x cols_pad] (pitch dst_ld) = src[rows x cols] (pitch src_ld), zero beyond rows/cols.
+// 16-byte asynchronous copies when the source allows it (the caller commits and waits), plain L2 loads
+// otherwise.  cols_pad is a multiple of 4.
+__device__ __forceinline__ void load_tile(float *dst, int dst_ld, const float *src, long long src_ld, int rows, int cols,
+                                          int rows_pad, int cols_pad) {
+    const bool vec = ((src_ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && ((cols & 3) == 0);
+    if (vec) {
+        const int cpr = cols_pad >> 2;
+        for (int idx = threadIdx.x; idx < rows_pad * cpr; idx += T) {
+            const int rr = idx / cpr, cc = (idx - rr * cpr) << 2;
+            const bool ok = rr < rows && cc < cols;
+            cp_async16(dst + rr * dst_ld + cc, ok ? src + (long long)rr * src_ld + cc : src, ok);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < rows_pad * cols_pad; idx += T) {
+            const int rr = idx / cols_pad, cc = idx - rr * cols_pad;
+            dst[rr * dst_ld + cc] = (rr < rows && cc < cols) ? __ldcg(src + (long long)rr * src_ld + cc) : 0.0f;
+        }
+    }
+}
+
+struct Barrier {
+    unsigned *count, *gen, *abort_word, *status;
+    unsigned my_gen;
+};
+
+// Grid-wide barrier: the last CTA to arrive resets the count and bumps the generation.  Bounded: after
+// ~2 s without release the CTA records the failure and nobody waits any more.
+__device__ __forceinline__ void grid_barrier(Barrier &b) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (*reinterpret_cast<volatile unsigned *>(b.abort_word) == 0u) {
+            __threadfence();
+            const unsigned arrived = atomicAdd(b.count, 1u);
+            if (arrived == gridDim.x - 1) {
+                *reinterpret_cast<volatile unsigned *>(b.count) = 0u;
+                __threadfence();
+                atomicAdd(b.gen, 1u);
+            } else {
+                unsigned long long t0 = 0;
+                for (unsigned it = 0;; ++it) {
+                    if (*reinterpret_cast<volatile unsigned *>(b.gen) != b.my_gen) break;
+                    if ((it & 1023u) == 1023u) {
+                        if (*reinterpret_cast<volatile unsigned *>(b.abort_word) != 0u) break;
+                        unsigned long long now;
+                        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                        if (t0 == 0) t0 = now;
+                        if (now - t0 > 2000000000ull) {
+                            atomicOr(b.status, ST_GRID_BARRIER);
+                            atomicExch(b.abort_word, 1u);
+                            break;
+                        }
+                    }
+                }
+            }
+            __threadfence();
+        }
+        b.my_gen += 1u;
+    }
+    __syncthreads();
+}
+
+// 4 x 4 register tile: acc[i][j] += sum_u a[i].u * w[u].j  (forward: a along k, w rows k..k+3)
+__device__ __forceinline__ void fma_nn(float (&acc)[4][4], const float4 (&a)[4], const float4 (&w)[4]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        acc[i][0] = fmaf(a[i].x, w[0].x, acc[i][0]); acc[i][1] = fmaf(a[i].x, w[0].y, acc[i][1]);
+        acc[i][2] = fmaf(a[i].x, w[0].z, acc[i][2]); acc[i][3] = fmaf(a[i].x, w[0].w, acc[i][3]);
+        acc[i][0] = fmaf(a[i].y, w[1].x, acc[i][0]); acc[i][1] = fmaf(a[i].y, w[1].y, acc[i][1]);
+        acc[i][2] = fmaf(a[i].y, w[1].z, acc[i][2]); acc[i][3] = fmaf(a[i].y, w[1].w, acc[i][3]);
+        acc[i][0] = fmaf(a[i].z, w[2].x, acc[i][0]); acc[i][1] = fmaf(a[i].z, w[2].y, acc[i][1]);
+        acc[i][2] = fmaf(a[i].z, w[2].z, acc[i][2]); acc[i][3] = fmaf(a[i].z, w[2].w, acc[i][3]);
+        acc[i][0] = fmaf(a[i].w, w[3].x, acc[i][0]); acc[i][1] = fmaf(a[i].w, w[3].y, acc[i][1]);
+        acc[i][2] = fmaf(a[i].w, w[3].z, acc[i][2]); acc[i][3] = fmaf(a[i].w, w[3].w, acc[i][3]);
+    }
+}
+// acc[i][j] += a[i] . w[j]  (both along the reduction dimension)
+__device__ __forceinline__ void fma_nt(float (&acc)[4][4], const float4 (&a)[4], const float4 (&w)[4]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            acc[i][j] = fmaf(a[i].x, w[j].x, acc[i][j]);
+            acc[i][j] = fmaf(a[i].y, w[j].y, acc[i][j]);
+            acc[i][j] = fmaf(a[i].z, w[j].z, acc[i][j]);
+            acc[i][j] = fmaf(a[i].w, w[j].w, acc[i][j]);
+        }
+}
+
+// How the 256 threads cover a [64 x 4*CG] result in 4 x 4 register tiles, KG of them sharing each tile
+// and splitting the reduction range.  Within a warp 8 row groups x 4 column groups, which keeps every
+// float4 read of the operand tiles free of bank conflicts.
+struct TileMap {
+    int CG, KG, kg, rg, cg;
+    bool active;
+};
+__device__ __forceinline__ TileMap tile_map(int width) {
+    TileMap m;
+    m.CG = ((width + 3) / 4 + 3) & ~3;       // column groups, a multiple of 4 (4..16)
+    const int t_out = 16 * m.CG;
+    m.KG = T / t_out;                        // 4, 2, 1, 1
+    m.kg = threadIdx.x / t_out;
+    m.active = m.kg < m.KG;
+    const int local = threadIdx.x - m.kg * t_out, lane = local & 31, wq = local >> 5;
+    m.rg = (lane & 7) + 8 * (wq & 1);
+    m.cg = (lane >> 3) + 4 * (wq >> 1);
+    return m;
+}
+
+template <int OPT>
+__device__ __forceinline__ void update_elem(float *p, float *s1, float *s2, float *gout, float g, const StepScalars &sc,
+                                            float wd) {
+    constexpr bool HAS1 = (OPT != VB200_OPT_SGD);
+    constexpr bool HAS2 = (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW);
+    float pv = *p, a = HAS1 ? __ldcs(s1) : 0.0f, b = HAS2 ? __ldcs(s2) : 0.0f;
+    update_one<OPT>(pv, a, b, g, sc, wd);
+    *p = pv;
+    if (HAS1) *s1 = a;
+    if (HAS2) *s2 = b;
+    *gout = g;
+}
+
+// The same for four consecutive elements (16-byte aligned).
+template <int OPT>
+__device__ __forceinline__ void update_vec4(float *p, float *s1, float *s2, float *gout, const float (&g)[4],
+                                            const StepScalars &sc, float wd) {
+    constexpr bool HAS1 = (OPT != VB200_OPT_SGD);
+    constexpr bool HAS2 = (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW);
+    float4 pv = *reinterpret_cast<const float4 *>(p);
+    float4 a = HAS1 ? __ldcs(reinterpret_cast<const float4 *>(s1)) : make_float4(0, 0, 0, 0);
+    float4 b = HAS2 ? __ldcs(reinterpret_cast<const float4 *>(s2)) : make_float4(0, 0, 0, 0);
+    update_one<OPT>(pv.x, a.x, b.x, g[0], sc, wd);
+    update_one<OPT>(pv.y, a.y, b.y, g[1], sc, wd);
+    update_one<OPT>(pv.z, a.z, b.z, g[2], sc, wd);
+    update_one<OPT>(pv.w, a.w, b.w, g[3], sc, wd);
+    *reinterpret_cast<float4 *>(p) = pv;
+    if (HAS1) *reinterpret_cast<float4 *>(s1) = a;
+    if (HAS2) *reinterpret_cast<float4 *>(s2) = b;
+    *reinterpret_cast<float4 *>(gout) = make_float4(g[0], g[1], g[2], g[3]);
+}
+
+template <int OPT>
+__global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant__ SmallStepArgs A) {
+    extern __shared__ __align__(16) float smem[];
+    float *bufA = smem;                        // [2][BUF_A]
+    float *bufB = bufA + 2 * BUF_A;            // [2][BUF_B]
+    float *actc = bufB + 2 * BUF_B;            // backward: act slice [BM][LDW]
+    float *part = actc + BM * LDW;             // [PART]
+    float *red = part + PART;                  // [64]
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int S = (int)cluster.num_blocks(), q = (int)cluster.block_rank();
+    const int NC = (int)gridDim.x / S, j = (int)blockIdx.x / S;
+    const int tid = threadIdx.x, B = A.B, n = A.n;
+    const int RB = BM / S;                     // rows whose partials this CTA adds up
+
+    Barrier bar;
+    bar.count = A.barrier;
+    bar.gen = A.barrier + 1;
+    bar.abort_word = A.barrier + 2;
+    bar.status = A.status;
+    bar.my_gen = *reinterpret_cast<volatile unsigned *>(bar.gen);   // nobody bumps it before all have arrived once
+
+    // ---- ask for this CTA's share of parameters and optimizer state to be brought into L2
+    if (tid < 3) {
+        const float *base = tid == 0 ? A.params : (tid == 1 ? A.s1 : A.s2);
+        const bool wanted = tid == 0 || (tid == 1 && OPT != VB200_OPT_SGD) || (tid == 2 && (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW));
+        if (wanted && base) {
+            const long long total = A.n_params_padded * 4LL;                       // bytes, a multiple of 256
+            const long long per = ((total + gridDim.x - 1) / gridDim.x + 255) & ~255LL;
+            long long lo = per * blockIdx.x, hi = lo + per < total ? lo + per : total;
+            for (; lo < hi; lo += 16384) {
+                const unsigned sz = (unsigned)(hi - lo < 16384 ? hi - lo : 16384);
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<const char *>(base) + lo), "r"(sz) : "memory");
+            }
+        }
+    }
+    const StepScalars sc = *A.scalars;
+    CRUMB(0, 1);
+
+    // =================================================================================== forward
+    for (int li = 0; li < n; ++li) {
+        const SmallStepLayer &L = A.L[li];
+        const int r = L.r, c = L.c;
+        const int ncl = round4(ceil_div(c, NC));                 // columns per cluster (<= WMAX, checked on the host)
+        const int n0 = j * ncl, ncols = min(ncl, c - n0);        // <= 0: nothing for this cluster
+        const int kc = round4(ceil_div(r, S));
+        const int k0 = q * kc, klen = min(kc, r - k0);           // <= 0: nothing for this rank
+        const bool last = li == n - 1;
+        float loss_acc = 0.0f;
+        if (ncols > 0) {
+            const TileMap tm = tile_map(ncl);
+            float acc[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) acc[i][u] = 0.0f;
+            const int ntiles = klen > 0 ? ceil_div(klen, KT) : 0;
+            const float *Wl = A.params + L.off_w;
+            auto issue = [&](int t) {
+                const int kb = k0 + t * KT, kn = min(KT, k0 + klen - kb);
+                load_tile(bufA + (t & 1) * BUF_A, LD, L.act_in + kb, r, B, kn, BM, KT);
+                load_tile(bufB + (t & 1) * BUF_B, LDW, Wl + (long long)kb * c + n0, c, kn, ncols, KT, 4 * tm.CG);
+                cp_async_commit();
+            };
+            if (ntiles > 0) issue(0);
+            for (int t = 0; t < ntiles; ++t) {
+                if (t + 1 < ntiles) {
+                    issue(t + 1);
+                    cp_async_wait<1>();
+                } else {
+                    cp_async_wait<0>();
+                }
+                __syncthreads();
+                if (tm.active) {
+                    const float *as = bufA + (t & 1) * BUF_A, *ws = bufB + (t & 1) * BUF_B;
+                    const int seg = KT / tm.KG, kbeg = tm.kg * seg;
+#pragma unroll 2
+                    for (int k = kbeg; k < kbeg + seg; k += 4) {
+                        float4 a[4], w[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4 *>(as + (tm.rg + 16 * i) * LD + k);
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) w[u] = *reinterpret_cast<const float4 *>(ws + (k + u) * LDW + 4 * tm.cg);
+                        fma_nn(acc, a, w);
+                    }
+                }
+                __syncthreads();
+            }
+            // partial sums of this CTA: part[kg][row][col], pitch 4*CG
+            const int PLD = 4 * tm.CG;
+            if (tm.active) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    *reinterpret_cast<float4 *>(part + ((tm.kg * BM) + tm.rg + 16 * i) * PLD + 4 * tm.cg) =
+                        make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+            }
+            CRUMB(li + 1, 2);
+            cluster.sync();
+            CRUMB(li + 1, 3);
+            // this CTA adds the S x KG partials of its rows in a fixed order and finishes the elements
+            const float *bias = A.params + L.off_b;
+            for (int e = tid; e < RB * ncols; e += T) {
+                const int row = q * RB + e / ncols, col = e % ncols;
+                if (row >= B) continue;
+                float sum = 0.0f;
+                for (int p = 0; p < S; ++p) {
+                    const float *pp = cluster.map_shared_rank(part, p);
+                    for (int g = 0; g < tm.KG; ++g) sum += pp[(g * BM + row) * PLD + col];
+                }
+                const long long o = (long long)row * c + n0 + col;
+                const float z = sum + bias[n0 + col];
+                if (!last) {
+                    if (L.pre_out) L.pre_out[o] = z;
+                    L.act_out[o] = act_forward(A.act, z);
+                } else if (A.forward_only) {
+                    L.act_out[o] = z;
+                } else {
+                    // MSE and its seed gradient (mlp_train_rust_codegen.rs:793-798)
+                    L.act_out[o] = z;
+                    const float d = __fsub_rn(z, A.y[o]);
+                    loss_acc = __fadd_rn(loss_acc, __fmul_rn(d, d));
+                    L.delta[o] = __fdiv_rn(__fmul_rn(2.0f, d), A.nt_global);
+                }
+            }
+            CRUMB(li + 1, 4);
+            cluster.sync();   // peers have finished reading this CTA's partials
+            CRUMB(li + 1, 5);
+        }
+        if (last && A.forward_only) break;   // inference: the outputs are stored, nothing follows
+        if (last) {
+            // per-CTA loss partial, fixed tree: warp shuffles, then the 8 warp sums in order
+            for (int o = 16; o; o >>= 1) loss_acc += __shfl_xor_sync(0xffffffffu, loss_acc, o);
+            if ((tid & 31) == 0) red[tid >> 5] = loss_acc;
+            __syncthreads();
+            if (tid == 0) {
+                float t = 0.0f;
+                for (int w = 0; w < T / 32; ++w) t += red[w];
+                A.loss_partials[blockIdx.x] = t;
+            }
+        }
+        CRUMB(li + 1, 6);
+        grid_barrier(bar);
+        CRUMB(li + 1, 7);
+    }
+
+    // =================================================================================== backward
+    for (int li = A.forward_only ? -1 : n - 1; li >= 0; --li) {
+        const SmallStepLayer &L = A.L[li];
+        const int r = L.r, c = L.c;
+        if (li == n - 1 && blockIdx.x == 0 && tid == 0) {
+            float t = 0.0f;
+            for (unsigned b = 0; b < gridDim.x; ++b) t += __ldcg(A.loss_partials + b);
+            *A.loss_sum = t;
+        }
+        const int kcl = round4(ceil_div(r, NC));                 // rows of W per cluster (<= WMAX)
+        const int k0 = j * kcl, krows = min(kcl, r - k0);        // <= 0: nothing for this cluster
+        const int nc = round4(ceil_div(c, S));
+        const int n0 = q * nc, nlen = min(nc, c - n0);           // <= 0: nothing for this rank
+        const bool need_dx = li > 0;
+        if (krows > 0) {
+            const TileMap tm = tile_map(kcl);                    // for the dX partial [BM x kcl]
+            float acc[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) acc[i][u] = 0.0f;
+            const int ntiles = nlen > 0 ? ceil_div(nlen, KT) : 0;
+            float *Wl = A.params + L.off_w;
+            const int wrows_pad = 4 * tm.CG;                     // rows of the W tile that dX reads (zero beyond krows)
+            auto issue = [&](int t) {
+                const int nb = n0 + t * KT, nn = min(KT, n0 + nlen - nb);
+                load_tile(bufA + (t & 1) * BUF_A, LD, L.delta + nb, c, B, nn, BM, KT);
+                load_tile(bufB + (t & 1) * BUF_B, LD, Wl + (long long)k0 * c + nb, c, krows, nn, wrows_pad, KT);
+                cp_async_commit();
+            };
+            if (ntiles > 0) {
+                load_tile(actc, LDW, L.act_in + k0, r, B, krows, BM, round4(kcl));
+                issue(0);
+            }
+            for (int t = 0; t < ntiles; ++t) {
+                if (t + 1 < ntiles) {
+                    issue(t + 1);
+                    cp_async_wait<1>();
+                } else {
+                    cp_async_wait<0>();
+                }
+                __syncthreads();
+                const float *ds = bufA + (t & 1) * BUF_A, *ws = bufB + (t & 1) * BUF_B;
+                const int nb = n0 + t * KT, nn = min(KT, n0 + nlen - nb);
+                // ---- bias gradient of this tile's columns (cluster 0 only), ascending rows, and its update
+                if (j == 0 && tid < nn) {
+                    float g = 0.0f;
+                    for (int b = 0; b < B; ++b) g += ds[b * LD + tid];
+                    const long long e = L.off_b + nb + tid;
+                    update_elem<OPT>(A.params + e, A.s1 + e, A.s2 + e, A.grads + e, g, sc, 0.0f);
+                }
+                // ---- dW block = act^T . delta (sum over the batch, ascending), then the optimizer on it
+                {
+                    const int ng = tid & 31, kgp = tid >> 5;     // 4 columns 4*ng.., 4 rows kgp*4 + 32*pass ..
+                    for (int pass = 0; pass * 32 < kcl; ++pass) {
+                        const int kk0 = kgp * 4 + 32 * pass;
+                        if (kk0 >= kcl) break;
+                        float g[4][4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) g[i][u] = 0.0f;
+#pragma unroll 4
+                        for (int b = 0; b < B; ++b) {
+                            const float4 av = *reinterpret_cast<const float4 *>(actc + b * LDW + kk0);
+                            const float4 dv = *reinterpret_cast<const float4 *>(ds + b * LD + 4 * ng);
+                            const float a4[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                g[i][0] = fmaf(a4[i], dv.x, g[i][0]);
+                                g[i][1] = fmaf(a4[i], dv.y, g[i][1]);
+                                g[i][2] = fmaf(a4[i], dv.z, g[i][2]);
+                                g[i][3] = fmaf(a4[i], dv.w, g[i][3]);
+                            }
+                        }
+                        const float wd = OPT == VB200_OPT_ADAMW ? sc.weight_decay : 0.0f;
+                        const bool vec = (c & 3) == 0 && 4 * ng + 3 < nn;   // offsets and n0, nb are multiples of 4
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int kk = kk0 + i;
+                            if (kk >= krows) continue;
+                            const long long e = L.off_w + (long long)(k0 + kk) * c + nb + 4 * ng;
+                            if (vec) {
+                                update_vec4<OPT>(A.params + e, A.s1 + e, A.s2 + e, A.grads + e, g[i], sc, wd);
+                            } else {
+#pragma unroll
+                                for (int u = 0; u < 4; ++u)
+                                    if (4 * ng + u < nn)
+                                        update_elem<OPT>(A.params + e + u, A.s1 + e + u, A.s2 + e + u, A.grads + e + u, g[i][u], sc, wd);
+                            }
+                        }
+                    }
+                }
+                // ---- partial of dX = delta . W^T over this tile's columns, from the pre-update W in shared memory
+                if (need_dx && tm.active) {
+                    const int seg = KT / tm.KG, nbeg = tm.kg * seg;
+#pragma unroll 2
+                    for (int nn4 = nbeg; nn4 < nbeg + seg; nn4 += 4) {
+                        float4 d[4], w[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) d[i] = *reinterpret_cast<const float4 *>(ds + (tm.rg + 16 * i) * LD + nn4);
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) w[u] = *reinterpret_cast<const float4 *>(ws + (tm.cg + tm.CG * u) * LD + nn4);
+                        fma_nt(acc, d, w);
+                    }
+                }
+                __syncthreads();
+            }
+            if (need_dx) {
+                // partials: part[kg][row][kk], kk = cg + CG*u, pitch 4*CG
+                const int PLD = 4 * tm.CG;
+                if (tm.active) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) part[((tm.kg * BM) + tm.rg + 16 * i) * PLD + tm.cg + tm.CG * u] = acc[i][u];
+                }
+                CRUMB(64 + li, 2);
+                cluster.sync();
+                CRUMB(64 + li, 3);
+                for (int e = tid; e < RB * krows; e += T) {
+                    const int row = q * RB + e / krows, kk = e % krows;
+                    if (row >= B) continue;
+                    float sum = 0.0f;
+                    for (int p = 0; p < S; ++p) {
+                        const float *pp = cluster.map_shared_rank(part, p);
+                        for (int g = 0; g < tm.KG; ++g) sum += pp[(g * BM + row) * PLD + kk];
+                    }
+                    const long long o = (long long)row * r + k0 + kk;
+                    L.delta_prev[o] = sum * act_backward(A.act, __ldcg(L.saved_prev + o));
+                }
+                cluster.sync();
+            }
+        }
+        CRUMB(64 + li, 6);
+        if (li > 0) grid_barrier(bar);
+        CRUMB(64 + li, 7);
+    }
+    CRUMB(255, 1);
+    cluster.sync();   // no CTA leaves while a peer may still read its shared memory
+    CRUMB(255, 2);
+}
+
+bool g_smem_set[kMaxDevices][5] = {};
+
+template <int OPT>
+cudaError_t launch_opt(const SmallStepArgs &args, int grid, int S, cudaStream_t s) {
+    const int dev = current_device();
+    const size_t smem = SMEM_FLOATS * sizeof(float);
+    if (!g_smem_set[dev][OPT]) {
+        cudaError_t e = cudaFuncSetAttribute(small_step_kernel<OPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        g_smem_set[dev][OPT] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(T);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = (unsigned)S;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeCooperative;   // all CTAs resident at once: they wait on one another
+    at[1].val.cooperative = 1;
+    cfg.attrs = at;
+    // VOLTA_B200_STEP_COOP=0 drops the cooperative attribute (the grid is sized to be resident either way)
+    static const bool coop = [] { const char *e = getenv("VOLTA_B200_STEP_COOP"); return !(e && e[0] == '0'); }();
+    cfg.numAttrs = coop ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, small_step_kernel<OPT>, args);
+}
+
+template <int OPT>
+int max_clusters(int S) {
+    const size_t smem = SMEM_FLOATS * sizeof(float);
+    if (cudaFuncSetAttribute(small_step_kernel<OPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)S);
+    cfg.blockDim = dim3(T);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = (unsigned)S;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, small_step_kernel<OPT>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+}  // namespace
+
+#ifdef VB_STEP_DEBUG
+extern "C" void vb_step_debug_set(unsigned *host_mapped) { cudaMemcpyToSymbol(g_step_progress, &host_mapped, sizeof host_mapped); }
+#endif
+
+// Shape limits of the persistent step (a function of the topology and of the cluster count alone).
+bool small_step_shape_ok(const int *layers, int n_sizes, int batch, int clusters) {
+    if (batch < 1 || batch > BM || n_sizes < 2 || n_sizes - 1 > kSmallStepMaxLayers || clusters < 1) return false;
+    for (int i = 0; i < n_sizes; ++i)
+        if (((layers[i] + clusters - 1) / clusters + 3) / 4 * 4 > WMAX) return false;
+    return true;
+}
+
+// Grid of the persistent step on the current device: `*cluster` CTAs per cluster (4 unless
+// VOLTA_B200_STEP_CLUSTER says 1, 2 or 8) times as many clusters as are resident at once, at most one
+// CTA per SM.  Returns 0 when the device cannot hold it.
+int small_step_grid(int optimizer, int *cluster) {
+    static const int want = [] { const char *e = getenv("VOLTA_B200_STEP_CLUSTER"); int v = e ? atoi(e) : 4; return (v == 1 || v == 2 || v == 4 || v == 8) ? v : 4; }();
+    int n = 0;
+    switch (optimizer) {
+    case VB200_OPT_SGD: n = max_clusters<VB200_OPT_SGD>(want); break;
+    case VB200_OPT_ADAM: n = max_clusters<VB200_OPT_ADAM>(want); break;
+    case VB200_OPT_ADAMW: n = max_clusters<VB200_OPT_ADAMW>(want); break;
+    case VB200_OPT_ADAGRAD: n = max_clusters<VB200_OPT_ADAGRAD>(want); break;
+    case VB200_OPT_SGD_MOMENTUM: n = max_clusters<VB200_OPT_SGD_MOMENTUM>(want); break;
+    }
+    const int by_sm = device_sm_count() / want;
+    if (n > by_sm) n = by_sm;
+    *cluster = want;
+    return n > 0 ? n * want : 0;
+}
+
+cudaError_t launch_small_step(const SmallStepArgs &args, int grid, int cluster, cudaStream_t s) {
+    switch (args.opt) {
+    case VB200_OPT_SGD: return launch_opt<VB200_OPT_SGD>(args, grid, cluster, s);
+    case VB200_OPT_ADAM: return launch_opt<VB200_OPT_ADAM>(args, grid, cluster, s);
+    case VB200_OPT_ADAMW: return launch_opt<VB200_OPT_ADAMW>(args, grid, cluster, s);
+    case VB200_OPT_ADAGRAD: return launch_opt<VB200_OPT_ADAGRAD>(args, grid, cluster, s);
+    case VB200_OPT_SGD_MOMENTUM: return launch_opt<VB200_OPT_SGD_MOMENTUM>(args, grid, cluster, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace vb

@@ -65,3 +65,47 @@ def kaiming_uniform_weights(layers, seed: int = 42):
         bs.append(np.zeros(c, dtype=np.float32))
         start += r * c
     return ws, bs
+
+
+# ---------------------------------------------------------------------------------------------
+# The same kind of tensors generated ON the GPU, for configurations whose inputs and weights are
+# too large to draw with numpy in reasonable time (configuration 5: 2.1 GB of inputs, 1.6 GB of
+# weights).  Blocks of 4096 rows (of 2^22 elements for weights) are seeded by (seed, block index), so
+# any rank generates exactly its rows of the same global tensor; values differ from the numpy
+# generator above (another bit source), distributions and shapes are the same.
+# ---------------------------------------------------------------------------------------------
+_DEV_BLOCK_ROWS = 4096
+
+
+def rows_cuda(dist: str, seed: int, row0: int, nrows: int, width: int, device=None):
+    """Rows [row0, row0+nrows) of a global [*, width] tensor as a CUDA tensor; row0 and nrows must be
+    multiples of 4096 or lie inside one block."""
+    import torch
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    out = torch.empty((nrows, width), dtype=torch.float32, device=device)
+    gen = torch.Generator(device=device)
+    r = row0
+    while r < row0 + nrows:
+        blk = r // _DEV_BLOCK_ROWS
+        lo, hi = blk * _DEV_BLOCK_ROWS, (blk + 1) * _DEV_BLOCK_ROWS
+        gen.manual_seed((seed << 20) + blk)
+        full = torch.empty((_DEV_BLOCK_ROWS, width), dtype=torch.float32, device=device)
+        full.normal_(generator=gen) if dist == "normal" else full.uniform_(-1.0, 1.0, generator=gen)
+        a, b = r, min(hi, row0 + nrows)
+        out[a - row0:b - row0] = full[a - lo:b - lo]
+        r = b
+    return out
+
+
+def kaiming_uniform_weights_cuda(layers, seed: int = 42, device=None):
+    """U(-sqrt(6/fan_in), +sqrt(6/fan_in)) per layer as CUDA tensors, one generator seed per layer; biases zero."""
+    import torch
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=device)
+    ws, bs = [], []
+    for i, (r, c) in enumerate(zip(layers[:-1], layers[1:])):
+        lim = float(np.sqrt(6.0 / r))
+        gen.manual_seed((seed << 20) + i)
+        ws.append(torch.empty((r, c), dtype=torch.float32, device=device).uniform_(-lim, lim, generator=gen))
+        bs.append(torch.zeros(c, dtype=torch.float32, device=device))
+    return ws, bs

@@ -54,7 +54,7 @@ class TrainHandle:
     def __init__(self, layers, activation="relu", optimizer="sgd", batch=1, *, global_batch=0, world_size=1, rank=0,
                  unique_id: bytes | None = None, momentum=0.0, weight_decay=0.0, gemm_path="auto", use_graph=True,
                  force_dp=False, fuse_sgd=False, dropout_p=0.0, use_layernorm=False, clip_grad=0.0, device_wait_ms=0,
-                 check_finite=False):
+                 check_finite=False, step_kernel=0):
         act = activation.lower()
         opt = optimizer.lower()
         if act not in ACTIVATIONS:
@@ -94,6 +94,7 @@ class TrainHandle:
         cfg.clip_grad = float(clip_grad)
         cfg.device_wait_ms = int(device_wait_ms)
         cfg.check_finite = 1 if check_finite else 0
+        cfg.step_kernel = int(step_kernel)   # 0 auto, 1 per-kernel schedule, 2 require the persistent step kernel
         self.dropout_p = float(dropout_p)
         self._cfg = cfg
         h = C.c_void_p()
@@ -115,7 +116,14 @@ class TrainHandle:
         return v
 
     def set_params(self, li: int, w, b):
-        """volta_train_set_params(h, li, w, b); li out of range is ignored."""
+        """volta_train_set_params(h, li, w, b); li out of range is ignored.  w and b: numpy arrays, or CUDA
+        tensors (copied device to device)."""
+        if hasattr(w, "data_ptr") and hasattr(b, "data_ptr"):
+            if 0 <= li < self.n and (w.numel() != self.layers[li] * self.layers[li + 1] or b.numel() != self.layers[li + 1]):
+                raise ValueError("set_params: wrong tensor size for layer %d" % li)
+            fp = C.POINTER(C.c_float)
+            self._check(self.lib.volta_b200_set_params(self.h, int(li), C.cast(_ptr(w), fp), C.cast(_ptr(b), fp)))
+            return
         w = np.ascontiguousarray(w, dtype=np.float32).reshape(-1)
         b = np.ascontiguousarray(b, dtype=np.float32).reshape(-1)
         if 0 <= li < self.n:
