@@ -68,8 +68,12 @@ def test_shapes_against_the_oracle_and_the_per_kernel_schedule(layers, B, act, o
     for step in range(3):
         for h in (g, k, o):
             h.step(x, y, lr)
-        assert abs(g.loss() - o.loss()) <= 1e-5 * abs(o.loss()), step
-        assert abs(g.loss() - k.loss()) <= 1e-5 * abs(k.loss()), step
+        # the first step from identical state is held to the one-step bars; later steps of an Adam run
+        # amplify any admissible difference (sign-like updates near zero gradients), so they get the
+        # bar stated for whole runs
+        tol = 1e-5 if step == 0 else LOSS_TOL
+        assert abs(g.loss() - o.loss()) <= tol * abs(o.loss()), step
+        assert abs(g.loss() - k.loss()) <= tol * abs(k.loss()), step
         if step == 0:
             assert_one_step_parity(g, o, opt, lr, before)
     g.free()

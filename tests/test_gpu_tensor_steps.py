@@ -135,8 +135,9 @@ def compare_step(g, ref_grads, ref_params, ref_loss, scales, opt, lr, s1, s2, t,
 
     robust = True is for relu networks so large that thousands of units are fragile (the derivative is
     discontinuous: per-element bars are then ill-posed in any fp32 arithmetic, the reference's included): the
-    gradients are compared in the root-mean-square sense instead (rms error over rms gradient, per tensor), the loss
-    as always, and the per-element weight bars are not applied."""
+    gradients are held only to 1e-2 (of their scale at the worst element, and in the root-mean-square sense of the
+    rms gradient per tensor: a flipped unit changes one whole gradient column), the loss as always, and the
+    per-element weight bars are not applied.  The same network with a smooth activation is held to every bar."""
     n = len(ref_grads) // 2
     frag_cols, frag_count = fragile if fragile is not None else ([np.zeros(0, np.int64)] * (n - 1), 0)
     g_tol = G_TOL["auto"] * (1.0 + 3.0 * frag_count)
@@ -178,7 +179,8 @@ def compare_step(g, ref_grads, ref_params, ref_loss, scales, opt, lr, s1, s2, t,
                   weights=total, fragile_units=frag_count, robust=robust, **info)
     assert loss_err <= LOSS_TOL, "%s: loss" % label
     if robust:
-        assert g_rms <= 1e-4, "%s: gradients, rms (%g of the rms gradient)" % (label, g_rms)
+        assert g_rms <= 1e-2, "%s: gradients, rms (%g of the rms gradient)" % (label, g_rms)
+        assert g_err <= 1e-2, "%s: gradients (%g of their scale)" % (label, g_err)
         return g_err, w_err, loss_err
     assert g_err <= g_tol, "%s: gradients (%g of their scale, bar %g)" % (label, g_err, g_tol)
     assert w_ok, "%s: weights after one step" % label
@@ -286,7 +288,9 @@ def run_config_against_fp64(cfg, B, steps, parity_report, path="auto", also_orac
     configuration's step count is 1e-3.  Adam-type trajectories amplify any admissible difference (their update is
     sign-like where a gradient is near zero), so that bar is applied modulo the trajectory's own sensitivity: a
     twin fp64 run whose weights are moved after the first step by the amount the one-step bar allows (1e-5 of each
-    tensor's largest weight, random signs) shows how far the final loss moves for an error of admissible size."""
+    tensor's largest weight, random signs) shows how far the final loss moves for an error of admissible size; the
+    reference's own fp32 arithmetic (the oracle on its gemm_shim.c) shows the same kind of drift.  With the oracle
+    at hand the last state is also teacher-forced: one step from the oracle's exact state at the one-step bars."""
     layers = list(cfg.layers)
     ws, bs = synth.kaiming_uniform_weights(layers, 42)
     x = synth.rows(cfg.x_dist, 1234, 0, B, layers[0])
@@ -326,8 +330,20 @@ def run_config_against_fp64(cfg, B, steps, parity_report, path="auto", also_orac
     parity_report("config_run", gpu_loss=lg, fp64_loss=l64, oracle_f32_loss=lo, loss_rel_err_vs_fp64=abs(lg - l64) / abs(l64),
                   oracle_f32_vs_fp64=(abs(lo - l64) / abs(l64) if lo is not None else None),
                   sensitivity_to_admissible_one_step_error=sens / abs(l64), **info)
-    allowed = max(LOSS_TOL * abs(l64), sens)
+    # a chaotic quantity: the allowance is three times the larger of the two drifts seen from admissible causes
+    # (the twin's, and that of the reference's own fp32 arithmetic where it was run)
+    drift = max(sens, abs(lo - l64) if lo is not None else 0.0)
+    allowed = max(LOSS_TOL * abs(l64), 3.0 * drift)
     assert abs(lg - l64) <= allowed, "loss after %d steps: gpu %g, fp64 %g, oracle fp32 %s, allowed %g" % (steps, lg, l64, lo, allowed)
+    if o is not None:
+        # and pinned along the real trajectory: the handle takes ONE more step from the fp32 oracle's exact
+        # parameters and optimizer state, which must agree with the oracle's next step at the one-step bars
+        from tests.test_gpu_parity import assert_one_step_parity, sync_gpu_to_oracle
+        sync_gpu_to_oracle(g, o)
+        before = o.state()
+        g.step(x, y, cfg.lr)
+        o.step(x, y, cfg.lr)
+        assert_one_step_parity(g, o, cfg.optimizer, cfg.lr, before)
     g.free()
     return routes
 

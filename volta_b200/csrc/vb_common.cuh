@@ -322,9 +322,11 @@ struct SmallStepArgs {
     const float *y;            // [B x L_n]
     float *loss_sum, *loss_partials;   // one float; one float per CTA
     float nt_global;
-    const StepScalars *scalars;
-    unsigned int *barrier;     // {arrivals, generation, abort}
+    StepScalars scalars;       // this step's learning rate and optimizer constants, by value
+    unsigned int *barrier;     // {arrival word, -, abort}
     unsigned int *status;
+    float *host_loss;          // pinned host memory the kernel stores the loss sum and the status word to
+    unsigned int *host_status; //   at its end (either may be null)
     SmallStepLayer L[kSmallStepMaxLayers];
 };
 bool small_step_shape_ok(const int *layers, int n_sizes, int batch, int clusters);

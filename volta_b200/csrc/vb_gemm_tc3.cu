@@ -22,8 +22,9 @@ namespace {
 
 constexpr int BM = 128, BN = 256, BK = 32;  // per CTA: 128 rows x 256 columns; the pair covers 256 x 256
 constexpr int RAW_STAGES = 4;   // raw tiles stay from the TMA load until the MMAs that read them retire
-// Low parts stay only from the split to the same MMAs: 2 slots by default, 3 (all 227 KB of shared memory) with
-// VOLTA_B200_TC_LO=3, which lets the split warps run one k-block further ahead of the tensor pipe.
+// Low parts stay only from the split to the same MMAs: 3 slots (with the 4 raw slots all 227 KB of shared
+// memory), so that the split warps run up to two k-blocks ahead of the tensor pipe; measured 3 % faster on
+// the large GEMMs than 2 slots (VOLTA_B200_TC_LO=2 selects those).
 constexpr int SPLIT_WARPS = 16, SPLIT_THREADS = SPLIT_WARPS * 32;
 constexpr int TMA_WARP = SPLIT_WARPS, MMA_WARP = SPLIT_WARPS + 1;
 constexpr int THREADS = (SPLIT_WARPS + 2) * 32;
@@ -473,7 +474,7 @@ cudaError_t launch3lo(const CUtensorMap &ma, const CUtensorMap &mb, long long m,
 template <bool AK, bool BKM>
 cudaError_t launch3(const CUtensorMap &ma, const CUtensorMap &mb, long long m, long long n, long long k, int tiles_m,
                     int tiles_n, const Epilogue &epi, unsigned int *status, cudaStream_t s, int splits) {
-    static const int lo = [] { const char *e = getenv("VOLTA_B200_TC_LO"); return (e && atoi(e) == 3) ? 3 : 2; }();
+    static const int lo = [] { const char *e = getenv("VOLTA_B200_TC_LO"); return (e && atoi(e) == 2) ? 2 : 3; }();
     if (lo == 3) return launch3lo<AK, BKM, 3>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s, splits);
     return launch3lo<AK, BKM, 2>(ma, mb, m, n, k, tiles_m, tiles_n, epi, status, s, splits);
 }

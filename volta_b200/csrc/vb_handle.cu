@@ -108,6 +108,8 @@ struct vb200_handle {
     // the whole step as one persistent kernel (batches of at most 64 rows on one GPU; vb_step_small.cu)
     bool small_step = false;
     bool ss_forward = false;   // the same kernel, forward only, serves inference of 9..64 rows
+    StepScalars ss_scalars{};  // this step's scalars, handed to the persistent kernel by value
+    const float *ss_x = nullptr, *ss_y = nullptr;   // device-resident inputs of this step, used where they lie
     int ss_grid = 0, ss_cluster = 0;
     unsigned int *grid_barrier = nullptr;   // {arrivals, generation, abort} in the arena
     int kernels_per_step = 0;
@@ -299,6 +301,7 @@ int enqueue_step_tail(vb200_handle *h, int slot) {
                                        h->n_params_padded, h->n_params_padded + (h->dp_fused ? 2 : 1), h->first_bad, s));
         VB_CUDA(h, cudaMemcpyAsync(h->host_first_bad, h->first_bad, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s));
     }
+    if (h->small_step) return VB200_OK;   // the persistent kernel stores loss and status into pinned memory itself
     VB_CUDA(h, cudaMemcpyAsync(&h->host_loss[slot], h->dp_fused ? h->loss_sum + 1 : h->loss_sum, sizeof(float),
                                cudaMemcpyDeviceToHost, s));
     VB_CUDA(h, cudaMemcpyAsync(h->host_status, h->status_word, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
@@ -322,13 +325,15 @@ int enqueue_small_step(vb200_handle *h, int slot, int rows) {
     a.s1 = h->s1;
     a.s2 = h->s2;
     a.n_params_padded = h->n_params_padded;
-    a.y = h->yin[slot];
+    a.y = h->ss_y ? h->ss_y : h->yin[slot];
     a.loss_sum = h->loss_sum;
     a.loss_partials = h->mse_scratch;
     a.nt_global = (float)h->global_nt;
-    a.scalars = h->scalars;
+    a.scalars = h->ss_scalars;
     a.barrier = h->grid_barrier;
     a.status = h->status_word;
+    a.host_loss = rows > 0 ? nullptr : &h->host_loss[slot];
+    a.host_status = rows > 0 ? nullptr : h->host_status;
     double flops = 0.0;
     for (int i = 0; i < n; ++i) {
         SmallStepLayer &l = a.L[i];
@@ -336,7 +341,7 @@ int enqueue_small_step(vb200_handle *h, int slot, int rows) {
         l.c = L[i + 1];
         l.off_w = h->off_w[i];
         l.off_b = h->off_b[i];
-        l.act_in = i == 0 ? h->xin[slot] : h->act[i];
+        l.act_in = i == 0 ? (h->ss_x && rows == 0 ? h->ss_x : h->xin[slot]) : h->act[i];
         l.act_out = h->act[i + 1];
         l.pre_out = (i < n - 1 && h->keep_pre) ? h->pre[i] : nullptr;
         l.delta = h->delta[i];
@@ -642,15 +647,23 @@ int copy_inputs(vb200_handle *h, int slot, const float *X, const float *Y, bool 
     }
     const bool xdev = ax.type == cudaMemoryTypeDevice || ax.type == cudaMemoryTypeManaged;
     const bool ydev = ay.type == cudaMemoryTypeDevice || ay.type == cudaMemoryTypeManaged;
+    // The persistent step kernel takes its input pointers as arguments of each launch: inputs that already
+    // live on the device are read where they lie (they must stay unchanged until the step has run), only
+    // host inputs go through the slot.
+    h->ss_x = (h->small_step && xdev) ? X : nullptr;
+    h->ss_y = (h->small_step && ydev) ? Y : nullptr;
+    *host_wait = !(xdev && ydev);
+    if (h->ss_x && h->ss_y) return VB200_OK;
     // the slot is free once the step that last read it has finished
     VB_CUDA(h, cudaStreamWaitEvent(h->copy_stream, h->ev_slot_free[slot], 0));
-    VB_CUDA(h, cudaMemcpyAsync(h->xin[slot], X, xb, xdev ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice,
-                               h->copy_stream));
-    VB_CUDA(h, cudaMemcpyAsync(h->yin[slot], Y, yb, ydev ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice,
-                               h->copy_stream));
+    if (!h->ss_x)
+        VB_CUDA(h, cudaMemcpyAsync(h->xin[slot], X, xb, xdev ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice,
+                                   h->copy_stream));
+    if (!h->ss_y)
+        VB_CUDA(h, cudaMemcpyAsync(h->yin[slot], Y, yb, ydev ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice,
+                                   h->copy_stream));
     VB_CUDA(h, cudaEventRecord(h->ev_copied[slot], h->copy_stream));
     VB_CUDA(h, cudaStreamWaitEvent(h->stream, h->ev_copied[slot], 0));
-    *host_wait = !(xdev && ydev);
     return VB200_OK;
 }
 
@@ -712,8 +725,12 @@ int do_step(vb200_handle *h, const float *X, const float *Y, float lr, bool prof
     if (rc) return rc;
     const int opt = h->cfg.optimizer;
     if (opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW) h->adam_step += 1;
-    VB_CUDA(h, launch_set_scalars(h->scalars, make_scalars(h, lr), h->stream));
-    if (profile || !h->use_graph) {
+    if (h->small_step) {
+        h->ss_scalars = make_scalars(h, lr);   // a kernel argument: no helper launch, no graph
+    } else {
+        VB_CUDA(h, launch_set_scalars(h->scalars, make_scalars(h, lr), h->stream));
+    }
+    if (profile || !h->use_graph || h->small_step) {
         h->profiling = profile;
         rc = enqueue_step(h, slot);
         h->profiling = false;
@@ -721,7 +738,7 @@ int do_step(vb200_handle *h, const float *X, const float *Y, float lr, bool prof
     } else {
         VB_CUDA(h, cudaGraphLaunch(h->graph[slot], h->stream));
     }
-    VB_CUDA(h, cudaEventRecord(h->ev_slot_free[slot], h->stream));
+    if (!(h->ss_x && h->ss_y)) VB_CUDA(h, cudaEventRecord(h->ev_slot_free[slot], h->stream));
     h->last_slot = slot;
     h->steps_done += 1;
     if (h->draws_per_step) h->dropout_rng = lcg_jump(h->dropout_rng, h->draws_per_step);
@@ -1044,7 +1061,10 @@ int build(vb200_handle *h) {
                 h->ss_grid = grid;
                 h->ss_cluster = cl;
                 h->ss_forward = true;
-                if (B <= 64) {
+                // where it applies by default: up to 4 M parameters.  Beyond that the per-kernel schedule's
+                // streaming optimizer (64 warps per SM against this kernel's 8) makes up for its launches
+                // (measured on the 6.3 M-parameter configuration: both take 0.22 ms per step).
+                if (B <= 64 && (c.step_kernel == 2 || h->n_params_padded <= (4LL << 20))) {
                     h->small_step = true;
                     h->fuse_sgd = false;
                 }
@@ -1054,17 +1074,24 @@ int build(vb200_handle *h) {
             return h->fail(VB200_ERR_UNSUPPORTED, "step_kernel = 2: the persistent step takes one GPU, at most 64 rows, at most 16 "
                                                   "layers of width <= 64 x (SMs / 4), and none of softmax / LayerNorm / dropout / clip");
     }
-    if (h->use_graph) {
-        int rc = capture_graphs(h);
-        if (rc && h->small_step && c.step_kernel != 2) {
-            // the device refused the cooperative cluster launch: the per-kernel schedule instead
+    if (h->ss_forward) {
+        // one forward-only launch on a single row of the (zeroed) input slot shows whether the device takes the
+        // cooperative cluster launch; if not, the per-kernel schedule serves instead
+        int rc = enqueue_small_step(h, 0, 1);
+        cudaError_t e = rc ? cudaErrorUnknown : cudaStreamSynchronize(h->stream);
+        if (rc || e != cudaSuccess) {
             cudaGetLastError();
+            if (c.step_kernel == 2) return h->fail(VB200_ERR_CUDA, "step_kernel = 2: the device refused the persistent kernel's launch: " + h->error);
             h->small_step = false;
             h->ss_forward = false;
             h->status = VB200_OK;
             h->error.clear();
-            rc = capture_graphs(h);
         }
+    }
+    if (h->small_step) {
+        h->kernels_per_step = 1;   // launched directly every step, with the step's scalars as an argument
+    } else if (h->use_graph) {
+        int rc = capture_graphs(h);
         if (rc) return rc;
     } else {
         // count the launches of one step without running it: the schedule is fixed

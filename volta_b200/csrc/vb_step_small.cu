@@ -19,6 +19,10 @@
 // Cluster 0 also sums the bias gradients.  Nothing is reduced through global memory, there are no
 // atomics on data, and every sum has a fixed order: results are bit-identical from run to run.
 //
+// One launch, nothing else: the step's scalars travel as a kernel argument, inputs that already live on
+// the device are read where they lie, and CTA 0 stores the loss sum and the status word straight into
+// pinned host memory, so that no copy or helper kernel surrounds the step.
+//
 // Memory.  Parameters and optimizer state are cold in HBM when a step starts; every CTA first asks
 // for its share of the flat parameter, m and v regions to be prefetched into L2
 // (cp.async.bulk.prefetch.L2), so that HBM streams them once, at full speed, underneath the forward
@@ -53,14 +57,6 @@ constexpr int PART = T * 16;            // every thread's 4 x 4 partial sums
 constexpr int SMEM_FLOATS = 2 * BUF_A + 2 * BUF_B + BM * LDW + PART + 64;
 constexpr unsigned ST_GRID_BARRIER = 128u;
 
-#ifdef VB_STEP_DEBUG
-// Debug builds: every CTA's thread 0 leaves (phase << 8 | stage) in a host-mapped array, so that the host can
-// see where each CTA stands while the kernel runs.
-__device__ unsigned *g_step_progress = nullptr;
-#define CRUMB(phase, stage) do { if (threadIdx.x == 0 && g_step_progress) { *reinterpret_cast<volatile unsigned *>(g_step_progress + blockIdx.x) = ((unsigned)(phase) << 8) | (unsigned)(stage); } } while (0)
-#else
-#define CRUMB(phase, stage) do {} while (0)
-#endif
 
 __device__ __forceinline__ int round4(int v) { return (v + 3) & ~3; }
 __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
@@ -69,6 +65,13 @@ __device__ __forceinline__ void cp_async16(float *dst_smem, const float *src, bo
     const unsigned d = (unsigned)__cvta_generic_to_shared(dst_smem);
     const int bytes = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+// A streaming 16-byte load that stays where it is written: the compiler neither sinks it towards its first
+// use nor merges it with others, so a load placed ahead of a long computation really is in flight during it.
+__device__ __forceinline__ float4 load_early(const float *p) {
+    float4 v;
+    asm volatile("ld.global.cs.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -88,50 +91,56 @@ __device__ __forceinline__ void load_tile(float *dst, int dst_ld, const float *s
             cp_async16(dst + rr * dst_ld + cc, ok ? src + (long long)rr * src_ld + cc : src, ok);
         }
     } else {
-        for (int idx = threadIdx.x; idx < rows_pad * cols_pad; idx += T) {
-            const int rr = idx / cols_pad, cc = idx - rr * cols_pad;
-            dst[rr * dst_ld + cc] = (rr < rows && cc < cols) ? __ldcg(src + (long long)rr * src_ld + cc) : 0.0f;
+        // groups of four destination floats, each element loaded on its own where it exists; rows run fastest
+        // over the threads, so that the few groups of a one-column operand that hold data go to different threads
+        const int cpr = cols_pad >> 2;
+        for (int idx = threadIdx.x; idx < rows_pad * cpr; idx += T) {
+            const int gg = idx / rows_pad, rr = idx - gg * rows_pad, cc = gg << 2;
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (rr < rows && cc < cols) {
+                const float *p = src + (long long)rr * src_ld + cc;
+                v.x = __ldcg(p);
+                if (cc + 1 < cols) v.y = __ldcg(p + 1);
+                if (cc + 2 < cols) v.z = __ldcg(p + 2);
+                if (cc + 3 < cols) v.w = __ldcg(p + 3);
+            }
+            *reinterpret_cast<float4 *>(dst + rr * dst_ld + cc) = v;
         }
     }
 }
 
 struct Barrier {
-    unsigned *count, *gen, *abort_word, *status;
-    unsigned my_gen;
+    unsigned *count, *abort_word, *status;
 };
 
-// Grid-wide barrier: the last CTA to arrive resets the count and bumps the generation.  Bounded: after
-// ~2 s without release the CTA records the failure and nobody waits any more.
+// Grid-wide barrier on ONE word: CTA 0 adds 2^31 - (G - 1), every other CTA adds 1, so the word's top bit
+// flips exactly when all G have arrived (and its low bits are back where they were: no reset, no second
+// word).  One atomic per CTA, then a spin on the same word.  Bounded: after ~2 s without release the CTA
+// records the failure and nobody waits any more.
 __device__ __forceinline__ void grid_barrier(Barrier &b) {
     __syncthreads();
     if (threadIdx.x == 0) {
         if (*reinterpret_cast<volatile unsigned *>(b.abort_word) == 0u) {
             __threadfence();
-            const unsigned arrived = atomicAdd(b.count, 1u);
-            if (arrived == gridDim.x - 1) {
-                *reinterpret_cast<volatile unsigned *>(b.count) = 0u;
-                __threadfence();
-                atomicAdd(b.gen, 1u);
-            } else {
-                unsigned long long t0 = 0;
-                for (unsigned it = 0;; ++it) {
-                    if (*reinterpret_cast<volatile unsigned *>(b.gen) != b.my_gen) break;
-                    if ((it & 1023u) == 1023u) {
-                        if (*reinterpret_cast<volatile unsigned *>(b.abort_word) != 0u) break;
-                        unsigned long long now;
-                        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-                        if (t0 == 0) t0 = now;
-                        if (now - t0 > 2000000000ull) {
-                            atomicOr(b.status, ST_GRID_BARRIER);
-                            atomicExch(b.abort_word, 1u);
-                            break;
-                        }
+            const unsigned inc = blockIdx.x == 0 ? 0x80000000u - (gridDim.x - 1u) : 1u;
+            const unsigned old = atomicAdd(b.count, inc);
+            unsigned long long t0 = 0;
+            for (unsigned it = 0;; ++it) {
+                if (((old ^ *reinterpret_cast<volatile unsigned *>(b.count)) & 0x80000000u) != 0u) break;
+                if ((it & 1023u) == 1023u) {
+                    if (*reinterpret_cast<volatile unsigned *>(b.abort_word) != 0u) break;
+                    unsigned long long now;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                    if (t0 == 0) t0 = now;
+                    if (now - t0 > 2000000000ull) {
+                        atomicOr(b.status, ST_GRID_BARRIER);
+                        atomicExch(b.abort_word, 1u);
+                        break;
                     }
                 }
             }
             __threadfence();
         }
-        b.my_gen += 1u;
     }
     __syncthreads();
 }
@@ -183,6 +192,34 @@ __device__ __forceinline__ TileMap tile_map(int width) {
     return m;
 }
 
+// The KG partial tiles of this CTA, part[kg][row][col], summed in k-group order into the first one.
+__device__ __forceinline__ void fold_kgroups(float *part, int KG, int PLD) {
+    __syncthreads();
+    if (KG > 1) {
+        const int n4 = (BM * PLD) >> 2;
+        for (int e = threadIdx.x; e < n4; e += T) {
+            float4 v = reinterpret_cast<const float4 *>(part)[e];
+            for (int g = 1; g < KG; ++g) {
+                const float4 w = reinterpret_cast<const float4 *>(part + g * BM * PLD)[e];
+                v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+            }
+            reinterpret_cast<float4 *>(part)[e] = v;
+        }
+    }
+}
+// Element `idx` of every rank's folded tile, added in rank order.  All remote loads are issued before
+// the first addition, so their latencies overlap.
+__device__ __forceinline__ float gather_ranks(cg::cluster_group &cluster, float *part, int S, int idx) {
+    float v[8];
+#pragma unroll
+    for (int p = 0; p < 8; ++p) v[p] = p < S ? cluster.map_shared_rank(part, p)[idx] : 0.0f;
+    float sum = v[0];
+#pragma unroll
+    for (int p = 1; p < 8; ++p)
+        if (p < S) sum += v[p];
+    return sum;
+}
+
 template <int OPT>
 __device__ __forceinline__ void update_elem(float *p, float *s1, float *s2, float *gout, float g, const StepScalars &sc,
                                             float wd) {
@@ -194,25 +231,6 @@ __device__ __forceinline__ void update_elem(float *p, float *s1, float *s2, floa
     if (HAS1) *s1 = a;
     if (HAS2) *s2 = b;
     *gout = g;
-}
-
-// The same for four consecutive elements (16-byte aligned).
-template <int OPT>
-__device__ __forceinline__ void update_vec4(float *p, float *s1, float *s2, float *gout, const float (&g)[4],
-                                            const StepScalars &sc, float wd) {
-    constexpr bool HAS1 = (OPT != VB200_OPT_SGD);
-    constexpr bool HAS2 = (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW);
-    float4 pv = *reinterpret_cast<const float4 *>(p);
-    float4 a = HAS1 ? __ldcs(reinterpret_cast<const float4 *>(s1)) : make_float4(0, 0, 0, 0);
-    float4 b = HAS2 ? __ldcs(reinterpret_cast<const float4 *>(s2)) : make_float4(0, 0, 0, 0);
-    update_one<OPT>(pv.x, a.x, b.x, g[0], sc, wd);
-    update_one<OPT>(pv.y, a.y, b.y, g[1], sc, wd);
-    update_one<OPT>(pv.z, a.z, b.z, g[2], sc, wd);
-    update_one<OPT>(pv.w, a.w, b.w, g[3], sc, wd);
-    *reinterpret_cast<float4 *>(p) = pv;
-    if (HAS1) *reinterpret_cast<float4 *>(s1) = a;
-    if (HAS2) *reinterpret_cast<float4 *>(s2) = b;
-    *reinterpret_cast<float4 *>(gout) = make_float4(g[0], g[1], g[2], g[3]);
 }
 
 template <int OPT>
@@ -232,10 +250,8 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
 
     Barrier bar;
     bar.count = A.barrier;
-    bar.gen = A.barrier + 1;
     bar.abort_word = A.barrier + 2;
     bar.status = A.status;
-    bar.my_gen = *reinterpret_cast<volatile unsigned *>(bar.gen);   // nobody bumps it before all have arrived once
 
     // ---- ask for this CTA's share of parameters and optimizer state to be brought into L2
     if (tid < 3) {
@@ -251,8 +267,7 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
             }
         }
     }
-    const StepScalars sc = *A.scalars;
-    CRUMB(0, 1);
+    const StepScalars &sc = A.scalars;
 
     // =================================================================================== forward
     for (int li = 0; li < n; ++li) {
@@ -264,22 +279,34 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
         const int k0 = q * kc, klen = min(kc, r - k0);           // <= 0: nothing for this rank
         const bool last = li == n - 1;
         float loss_acc = 0.0f;
+        const TileMap tm = tile_map(ncl);
+        const int ntiles = (ncols > 0 && klen > 0) ? ceil_div(klen, KT) : 0;
+        const float *Wl = A.params + L.off_w;
+        auto issue_w = [&](int t) {
+            const int kb = k0 + t * KT, kn = min(KT, k0 + klen - kb);
+            load_tile(bufB + (t & 1) * BUF_B, LDW, Wl + (long long)kb * c + n0, c, kn, ncols, KT, 4 * tm.CG);
+        };
+        auto issue_a = [&](int t) {
+            const int kb = k0 + t * KT, kn = min(KT, k0 + klen - kb);
+            load_tile(bufA + (t & 1) * BUF_A, LD, L.act_in + kb, r, B, kn, BM, KT);
+            cp_async_commit();
+        };
+        // the first W tile does not depend on the previous layer: ask for it before waiting for that layer
+        if (ntiles > 0) issue_w(0);
+        if (li > 0) {
+            grid_barrier(bar);
+        }
         if (ncols > 0) {
-            const TileMap tm = tile_map(ncl);
             float acc[4][4];
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
                 for (int u = 0; u < 4; ++u) acc[i][u] = 0.0f;
-            const int ntiles = klen > 0 ? ceil_div(klen, KT) : 0;
-            const float *Wl = A.params + L.off_w;
             auto issue = [&](int t) {
-                const int kb = k0 + t * KT, kn = min(KT, k0 + klen - kb);
-                load_tile(bufA + (t & 1) * BUF_A, LD, L.act_in + kb, r, B, kn, BM, KT);
-                load_tile(bufB + (t & 1) * BUF_B, LDW, Wl + (long long)kb * c + n0, c, kn, ncols, KT, 4 * tm.CG);
-                cp_async_commit();
+                issue_w(t);
+                issue_a(t);
             };
-            if (ntiles > 0) issue(0);
+            if (ntiles > 0) issue_a(0);
             for (int t = 0; t < ntiles; ++t) {
                 if (t + 1 < ntiles) {
                     issue(t + 1);
@@ -311,19 +338,14 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                     *reinterpret_cast<float4 *>(part + ((tm.kg * BM) + tm.rg + 16 * i) * PLD + 4 * tm.cg) =
                         make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
             }
-            CRUMB(li + 1, 2);
+            fold_kgroups(part, tm.KG, PLD);
             cluster.sync();
-            CRUMB(li + 1, 3);
-            // this CTA adds the S x KG partials of its rows in a fixed order and finishes the elements
+            // this CTA adds the S ranks' tiles of its rows in rank order and finishes the elements
             const float *bias = A.params + L.off_b;
             for (int e = tid; e < RB * ncols; e += T) {
                 const int row = q * RB + e / ncols, col = e % ncols;
                 if (row >= B) continue;
-                float sum = 0.0f;
-                for (int p = 0; p < S; ++p) {
-                    const float *pp = cluster.map_shared_rank(part, p);
-                    for (int g = 0; g < tm.KG; ++g) sum += pp[(g * BM + row) * PLD + col];
-                }
+                const float sum = gather_ranks(cluster, part, S, row * PLD + col);
                 const long long o = (long long)row * c + n0 + col;
                 const float z = sum + bias[n0 + col];
                 if (!last) {
@@ -339,9 +361,7 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                     L.delta[o] = __fdiv_rn(__fmul_rn(2.0f, d), A.nt_global);
                 }
             }
-            CRUMB(li + 1, 4);
-            cluster.sync();   // peers have finished reading this CTA's partials
-            CRUMB(li + 1, 5);
+            // (no second cluster barrier: `part` is next written behind the next grid barrier, or never)
         }
         if (last && A.forward_only) break;   // inference: the outputs are stored, nothing follows
         if (last) {
@@ -355,45 +375,47 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                 A.loss_partials[blockIdx.x] = t;
             }
         }
-        CRUMB(li + 1, 6);
-        grid_barrier(bar);
-        CRUMB(li + 1, 7);
     }
 
     // =================================================================================== backward
     for (int li = A.forward_only ? -1 : n - 1; li >= 0; --li) {
         const SmallStepLayer &L = A.L[li];
         const int r = L.r, c = L.c;
-        if (li == n - 1 && blockIdx.x == 0 && tid == 0) {
-            float t = 0.0f;
-            for (unsigned b = 0; b < gridDim.x; ++b) t += __ldcg(A.loss_partials + b);
-            *A.loss_sum = t;
-        }
         const int kcl = round4(ceil_div(r, NC));                 // rows of W per cluster (<= WMAX)
         const int k0 = j * kcl, krows = min(kcl, r - k0);        // <= 0: nothing for this cluster
         const int nc = round4(ceil_div(c, S));
         const int n0 = q * nc, nlen = min(nc, c - n0);           // <= 0: nothing for this rank
         const bool need_dx = li > 0;
+        const TileMap tm = tile_map(kcl);                        // for the dX partial [BM x kcl]
+        const int ntiles = (krows > 0 && nlen > 0) ? ceil_div(nlen, KT) : 0;
+        float *Wl = A.params + L.off_w;
+        const int wrows_pad = 4 * tm.CG;                         // rows of the W tile that dX reads (zero beyond krows)
+        auto issue_w = [&](int t) {
+            const int nb = n0 + t * KT, nn = min(KT, n0 + nlen - nb);
+            load_tile(bufB + (t & 1) * BUF_B, LD, Wl + (long long)k0 * c + nb, c, krows, nn, wrows_pad, KT);
+        };
+        auto issue_d = [&](int t) {
+            const int nb = n0 + t * KT, nn = min(KT, n0 + nlen - nb);
+            load_tile(bufA + (t & 1) * BUF_A, LD, L.delta + nb, c, B, nn, BM, KT);
+            cp_async_commit();
+        };
+        // W and this layer's input activations were final long ago: ask for them before waiting for the deltas
+        if (ntiles > 0) {
+            load_tile(actc, LDW, L.act_in + k0, r, B, krows, BM, round4(kcl));
+            issue_w(0);
+        }
+        grid_barrier(bar);
         if (krows > 0) {
-            const TileMap tm = tile_map(kcl);                    // for the dX partial [BM x kcl]
             float acc[4][4];
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
                 for (int u = 0; u < 4; ++u) acc[i][u] = 0.0f;
-            const int ntiles = nlen > 0 ? ceil_div(nlen, KT) : 0;
-            float *Wl = A.params + L.off_w;
-            const int wrows_pad = 4 * tm.CG;                     // rows of the W tile that dX reads (zero beyond krows)
             auto issue = [&](int t) {
-                const int nb = n0 + t * KT, nn = min(KT, n0 + nlen - nb);
-                load_tile(bufA + (t & 1) * BUF_A, LD, L.delta + nb, c, B, nn, BM, KT);
-                load_tile(bufB + (t & 1) * BUF_B, LD, Wl + (long long)k0 * c + nb, c, krows, nn, wrows_pad, KT);
-                cp_async_commit();
+                issue_w(t);
+                issue_d(t);
             };
-            if (ntiles > 0) {
-                load_tile(actc, LDW, L.act_in + k0, r, B, krows, BM, round4(kcl));
-                issue(0);
-            }
+            if (ntiles > 0) issue_d(0);
             for (int t = 0; t < ntiles; ++t) {
                 if (t + 1 < ntiles) {
                     issue(t + 1);
@@ -404,12 +426,34 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                 __syncthreads();
                 const float *ds = bufA + (t & 1) * BUF_A, *ws = bufB + (t & 1) * BUF_B;
                 const int nb = n0 + t * KT, nn = min(KT, n0 + nlen - nb);
-                // ---- bias gradient of this tile's columns (cluster 0 only), ascending rows, and its update
-                if (j == 0 && tid < nn) {
-                    float g = 0.0f;
-                    for (int b = 0; b < B; ++b) g += ds[b * LD + tid];
-                    const long long e = L.off_b + nb + tid;
-                    update_elem<OPT>(A.params + e, A.s1 + e, A.s2 + e, A.grads + e, g, sc, 0.0f);
+                // ---- bias gradient: of the NA clusters that own rows of this W, cluster j takes the tile's columns
+                // j, j + NA, ... (all of them hold the same delta tile); warp 0 sums a column's rows on a fixed
+                // tree (lane l: rows l and l + 32, then shuffles), lane i applies the update for the i-th column
+                // (the parameter and its state are asked for here and used at the end of the tile)
+                float db_g = 0.0f, db_p = 0.0f, db_s1 = 0.0f, db_s2 = 0.0f;
+                long long db_e = -1;
+                auto db_finish = [&]() {
+                    update_one<OPT>(db_p, db_s1, db_s2, db_g, sc, 0.0f);
+                    A.params[db_e] = db_p;
+                    if (OPT != VB200_OPT_SGD) A.s1[db_e] = db_s1;
+                    if (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW) A.s2[db_e] = db_s2;
+                    A.grads[db_e] = db_g;
+                };
+                if (tid < 32) {
+                    const int NA = ceil_div(r, kcl);   // clusters with krows > 0
+                    for (int i = 0, col = j; col < nn; ++i, col += NA) {
+                        float v = ds[tid * LD + col] + ds[(tid + 32) * LD + col];
+#pragma unroll
+                        for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                        if ((i & 31) == tid) {
+                            if (db_e >= 0) db_finish();   // more than 32 columns for this cluster: finish the earlier one first
+                            db_g = v;
+                            db_e = L.off_b + nb + col;
+                            db_p = A.params[db_e];
+                            if (OPT != VB200_OPT_SGD) db_s1 = __ldcs(A.s1 + db_e);
+                            if (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW) db_s2 = __ldcs(A.s2 + db_e);
+                        }
+                    }
                 }
                 // ---- dW block = act^T . delta (sum over the batch, ascending), then the optimizer on it
                 {
@@ -422,6 +466,21 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                         for (int i = 0; i < 4; ++i)
 #pragma unroll
                             for (int u = 0; u < 4; ++u) g[i][u] = 0.0f;
+                        // optimizer state of the four rows, asked for before the products so that its latency
+                        // hides behind them (the weights themselves sit in the shared-memory tile)
+                        constexpr bool HAS1 = (OPT != VB200_OPT_SGD);
+                        constexpr bool HAS2 = (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW);
+                        const bool vec = (c & 3) == 0 && 4 * ng + 3 < nn;   // offsets and n0, nb are multiples of 4
+                        float4 st1[4], st2[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            st1[i] = st2[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                            if (vec && kk0 + i < krows) {
+                                const long long e = L.off_w + (long long)(k0 + kk0 + i) * c + nb + 4 * ng;
+                                if (HAS1) st1[i] = load_early(A.s1 + e);
+                                if (HAS2) st2[i] = load_early(A.s2 + e);
+                            }
+                        }
 #pragma unroll 4
                         for (int b = 0; b < B; ++b) {
                             const float4 av = *reinterpret_cast<const float4 *>(actc + b * LDW + kk0);
@@ -436,14 +495,45 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                             }
                         }
                         const float wd = OPT == VB200_OPT_ADAMW ? sc.weight_decay : 0.0f;
-                        const bool vec = (c & 3) == 0 && 4 * ng + 3 < nn;   // offsets and n0, nb are multiples of 4
+                        if (c == 1) {
+                            // a width-one layer's W is a column: this thread's four rows are four consecutive floats
+                            // (k0 and kk0 are multiples of 4), updated as one group where all four exist
+                            if (ng == 0 && kk0 < krows) {
+                                const long long e = L.off_w + k0 + kk0;
+                                if (kk0 + 3 < krows) {
+                                    float4 pv = *reinterpret_cast<const float4 *>(A.params + e);
+                                    float4 a1 = HAS1 ? __ldcs(reinterpret_cast<const float4 *>(A.s1 + e)) : make_float4(0, 0, 0, 0);
+                                    float4 a2 = HAS2 ? __ldcs(reinterpret_cast<const float4 *>(A.s2 + e)) : make_float4(0, 0, 0, 0);
+                                    update_one<OPT>(pv.x, a1.x, a2.x, g[0][0], sc, wd);
+                                    update_one<OPT>(pv.y, a1.y, a2.y, g[1][0], sc, wd);
+                                    update_one<OPT>(pv.z, a1.z, a2.z, g[2][0], sc, wd);
+                                    update_one<OPT>(pv.w, a1.w, a2.w, g[3][0], sc, wd);
+                                    *reinterpret_cast<float4 *>(A.params + e) = pv;
+                                    if (HAS1) *reinterpret_cast<float4 *>(A.s1 + e) = a1;
+                                    if (HAS2) *reinterpret_cast<float4 *>(A.s2 + e) = a2;
+                                    *reinterpret_cast<float4 *>(A.grads + e) = make_float4(g[0][0], g[1][0], g[2][0], g[3][0]);
+                                } else {
+                                    for (int i = 0; kk0 + i < krows; ++i)
+                                        update_elem<OPT>(A.params + e + i, A.s1 + e + i, A.s2 + e + i, A.grads + e + i, g[i][0], sc, wd);
+                                }
+                            }
+                            continue;
+                        }
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             const int kk = kk0 + i;
                             if (kk >= krows) continue;
                             const long long e = L.off_w + (long long)(k0 + kk) * c + nb + 4 * ng;
                             if (vec) {
-                                update_vec4<OPT>(A.params + e, A.s1 + e, A.s2 + e, A.grads + e, g[i], sc, wd);
+                                float4 pv = *reinterpret_cast<const float4 *>(ws + kk * LD + 4 * ng);   // pre-update W
+                                update_one<OPT>(pv.x, st1[i].x, st2[i].x, g[i][0], sc, wd);
+                                update_one<OPT>(pv.y, st1[i].y, st2[i].y, g[i][1], sc, wd);
+                                update_one<OPT>(pv.z, st1[i].z, st2[i].z, g[i][2], sc, wd);
+                                update_one<OPT>(pv.w, st1[i].w, st2[i].w, g[i][3], sc, wd);
+                                *reinterpret_cast<float4 *>(A.params + e) = pv;
+                                if (HAS1) *reinterpret_cast<float4 *>(A.s1 + e) = st1[i];
+                                if (HAS2) *reinterpret_cast<float4 *>(A.s2 + e) = st2[i];
+                                *reinterpret_cast<float4 *>(A.grads + e) = make_float4(g[i][0], g[i][1], g[i][2], g[i][3]);
                             } else {
 #pragma unroll
                                 for (int u = 0; u < 4; ++u)
@@ -466,6 +556,7 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                         fma_nt(acc, d, w);
                     }
                 }
+                if (db_e >= 0) db_finish();
                 __syncthreads();
             }
             if (need_dx) {
@@ -477,30 +568,36 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
 #pragma unroll
                         for (int u = 0; u < 4; ++u) part[((tm.kg * BM) + tm.rg + 16 * i) * PLD + tm.cg + tm.CG * u] = acc[i][u];
                 }
-                CRUMB(64 + li, 2);
+                fold_kgroups(part, tm.KG, PLD);
                 cluster.sync();
-                CRUMB(64 + li, 3);
                 for (int e = tid; e < RB * krows; e += T) {
                     const int row = q * RB + e / krows, kk = e % krows;
                     if (row >= B) continue;
-                    float sum = 0.0f;
-                    for (int p = 0; p < S; ++p) {
-                        const float *pp = cluster.map_shared_rank(part, p);
-                        for (int g = 0; g < tm.KG; ++g) sum += pp[(g * BM + row) * PLD + kk];
-                    }
+                    const float sum = gather_ranks(cluster, part, S, row * PLD + kk);
                     const long long o = (long long)row * r + k0 + kk;
                     L.delta_prev[o] = sum * act_backward(A.act, __ldcg(L.saved_prev + o));
                 }
-                cluster.sync();
+                // (no second cluster barrier: the next phase writes `part` behind its grid barrier)
             }
         }
-        CRUMB(64 + li, 6);
-        if (li > 0) grid_barrier(bar);
-        CRUMB(64 + li, 7);
     }
-    CRUMB(255, 1);
+    if (blockIdx.x == 0 && !A.forward_only) {
+        // The loss: every CTA's partial (final since the barrier behind the last forward layer), added in CTA
+        // order.  Done here, where nobody waits for CTA 0: warp 0 fetches the partials in parallel, thread 0 adds.
+        float *lp = bufA;   // the staging buffers are idle by now
+        for (unsigned b = tid; b < gridDim.x; b += T) lp[b] = __ldcg(A.loss_partials + b);
+        __syncthreads();
+        if (tid == 0) {
+            float t = 0.0f;
+            for (unsigned b = 0; b < gridDim.x; ++b) t += lp[b];
+            *A.loss_sum = t;
+            if (A.host_loss) *reinterpret_cast<volatile float *>(A.host_loss) = t;
+            // CTA 0 passed every barrier, so no other CTA can still be about to give up on one: the status word is final
+            if (A.host_status) *reinterpret_cast<volatile unsigned *>(A.host_status) = *reinterpret_cast<volatile unsigned *>(A.status);
+            __threadfence_system();
+        }
+    }
     cluster.sync();   // no CTA leaves while a peer may still read its shared memory
-    CRUMB(255, 2);
 }
 
 bool g_smem_set[kMaxDevices][5] = {};
@@ -560,10 +657,6 @@ int max_clusters(int S) {
 }
 
 }  // namespace
-
-#ifdef VB_STEP_DEBUG
-extern "C" void vb_step_debug_set(unsigned *host_mapped) { cudaMemcpyToSymbol(g_step_progress, &host_mapped, sizeof host_mapped); }
-#endif
 
 // Shape limits of the persistent step (a function of the topology and of the cluster count alone).
 bool small_step_shape_ok(const int *layers, int n_sizes, int batch, int clusters) {
