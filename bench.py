@@ -367,8 +367,9 @@ def run_workload(job: Job, cfg, args, steps: int, warmup: int, device_data: bool
     def make_handle():
         h = TrainHandle(layers, cfg.activation, cfg.optimizer, B, global_batch=cfg.batch, world_size=world, rank=rank,
                         unique_id=job.unique_id(), gemm_path=args.gemm_path,
-                        fuse_sgd=(cfg.optimizer == "sgd" and world == 1))
-        if world > 1 and args.dp_mode == "fused":
+                        fuse_sgd=(cfg.optimizer == "sgd" and world == 1),
+                        dp_exchange="peer_copy" if (world > 1 and args.dp_mode == "copy") else "nccl")
+        if world > 1 and args.dp_mode in ("fused", "copy"):
             handles = [None] * world
             dist.all_gather_object(handles, h.ipc_handle())
             h.attach_peers(handles)
@@ -462,7 +463,7 @@ def run_workload(job: Job, cfg, args, steps: int, warmup: int, device_data: bool
 
     # ---- per-kernel times (single GPU only; plain launches, event pairs)
     kernel_table, agg = None, None
-    if profile and (world == 1 or args.dp_mode == "nccl"):
+    if profile and (world == 1 or args.dp_mode in ("nccl", "copy")):
         agg = {}
         reps = 3
         for _ in range(reps):
@@ -485,7 +486,10 @@ def run_workload(job: Job, cfg, args, steps: int, warmup: int, device_data: bool
         bits = int(np.float32(g.loss()).view(np.uint32))
         g.free()
         return bits
-    a_bits, b_bits = short_run(), short_run()
+    if args.lean:
+        a_bits = b_bits = 0
+    else:
+        a_bits, b_bits = short_run(), short_run()
     same = a_bits == b_bits
     if world > 1:
         t = torch.tensor([a_bits, b_bits], device="cuda", dtype=torch.int64)
@@ -640,9 +644,12 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-workloads", action="store_true")
     ap.add_argument("--no-c5", action="store_true")
-    ap.add_argument("--dp-mode", default="nccl", choices=["nccl", "fused"],
-                    help="gradient exchange under data parallelism: bucketed NCCL all-reduce + optimizer, or the fused "
-                         "peer-memory reduce + update kernels")
+    ap.add_argument("--lean", action="store_true",
+                    help="for profiler captures: no TF32 peak measurement, no per-kernel profile, no repeat-run check")
+    ap.add_argument("--dp-mode", default="nccl", choices=["nccl", "fused", "copy"],
+                    help="gradient exchange under data parallelism: bucketed NCCL all-reduce + optimizer, the fused "
+                         "peer-memory reduce + update kernels, or copy-engine pushes into per-rank receive slots + a local "
+                         "ordered sum and update")
     ap.add_argument("--batch", type=int, default=None,
                     help="override the workload's global batch (for small profiler captures; not a headline number)")
     args = ap.parse_args()
@@ -677,15 +684,16 @@ def main():
     torch = job.torch
     peaks = measured_peaks()
     tf32 = None
-    if world == 1:
+    if world == 1 and not args.lean:
         try:
             tf32 = measure_tf32_peak()
         except Exception as exc:  # the bf16-derived denominator is then used and said so
             tf32 = None
             print("TF32 peak measurement failed: %s" % exc, file=sys.stderr)
 
-    res = run_workload(job, cfg, args, steps, warmup, device_data=cfg.batch * cfg.layers[0] > 3e8, profile=True)
-    roofline = roofline_of(res, cfg, peaks, tf32) if world == 1 else None
+    res = run_workload(job, cfg, args, steps, warmup, device_data=cfg.batch * cfg.layers[0] > 3e8, profile=not args.lean,
+                       e2e_steps=0 if args.lean else None)
+    roofline = roofline_of(res, cfg, peaks, tf32) if (world == 1 and res["agg"]) else None
     if world > 1 and res["agg"]:
         # per-phase view of rank 0's step under data parallelism (plain launches, the exchange overlapped as in
         # the graph): where the time beyond global-batch / N goes

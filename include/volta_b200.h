@@ -46,6 +46,9 @@ enum { VB200_OPT_SGD = 0, VB200_OPT_ADAM = 1, VB200_OPT_ADAMW = 2, VB200_OPT_ADA
  * GEMM that can take it; TENSOR_PAIR forces the CTA-pair kernel for outputs of at least 256 x 256
  * (other shapes go as under TENSOR). */
 enum { VB200_GEMM_AUTO = 0, VB200_GEMM_FFMA = 1, VB200_GEMM_TENSOR = 2, VB200_GEMM_TENSOR_PAIR = 3 };
+/* how data-parallel ranks exchange gradients once volta_b200_dp_attach_peers has been called (before that,
+ * and always with VB200_DP_NCCL, gradient buckets are all-reduced by NCCL) */
+enum { VB200_DP_NCCL = 0, VB200_DP_PEER_KERNEL = 1, VB200_DP_PEER_COPY = 2 };
 
 /* Error codes (0 = success). The reference reports no errors on this path
  * (void functions, mlp_train_rust_codegen.rs:670-699); the replacement never traps and
@@ -100,6 +103,9 @@ typedef struct vb200_config {
     int32_t step_kernel;               /* the whole step as ONE persistent kernel (one GPU, batch <= 64, widths up to
                                           64 x SMs/4, none of the optional stages): 0 = wherever that applies and
                                           gemm_path is AUTO, 1 = never, 2 = required (create fails otherwise) */
+    int32_t dp_exchange;               /* VB200_DP_*: what volta_b200_dp_attach_peers switches the step to.  0 and 1:
+                                          the peer-memory kernel.  2: copies; the arena then also holds one
+                                          gradient-sized receive slot per rank, so it must be chosen at creation */
 } vb200_config;
 
 typedef struct vb200_handle vb200_handle;
@@ -261,7 +267,12 @@ int volta_b200_dp_check(const uint8_t id[128], int32_t world_size, int32_t rank,
  * gradients with peer loads in rank order, applies the optimizer to that share and stores the new
  * parameters into every rank's arena; flag words in the arenas order the ranks, with bounded waits.
  * Needs peer access between the GPUs (NVLink); at most 8 ranks; optimizer state becomes sharded
- * (save_state is refused). */
+ * (save_state is refused).
+ * With dp_exchange = VB200_DP_PEER_COPY the attached handle exchanges by COPY instead: as soon as a layer's dW
+ * exists, the rank's copy engines push it into its receive slot in every peer's arena (no SM is taken from the
+ * backward GEMMs that run meanwhile); once a flag barrier shows that all ranks' pushes of the bucket have landed,
+ * one kernel per rank adds the N copies in rank order and applies the optimizer to the whole bucket.  Every
+ * rank keeps the full optimizer state (save_state works), and the sum has the same fixed order on every rank. */
 int volta_b200_dp_ipc_handle(vb200_handle *h, uint8_t out[64]);
 int volta_b200_dp_attach_peers(vb200_handle *h, const uint8_t *handles, int32_t count);
 /* Failure detection of that path, checked without failing anything: runs ONE barrier kernel on this

@@ -56,7 +56,8 @@ def oracle_shard_worker(rank, world, port, opt, real, out_dir, act="silu", dropo
 
 
 def gpu_shard_worker(rank, world, port, opt, out_dir, repeat, fused=False, act="silu", options=None):
-    """One GPU rank: libvolta_b200 handle on its row shard; the unique id travels over gloo."""
+    """One GPU rank: libvolta_b200 handle on its row shard; the unique id travels over gloo.  fused: False (NCCL),
+    True / "fused" (the peer-memory kernel) or "copy" (pushes by the copy engines + local sum)."""
     import torch
     import torch.distributed as dist
     from volta_b200 import TrainHandle
@@ -71,7 +72,7 @@ def gpu_shard_worker(rank, world, port, opt, out_dir, repeat, fused=False, act="
         box = [dp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         h = TrainHandle(LAYERS, act, opt, B, global_batch=GLOBAL_BATCH, world_size=world, rank=rank, unique_id=box[0],
-                        **(options or {}))
+                        dp_exchange="peer_copy" if fused == "copy" else "nccl", **(options or {}))
         if fused:
             handles = [None] * world
             dist.all_gather_object(handles, h.ipc_handle())
@@ -90,7 +91,7 @@ def gpu_shard_worker(rank, world, port, opt, out_dir, repeat, fused=False, act="
     dist.destroy_process_group()
 
 
-def gpu_missing_rank_worker(rank, world, port, out_dir, wait_ms=200):
+def gpu_missing_rank_worker(rank, world, port, out_dir, wait_ms=200, exchange="nccl"):
     """Two ranks on the fused peer-memory path take two steps together; then rank 1 sits a step out (alive,
     its arena still mapped, nothing of its own in flight) while rank 0 steps alone with a short wait limit.
     Rank 0 records what it saw: the error code, and its parameters before and after the lonely step."""
@@ -108,7 +109,7 @@ def gpu_missing_rank_worker(rank, world, port, out_dir, wait_ms=200):
     box = [dp_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(box, src=0)
     h = TrainHandle(LAYERS, "silu", "adam", B, global_batch=GLOBAL_BATCH, world_size=world, rank=rank, unique_id=box[0],
-                    device_wait_ms=wait_ms)
+                    device_wait_ms=wait_ms, dp_exchange=exchange)
     handles = [None] * world
     dist.all_gather_object(handles, h.ipc_handle())
     h.attach_peers(handles)

@@ -32,7 +32,10 @@ def test_data_parallel_path_on_a_single_rank_matches_the_plain_path():
     x, y, ws, bs = dpc.inputs()
     outs = []
     for dp in (False, True):
-        h = TrainHandle(dpc.LAYERS, "silu", "adam", dpc.GLOBAL_BATCH, force_dp=dp, unique_id=dp_unique_id() if dp else None)
+        # step_kernel=1: both handles on the per-kernel schedule (at this batch a plain handle would otherwise take
+        # the persistent step kernel, whose sums are ordered differently)
+        h = TrainHandle(dpc.LAYERS, "silu", "adam", dpc.GLOBAL_BATCH, force_dp=dp, unique_id=dp_unique_id() if dp else None,
+                        step_kernel=1)
         for i, (w, b) in enumerate(zip(ws, bs)):
             h.set_params(i, w, b)
         losses = []
@@ -46,17 +49,19 @@ def test_data_parallel_path_on_a_single_rank_matches_the_plain_path():
         assert np.array_equal(a, b)
 
 
+@pytest.mark.parametrize("exchange", ["peer_kernel", "peer_copy"])
 @pytest.mark.parametrize("opt", ["adam", "sgd_momentum"])
-def test_fused_peer_memory_update_on_a_single_rank_matches_the_plain_path(opt):
-    """The fused reduce + update + redistribute kernels and their flag barriers with one rank (its
-    own arena as the only peer): a sum over one rank adds nothing, so the bits must equal the plain
-    handle's."""
+def test_fused_peer_memory_update_on_a_single_rank_matches_the_plain_path(opt, exchange):
+    """The fused reduce + update + redistribute kernels (or, by copy, the gather + update kernels) and their flag
+    barriers with one rank (its own arena as the only peer): a sum over one rank adds nothing, so the bits must
+    equal the plain handle's."""
     from volta_b200 import TrainHandle
     from volta_b200.train import dp_unique_id
     x, y, ws, bs = dpc.inputs()
     outs = []
     for fused in (False, True):
-        h = TrainHandle(dpc.LAYERS, "silu", opt, dpc.GLOBAL_BATCH, force_dp=fused, unique_id=dp_unique_id() if fused else None)
+        h = TrainHandle(dpc.LAYERS, "silu", opt, dpc.GLOBAL_BATCH, force_dp=fused, unique_id=dp_unique_id() if fused else None,
+                        step_kernel=1, dp_exchange=exchange if fused else "nccl")
         if fused:
             h.attach_peers([h.ipc_handle()])
         for i, (w, b) in enumerate(zip(ws, bs)):
@@ -73,13 +78,14 @@ def test_fused_peer_memory_update_on_a_single_rank_matches_the_plain_path(opt):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("mode", ["nccl", "fused"])
+@pytest.mark.parametrize("mode", ["nccl", "fused", "copy"])
 @pytest.mark.parametrize("opt", ["sgd_momentum", "adam"])
 def test_gpu_ranks_match_the_full_batch_oracle(opt, mode, world):
     if torch.cuda.device_count() < world:
         pytest.skip("needs %d GPUs" % world)
     out = tempfile.mkdtemp()
-    mp.spawn(dpc.gpu_shard_worker, args=(world, _free_port(), opt, out, 2, mode == "fused"), nprocs=world, join=True)
+    mp.spawn(dpc.gpu_shard_worker, args=(world, _free_port(), opt, out, 2, {"nccl": False, "fused": True, "copy": "copy"}[mode]),
+             nprocs=world, join=True)
     x, y, ws, bs = dpc.inputs()
     o = Oracle(dpc.LAYERS, "silu", opt, dpc.GLOBAL_BATCH)
     for i, (w, b) in enumerate(zip(ws, bs)):
@@ -147,14 +153,15 @@ def test_two_gpu_ranks_with_the_optional_stages_match_the_full_batch_oracle():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_a_rank_that_sits_a_step_out_is_detected_and_no_update_is_applied(monkeypatch):
-    """Failure detection on the fused peer-memory path, made on the host: rank 1 stays alive with its arena
+@pytest.mark.parametrize("exchange", ["peer_kernel", "peer_copy"])
+def test_a_rank_that_sits_a_step_out_is_detected_and_no_update_is_applied(monkeypatch, exchange):
+    """Failure detection on the peer-memory paths, made on the host: rank 1 stays alive with its arena
     mapped but does not take the third step.  Rank 0's barrier gives up after its limit (200 ms), the
     reduce + update kernels then touch no rank's memory, the step reports VB200_ERR_DEVICE_WAIT, rank 0's
     parameters are bit-identical to before the step and further steps are refused.  No rank is killed."""
     monkeypatch.setenv("NCCL_NVLS_ENABLE", "0")
     out = tempfile.mkdtemp()
-    mp.spawn(dpc.gpu_missing_rank_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    mp.spawn(dpc.gpu_missing_rank_worker, args=(2, _free_port(), out, 200, exchange), nprocs=2, join=True)
     r = np.load("%s/rank0.npz" % out)
     assert int(r["code"]) == 5 and "did not reach a barrier" in str(r["msg"])
     assert int(r["get_params_rc"]) == 5 and int(r["refused"]) == 5

@@ -300,6 +300,15 @@ cudaError_t launch_dp_reduce_update(int optimizer, const PeerTable &peers, long 
                                     long long s1_off, long long s2_off, long long seg_begin, long long seg_len,
                                     long long n_decay, int world, int rank, const StepScalars *scalars,
                                     long long loss_off, const unsigned int *status, cudaStream_t s);
+// Exchange by copy: for the floats [seg_begin, seg_begin + seg_len) this rank adds the `world` gradient copies
+// (its own `grads`, and for every other rank q the receive slot recv + q * slot_floats that rank q's copy
+// engines filled) in rank order, stores the sum back into `grads` and applies the optimizer to the whole
+// segment.  With loss_index >= 0 the loss sums at that index of every copy are added likewise into
+// grads[loss_index + 1].  Local memory only.  Does nothing once the DP-barrier bit of *status is set.
+cudaError_t launch_dp_gather_update(int optimizer, float *params, float *s1, float *s2, float *grads, const float *recv,
+                                    long long slot_floats, long long seg_begin, long long seg_len, long long n_decay,
+                                    int world, int rank, const StepScalars *scalars, long long loss_index,
+                                    const unsigned int *status, cudaStream_t s);
 constexpr unsigned kStatusDpBarrier = 64u;   // status-word bit: a data-parallel barrier wait ran out
 
 // ---- the whole step as one persistent kernel, batches of at most 64 rows (vb_step_small.cu)

@@ -112,7 +112,84 @@ __global__ void __launch_bounds__(256) dp_reduce_update_kernel(PeerTable peers, 
     __threadfence_system();
 }
 
+// The copy exchange's consumer: every rank's copy of the segment is local by now (own gradients in `grads`,
+// rank q's in its receive slot), so this is the streaming optimizer with `world` gradient operands.
+template <int OPT>
+__global__ void __launch_bounds__(256) dp_gather_update_kernel(float *__restrict__ params, float *__restrict__ s1p,
+                                                               float *__restrict__ s2p, float *__restrict__ grads,
+                                                               const float *__restrict__ recv, long long slot_floats,
+                                                               long long seg_begin, long long seg_len, long long n_decay,
+                                                               int world, int rank, const StepScalars *__restrict__ scp,
+                                                               long long loss_index, const unsigned int *__restrict__ status) {
+    pdl_wait();
+    if (*reinterpret_cast<const volatile unsigned int *>(status) & ST_DP_BARRIER) return;
+    const StepScalars sc = *scp;
+    constexpr bool HAS1 = (OPT != VB200_OPT_SGD);
+    constexpr bool HAS2 = (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW);
+    const long long seg4 = seg_len >> 2, b4 = seg_begin >> 2;
+    float4 *g4 = reinterpret_cast<float4 *>(grads) + b4;
+    float4 *p4 = reinterpret_cast<float4 *>(params) + b4;
+    float4 *a4 = reinterpret_cast<float4 *>(s1p) + b4;
+    float4 *c4 = reinterpret_cast<float4 *>(s2p) + b4;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < seg4; i += stride) {
+        float4 v[kMaxPeers];
+#pragma unroll
+        for (int q = 0; q < kMaxPeers; ++q)   // all loads first, then the sum in rank order
+            if (q < world)
+                v[q] = q == rank ? g4[i] : __ldcs(reinterpret_cast<const float4 *>(recv + q * slot_floats) + b4 + i);
+        float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int q = 0; q < kMaxPeers; ++q)
+            if (q < world) { g.x += v[q].x; g.y += v[q].y; g.z += v[q].z; g.w += v[q].w; }
+        float4 pv = p4[i];
+        float4 a = HAS1 ? a4[i] : make_float4(0, 0, 0, 0);
+        float4 b = HAS2 ? c4[i] : make_float4(0, 0, 0, 0);
+        const long long e = seg_begin + (i << 2);
+        const float wd0 = (OPT == VB200_OPT_ADAMW && e + 0 < n_decay) ? sc.weight_decay : 0.0f;
+        const float wd1 = (OPT == VB200_OPT_ADAMW && e + 1 < n_decay) ? sc.weight_decay : 0.0f;
+        const float wd2 = (OPT == VB200_OPT_ADAMW && e + 2 < n_decay) ? sc.weight_decay : 0.0f;
+        const float wd3 = (OPT == VB200_OPT_ADAMW && e + 3 < n_decay) ? sc.weight_decay : 0.0f;
+        update_one<OPT>(pv.x, a.x, b.x, g.x, sc, wd0);
+        update_one<OPT>(pv.y, a.y, b.y, g.y, sc, wd1);
+        update_one<OPT>(pv.z, a.z, b.z, g.z, sc, wd2);
+        update_one<OPT>(pv.w, a.w, b.w, g.w, sc, wd3);
+        p4[i] = pv;
+        if (HAS1) a4[i] = a;
+        if (HAS2) c4[i] = b;
+        g4[i] = g;   // the global gradient, as the all-reduce path leaves it
+    }
+    if (loss_index >= 0 && blockIdx.x == 0 && threadIdx.x == 0) {
+        float total = 0.0f;
+        for (int q = 0; q < world; ++q) total += q == rank ? grads[loss_index] : recv[q * slot_floats + loss_index];
+        grads[loss_index + 1] = total;
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_dp_gather_update(int optimizer, float *params, float *s1, float *s2, float *grads, const float *recv,
+                                    long long slot_floats, long long seg_begin, long long seg_len, long long n_decay,
+                                    int world, int rank, const StepScalars *scalars, long long loss_index,
+                                    const unsigned int *status, cudaStream_t s) {
+    if (seg_len <= 0 || (seg_len & 3) || (seg_begin & 3) || (slot_floats & 3) || world < 1 || world > kMaxPeers)
+        return cudaErrorInvalidValue;
+    long long want = ((seg_len >> 2) + 255) / 256;
+    const int cap = device_sm_count() * 8;
+    int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+#define VB_DP_LAUNCH(O)                                                                                              \
+    return launch_pdl(dp_gather_update_kernel<O>, dim3(blocks), dim3(256), 0, s, params, s1, s2, grads, recv, slot_floats, \
+                      seg_begin, seg_len, n_decay, world, rank, scalars, loss_index, status)
+    switch (optimizer) {
+    case VB200_OPT_SGD: VB_DP_LAUNCH(VB200_OPT_SGD);
+    case VB200_OPT_ADAM: VB_DP_LAUNCH(VB200_OPT_ADAM);
+    case VB200_OPT_ADAMW: VB_DP_LAUNCH(VB200_OPT_ADAMW);
+    case VB200_OPT_ADAGRAD: VB_DP_LAUNCH(VB200_OPT_ADAGRAD);
+    case VB200_OPT_SGD_MOMENTUM: VB_DP_LAUNCH(VB200_OPT_SGD_MOMENTUM);
+    }
+#undef VB_DP_LAUNCH
+    return cudaErrorInvalidValue;
+}
 
 cudaError_t launch_dp_barrier(const PeerTable &peers, long long flags_off, int world, int rank,
                               const StepScalars *scalars, unsigned stride, unsigned index, unsigned int *status,

@@ -117,6 +117,11 @@ struct vb200_handle {
     DpComm *dp = nullptr;
     // fused data parallelism over peer memory (after volta_b200_dp_attach_peers)
     bool dp_fused = false;
+    // exchange by copy (dp_exchange = VB200_DP_PEER_COPY, after attach): one receive slot per rank in the arena
+    bool dp_copy = false;
+    float *recv = nullptr;
+    long long off_recv = 0, recv_slot_floats = 0;
+    std::vector<cudaEvent_t> ev_dx;
     PeerTable peers{};
     std::vector<void *> peer_mappings;   // cudaIpcOpenMemHandle results to close
     long long off_params = 0, off_grads = 0, off_s1 = 0, off_s2 = 0, off_flags = 0, off_loss = 0;  // bytes in the arena
@@ -298,11 +303,11 @@ int enqueue_step_tail(vb200_handle *h, int slot) {
         // the gradient region carries the loss sum right behind it (one more float, or two when the fused
         // data-parallel path keeps the all-rank total beside the local sum)
         VB_CUDA(h, launch_finite_guard(h->params, h->grads, has1 ? h->s1 : nullptr, has2 ? h->s2 : nullptr,
-                                       h->n_params_padded, h->n_params_padded + (h->dp_fused ? 2 : 1), h->first_bad, s));
+                                       h->n_params_padded, h->n_params_padded + ((h->dp_fused || h->dp_copy) ? 2 : 1), h->first_bad, s));
         VB_CUDA(h, cudaMemcpyAsync(h->host_first_bad, h->first_bad, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s));
     }
     if (h->small_step) return VB200_OK;   // the persistent kernel stores loss and status into pinned memory itself
-    VB_CUDA(h, cudaMemcpyAsync(&h->host_loss[slot], h->dp_fused ? h->loss_sum + 1 : h->loss_sum, sizeof(float),
+    VB_CUDA(h, cudaMemcpyAsync(&h->host_loss[slot], (h->dp_fused || h->dp_copy) ? h->loss_sum + 1 : h->loss_sum, sizeof(float),
                                cudaMemcpyDeviceToHost, s));
     VB_CUDA(h, cudaMemcpyAsync(h->host_status, h->status_word, sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
     return VB200_OK;
@@ -438,6 +443,21 @@ int enqueue_step(vb200_handle *h, int slot) {
         VB_CUDA(h, run_gemm(h, GEMM_NT, h->delta[i], h->params + h->off_w[i], B, r, c, e));
         return VB200_OK;
     };
+#define VB_TRY(call)          \
+    do {                      \
+        int _rc = (call);     \
+        if (_rc) return _rc;  \
+    } while (0)
+    // exchange by copy: floats [begin, begin + count) of this rank's gradient region go into slot `rank` of every
+    // other rank's arena, nearest higher rank first, so that at any moment the ranks write to different peers
+    auto push_to_peers = [&](long long begin, long long count) -> int {
+        for (int d = 1; d < h->world; ++d) {
+            const int p = (h->rank + d) % h->world;
+            char *dst = h->peers.base[p] + h->off_recv + ((long long)h->rank * h->recv_slot_floats + begin) * 4;
+            VB_CUDA(h, cudaMemcpyAsync(dst, h->grads + begin, (size_t)count * 4, cudaMemcpyDeviceToDevice, h->comm_stream));
+        }
+        return VB200_OK;
+    };
     auto do_dw = [&](int i) -> int {
         const long long r = L[i], c = L[i + 1];
         const bool fused = h->fuse_sgd && c != 1;
@@ -457,7 +477,12 @@ int enqueue_step(vb200_handle *h, int slot) {
             Scope sc(h, nm, 2.0 * B * r * c, 4.0 * (B * r + B * c + (fused ? 2.0 : 1.0) * r * c));
             VB_CUDA(h, run_gemm(h, GEMM_TN, A(i), h->delta[i], r, c, B, e));
         }
-        if (h->dp && !h->dp_fused) {
+        if (h->dp_copy) {
+            // bucket i = dW_i: the copy engines push it into this rank's slot of every peer while the main stream goes on
+            VB_CUDA(h, cudaEventRecord(h->ev_bucket[i], s));
+            VB_CUDA(h, cudaStreamWaitEvent(h->comm_stream, h->ev_bucket[i], 0));
+            VB_TRY(push_to_peers(h->off_w[i], pad64(r * c)));
+        } else if (h->dp && !h->dp_fused) {
             // bucket i = dW_i: reduce on the side stream while the main stream goes on
             VB_CUDA(h, cudaEventRecord(h->ev_bucket[i], s));
             VB_CUDA(h, cudaStreamWaitEvent(h->comm_stream, h->ev_bucket[i], 0));
@@ -474,11 +499,6 @@ int enqueue_step(vb200_handle *h, int slot) {
         VB_CUDA(h, launch_colsum(h->grads + h->off_b[i], h->delta[i], B, c, h->colsum_scratch, s));
         return VB200_OK;
     };
-#define VB_TRY(call)          \
-    do {                      \
-        int _rc = (call);     \
-        if (_rc) return _rc;  \
-    } while (0)
     for (int i = n - 1; i >= 0; --i) {
         const long long r = L[i], c = L[i + 1];
         VB_TRY(do_rows(i));
@@ -492,6 +512,18 @@ int enqueue_step(vb200_handle *h, int slot) {
         VB_TRY(do_dw(i));
         VB_TRY(do_db(i));
         if (!fused) VB_TRY(do_dx(i));
+        if (h->dp_copy) {
+            // bucket i, on the side stream: once this rank is past dX_i (nothing reads W_i any more) and a barrier
+            // shows that every rank's push of the bucket has landed, add the copies and update W_i
+            VB_CUDA(h, cudaEventRecord(h->ev_dx[i], s));
+            VB_CUDA(h, cudaStreamWaitEvent(h->comm_stream, h->ev_dx[i], 0));
+            h->kernels_per_step += 2;
+            VB_CUDA(h, launch_dp_barrier(h->peers, h->off_flags, h->world, h->rank, h->scalars, (unsigned)(n + 2),
+                                         (unsigned)(n - i), h->status_word, h->wait_ns, h->comm_stream));
+            VB_CUDA(h, launch_dp_gather_update(h->cfg.optimizer, h->params, h->s1, h->s2, h->grads, h->recv, h->recv_slot_floats,
+                                               h->off_w[i], pad64(r * c), h->n_weights_padded, h->world, h->rank, h->scalars,
+                                               -1, h->status_word, h->comm_stream));
+        }
         if (h->dp_fused) {
             // bucket i over peer memory, on the side stream: once EVERY rank is past dX_i (nobody reads
             // W_i any more, every dW_i is final) reduce + update + redistribute W_i in one kernel
@@ -552,7 +584,29 @@ int enqueue_step(vb200_handle *h, int slot) {
         VB_CUDA(h, cudaEventRecord(h->ev_join, h->comm_stream));
         VB_CUDA(h, cudaStreamWaitEvent(s, h->ev_join, 0));
     }
-    if (h->dp && !h->dp_fused) {
+    if (h->dp_copy) {
+        // last bucket: every bias gradient and the loss sum; then one barrier so that no rank starts the next
+        // step's pushes while another still reads its receive slots
+        VB_CUDA(h, cudaEventRecord(h->ev_bucket[n], s));
+        VB_CUDA(h, cudaStreamWaitEvent(h->comm_stream, h->ev_bucket[n], 0));
+        const long long nb = h->n_params_padded - h->n_weights_padded;
+        {
+            int rc = push_to_peers(h->n_weights_padded, nb + 64);
+            if (rc) return rc;
+        }
+        h->kernels_per_step += 3;
+        VB_CUDA(h, launch_dp_barrier(h->peers, h->off_flags, h->world, h->rank, h->scalars, (unsigned)(n + 2),
+                                     (unsigned)(n + 1), h->status_word, h->wait_ns, h->comm_stream));
+        VB_CUDA(h, launch_dp_gather_update(h->cfg.optimizer, h->params, h->s1, h->s2, h->grads, h->recv, h->recv_slot_floats,
+                                           h->n_weights_padded, nb, h->n_weights_padded, h->world, h->rank, h->scalars,
+                                           h->n_params_padded, h->status_word, h->comm_stream));
+        VB_CUDA(h, launch_dp_barrier(h->peers, h->off_flags, h->world, h->rank, h->scalars, (unsigned)(n + 2),
+                                     (unsigned)(n + 2), h->status_word, h->wait_ns, h->comm_stream));
+        VB_CUDA(h, cudaEventRecord(h->ev_join, h->comm_stream));
+        Scope sc(h, "wait_for_gradient_exchange", 0.0, 0.0, false);
+        VB_CUDA(h, cudaStreamWaitEvent(s, h->ev_join, 0));
+    }
+    if (h->dp && !h->dp_fused && !h->dp_copy) {
         // last bucket: every bias gradient plus the loss sum, contiguous behind the weights
         VB_CUDA(h, cudaEventRecord(h->ev_bucket[n], s));
         VB_CUDA(h, cudaStreamWaitEvent(h->comm_stream, h->ev_bucket[n], 0));
@@ -569,8 +623,8 @@ int enqueue_step(vb200_handle *h, int slot) {
     {
         const int opt = h->cfg.optimizer;
         double bpp = opt == VB200_OPT_SGD ? 12.0 : (opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW) ? 28.0 : 20.0;
-        if (h->dp_fused) {
-            // every parameter was updated by its owner rank inside the bucket kernels
+        if (h->dp_fused || h->dp_copy) {
+            // every parameter was updated inside the bucket kernels
         } else if (h->fuse_sgd) {
             // weights of every layer wider than one were updated by their dW GEMM; the rest follows here
             for (int i = 0; i < n; ++i)
@@ -777,6 +831,7 @@ void destroy(vb200_handle *h) {
     for (int q = 0; q < 2; ++q)
         if (h->ev_clip[q]) cudaEventDestroy(h->ev_clip[q]);
     for (auto e : h->ev_bucket) cudaEventDestroy(e);
+    for (auto e : h->ev_dx) cudaEventDestroy(e);
     for (void *m : h->peer_mappings) cudaIpcCloseMemHandle(m);
     if (h->arena) cudaFree(h->arena);
     if (h->mirror_params) cudaFreeHost(h->mirror_params);
@@ -811,11 +866,12 @@ int validate(const vb200_config *c, std::string *why) {
     if (c->device_wait_ms < 0) { *why = "device_wait_ms must not be negative"; return VB200_ERR_INVALID; }
     if (c->check_finite != 0 && c->check_finite != 1) { *why = "check_finite must be 0 or 1"; return VB200_ERR_INVALID; }
     if (c->step_kernel < 0 || c->step_kernel > 2) { *why = "step_kernel must be 0, 1 or 2"; return VB200_ERR_INVALID; }
+    if (c->dp_exchange < VB200_DP_NCCL || c->dp_exchange > VB200_DP_PEER_COPY) { *why = "unknown dp_exchange"; return VB200_ERR_INVALID; }
     return VB200_OK;
 }
 
 struct PlanIdx {
-    int params, grads, s1, s2, sc, mse, cs, gs, x[2], y[2], ln = -1;
+    int params, grads, s1, s2, sc, mse, cs, gs, x[2], y[2], ln = -1, recv = -1;
     std::vector<int> act, pre, delta, ln_is, mask;
     int64_t ln_floats = 0;
     std::vector<int64_t> off_ln;
@@ -854,6 +910,9 @@ void make_plan(const vb200_config &c, ArenaPlan &pl, PlanIdx &ix, std::vector<in
     ix.s1 = pl.add("opt_state1", has1 ? P * 4 : 4, 0, end, true);
     ix.s2 = pl.add("opt_state2", has2 ? P * 4 : 4, 0, end, true);
     ix.sc = pl.add("scalars+status", 1024, 0, end, true);
+    // exchange by copy: rank q's copy engines write its gradients (and loss sum) into slot q
+    if (c.dp_exchange == VB200_DP_PEER_COPY && (c.world_size > 1 || c.force_dp == 1))
+        ix.recv = pl.add("dp_receive_slots", (int64_t)(c.world_size > 1 ? c.world_size : 1) * (P + 64) * 4, 0, end, true);
     long long mse = std::max<long long>(loss_blocks((long long)B * L[n]), 256);   // >= one loss partial per CTA of the persistent step
     if (clip) {  // block partials of every delta's sum of squares
         long long all = 0;
@@ -998,6 +1057,11 @@ int build(vb200_handle *h) {
         if (ms > 0) h->wait_ns = (unsigned long long)ms * 1000000ull;
     }
     h->off_loss = h->off_grads + P * 4;
+    if (ix.recv >= 0) {
+        h->recv = at(ix.recv);
+        h->off_recv = pl.offset(ix.recv);
+        h->recv_slot_floats = P + 64;
+    }
 
     for (int s = 0; s < 2; ++s) { h->xin[s] = at(i_x[s]); h->yin[s] = at(i_y[s]); }
     h->act.assign(n + 1, nullptr);
@@ -1040,6 +1104,8 @@ int build(vb200_handle *h) {
         for (int q = 0; q < 2; ++q) VB_CUDA(h, cudaEventCreateWithFlags(&h->ev_clip[q], cudaEventDisableTiming));
         h->ev_bucket.resize(n + 1);
         for (auto &ev : h->ev_bucket) VB_CUDA(h, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        h->ev_dx.resize(n);
+        for (auto &ev : h->ev_dx) VB_CUDA(h, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
         h->dp = new DpComm();
         if (h->dp->init(c.nccl_unique_id, h->world, h->rank)) return h->fail(VB200_ERR_NCCL, h->dp->error());
         // NCCL sets up its channels and peer connections on the first collective (allocations and
@@ -1757,7 +1823,9 @@ int volta_b200_dp_attach_peers(vb200_handle *h, const uint8_t *handles, int32_t 
     if (!h->dp) return h->reject(VB200_ERR_INVALID, "attach_peers: the handle was not created for data parallelism");
     if (count != h->world || count > kMaxPeers || !handles)
         return h->reject(VB200_ERR_INVALID, "attach_peers: need one 64-byte handle per rank (at most 8 ranks)");
-    if (h->dp_fused) return h->reject(VB200_ERR_INVALID, "attach_peers: already attached");
+    if (h->dp_fused || h->dp_copy) return h->reject(VB200_ERR_INVALID, "attach_peers: already attached");
+    const bool by_copy = h->cfg.dp_exchange == VB200_DP_PEER_COPY;
+    if (by_copy && !h->recv) return h->reject(VB200_ERR_INVALID, "attach_peers: the handle has no receive slots");
     if (h->layernorm || h->clip > 0.0f)
         return h->reject(VB200_ERR_UNSUPPORTED, "attach_peers: LayerNorm and the clip need the NCCL data-parallel path");
     VB_CUDA(h, cudaStreamSynchronize(h->stream));
@@ -1779,7 +1847,7 @@ int volta_b200_dp_attach_peers(vb200_handle *h, const uint8_t *handles, int32_t 
             cudaGraphExecDestroy(h->graph[sl]);
             h->graph[sl] = nullptr;
         }
-    h->dp_fused = true;
+    (by_copy ? h->dp_copy : h->dp_fused) = true;
     if (h->use_graph) {
         int rc = capture_graphs(h);
         if (rc) return rc;
@@ -1791,7 +1859,7 @@ int volta_b200_dp_wait_selftest(vb200_handle *h, int32_t declared_world, int32_t
     if (!h) return VB200_ERR_INVALID;
     if (declared_world < 2 || declared_world > kMaxPeers || wait_ms <= 0 || wait_ms > 10000)
         return h->reject(VB200_ERR_INVALID, "dp_wait_selftest: world must lie in 2..8 and wait_ms in 1..10000");
-    if (h->dp_fused) return h->reject(VB200_ERR_INVALID, "dp_wait_selftest: not on a handle attached to peers");
+    if (h->dp_fused || h->dp_copy) return h->reject(VB200_ERR_INVALID, "dp_wait_selftest: not on a handle attached to peers");
     // every "peer" is this handle's own arena: slot 0 of the flag words gets written, the others never do
     PeerTable self{};
     for (int q = 0; q < kMaxPeers; ++q) self.base[q] = h->arena;

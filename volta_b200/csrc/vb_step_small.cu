@@ -37,6 +37,8 @@
 // (src/engine/ir/codegen/inner.rs:183-406) for up to 64 rows in one launch.
 #include <cooperative_groups.h>
 
+#include <type_traits>
+
 #include "vb_common.cuh"
 #include "vb_optimizer.cuh"
 
@@ -427,9 +429,9 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                 const float *ds = bufA + (t & 1) * BUF_A, *ws = bufB + (t & 1) * BUF_B;
                 const int nb = n0 + t * KT, nn = min(KT, n0 + nlen - nb);
                 // ---- bias gradient: of the NA clusters that own rows of this W, cluster j takes the tile's columns
-                // j, j + NA, ... (all of them hold the same delta tile); warp 0 sums a column's rows on a fixed
-                // tree (lane l: rows l and l + 32, then shuffles), lane i applies the update for the i-th column
-                // (the parameter and its state are asked for here and used at the end of the tile)
+                // j, j + NA, ... (all of them hold the same delta tile).  The sums are taken by warp 0 behind its first
+                // block of products (lane l: columns 4l .. 4l+3, rows ascending); the parameter and its state are asked
+                // for there and used at the end of the tile.
                 float db_g = 0.0f, db_p = 0.0f, db_s1 = 0.0f, db_s2 = 0.0f;
                 long long db_e = -1;
                 auto db_finish = [&]() {
@@ -439,41 +441,27 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                     if (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW) A.s2[db_e] = db_s2;
                     A.grads[db_e] = db_g;
                 };
-                if (tid < 32) {
-                    const int NA = ceil_div(r, kcl);   // clusters with krows > 0
-                    for (int i = 0, col = j; col < nn; ++i, col += NA) {
-                        float v = ds[tid * LD + col] + ds[(tid + 32) * LD + col];
-#pragma unroll
-                        for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                        if ((i & 31) == tid) {
-                            if (db_e >= 0) db_finish();   // more than 32 columns for this cluster: finish the earlier one first
-                            db_g = v;
-                            db_e = L.off_b + nb + col;
-                            db_p = A.params[db_e];
-                            if (OPT != VB200_OPT_SGD) db_s1 = __ldcs(A.s1 + db_e);
-                            if (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW) db_s2 = __ldcs(A.s2 + db_e);
-                        }
-                    }
-                }
-                // ---- dW block = act^T . delta (sum over the batch, ascending), then the optimizer on it
-                {
-                    const int ng = tid & 31, kgp = tid >> 5;     // 4 columns 4*ng.., 4 rows kgp*4 + 32*pass ..
-                    for (int pass = 0; pass * 32 < kcl; ++pass) {
-                        const int kk0 = kgp * 4 + 32 * pass;
+                // ---- dW block = act^T . delta (sum over the batch, ascending), then the optimizer on it.  A thread
+                // owns 4 columns and RPT rows of the block; RPT shrinks with the slab so that all eight warps have rows.
+                auto dw_block = [&](auto rpt_tag) {
+                    constexpr int RPT = decltype(rpt_tag)::value;
+                    const int ng = tid & 31, kgp = tid >> 5;     // columns 4*ng .., rows kgp*RPT + 8*RPT*pass ..
+                    for (int pass = 0; pass * 8 * RPT < kcl; ++pass) {
+                        const int kk0 = kgp * RPT + 8 * RPT * pass;
                         if (kk0 >= kcl) break;
-                        float g[4][4];
+                        float g[RPT][4];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i)
+                        for (int i = 0; i < RPT; ++i)
 #pragma unroll
                             for (int u = 0; u < 4; ++u) g[i][u] = 0.0f;
-                        // optimizer state of the four rows, asked for before the products so that its latency
+                        // optimizer state of the rows, asked for before the products so that its latency
                         // hides behind them (the weights themselves sit in the shared-memory tile)
                         constexpr bool HAS1 = (OPT != VB200_OPT_SGD);
                         constexpr bool HAS2 = (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW);
                         const bool vec = (c & 3) == 0 && 4 * ng + 3 < nn;   // offsets and n0, nb are multiples of 4
-                        float4 st1[4], st2[4];
+                        float4 st1[RPT], st2[RPT];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
+                        for (int i = 0; i < RPT; ++i) {
                             st1[i] = st2[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                             if (vec && kk0 + i < krows) {
                                 const long long e = L.off_w + (long long)(k0 + kk0 + i) * c + nb + 4 * ng;
@@ -483,44 +471,76 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                         }
 #pragma unroll 4
                         for (int b = 0; b < B; ++b) {
-                            const float4 av = *reinterpret_cast<const float4 *>(actc + b * LDW + kk0);
+                            float a4[RPT];
+                            if (RPT == 4) {
+                                const float4 av = *reinterpret_cast<const float4 *>(actc + b * LDW + kk0);
+                                a4[0] = av.x; a4[RPT > 1 ? 1 : 0] = av.y; a4[RPT > 2 ? 2 : 0] = av.z; a4[RPT > 3 ? 3 : 0] = av.w;
+                            } else if (RPT == 2) {
+                                const float2 av = *reinterpret_cast<const float2 *>(actc + b * LDW + kk0);
+                                a4[0] = av.x; a4[RPT > 1 ? 1 : 0] = av.y;
+                            } else {
+                                a4[0] = actc[b * LDW + kk0];
+                            }
                             const float4 dv = *reinterpret_cast<const float4 *>(ds + b * LD + 4 * ng);
-                            const float a4[4] = {av.x, av.y, av.z, av.w};
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
+                            for (int i = 0; i < RPT; ++i) {
                                 g[i][0] = fmaf(a4[i], dv.x, g[i][0]);
                                 g[i][1] = fmaf(a4[i], dv.y, g[i][1]);
                                 g[i][2] = fmaf(a4[i], dv.z, g[i][2]);
                                 g[i][3] = fmaf(a4[i], dv.w, g[i][3]);
                             }
                         }
+                        if (kgp == 0 && pass == 0) {
+                            float cs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 8
+                            for (int b = 0; b < B; ++b) {
+                                const float4 dv = *reinterpret_cast<const float4 *>(ds + b * LD + 4 * ng);
+                                cs[0] += dv.x; cs[1] += dv.y; cs[2] += dv.z; cs[3] += dv.w;
+                            }
+                            const int NA = ceil_div(r, kcl);   // clusters with krows > 0
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                const int col = 4 * ng + u;
+                                if (col < nn && col % NA == j) {
+                                    if (db_e >= 0) db_finish();   // NA < 4: more than one column for this lane
+                                    db_g = cs[u];
+                                    db_e = L.off_b + nb + col;
+                                    db_p = A.params[db_e];
+                                    if (OPT != VB200_OPT_SGD) db_s1 = __ldcs(A.s1 + db_e);
+                                    if (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW) db_s2 = __ldcs(A.s2 + db_e);
+                                }
+                            }
+                        }
                         const float wd = OPT == VB200_OPT_ADAMW ? sc.weight_decay : 0.0f;
                         if (c == 1) {
-                            // a width-one layer's W is a column: this thread's four rows are four consecutive floats
-                            // (k0 and kk0 are multiples of 4), updated as one group where all four exist
+                            // a width-one layer's W is a column: this thread's rows are consecutive floats, updated
+                            // as one group of four where all four exist (k0 and kk0 are then multiples of 4)
                             if (ng == 0 && kk0 < krows) {
                                 const long long e = L.off_w + k0 + kk0;
-                                if (kk0 + 3 < krows) {
+                                if (RPT == 4 && kk0 + 3 < krows) {
                                     float4 pv = *reinterpret_cast<const float4 *>(A.params + e);
                                     float4 a1 = HAS1 ? __ldcs(reinterpret_cast<const float4 *>(A.s1 + e)) : make_float4(0, 0, 0, 0);
                                     float4 a2 = HAS2 ? __ldcs(reinterpret_cast<const float4 *>(A.s2 + e)) : make_float4(0, 0, 0, 0);
                                     update_one<OPT>(pv.x, a1.x, a2.x, g[0][0], sc, wd);
-                                    update_one<OPT>(pv.y, a1.y, a2.y, g[1][0], sc, wd);
-                                    update_one<OPT>(pv.z, a1.z, a2.z, g[2][0], sc, wd);
-                                    update_one<OPT>(pv.w, a1.w, a2.w, g[3][0], sc, wd);
+                                    update_one<OPT>(pv.y, a1.y, a2.y, g[RPT > 1 ? 1 : 0][0], sc, wd);
+                                    update_one<OPT>(pv.z, a1.z, a2.z, g[RPT > 2 ? 2 : 0][0], sc, wd);
+                                    update_one<OPT>(pv.w, a1.w, a2.w, g[RPT > 3 ? 3 : 0][0], sc, wd);
                                     *reinterpret_cast<float4 *>(A.params + e) = pv;
                                     if (HAS1) *reinterpret_cast<float4 *>(A.s1 + e) = a1;
                                     if (HAS2) *reinterpret_cast<float4 *>(A.s2 + e) = a2;
-                                    *reinterpret_cast<float4 *>(A.grads + e) = make_float4(g[0][0], g[1][0], g[2][0], g[3][0]);
+                                    *reinterpret_cast<float4 *>(A.grads + e) =
+                                        make_float4(g[0][0], g[RPT > 1 ? 1 : 0][0], g[RPT > 2 ? 2 : 0][0], g[RPT > 3 ? 3 : 0][0]);
                                 } else {
-                                    for (int i = 0; kk0 + i < krows; ++i)
-                                        update_elem<OPT>(A.params + e + i, A.s1 + e + i, A.s2 + e + i, A.grads + e + i, g[i][0], sc, wd);
+#pragma unroll
+                                    for (int i = 0; i < RPT; ++i)
+                                        if (kk0 + i < krows)
+                                            update_elem<OPT>(A.params + e + i, A.s1 + e + i, A.s2 + e + i, A.grads + e + i, g[i][0], sc, wd);
                                 }
                             }
                             continue;
                         }
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
+                        for (int i = 0; i < RPT; ++i) {
                             const int kk = kk0 + i;
                             if (kk >= krows) continue;
                             const long long e = L.off_w + (long long)(k0 + kk) * c + nb + 4 * ng;
@@ -542,7 +562,10 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                             }
                         }
                     }
-                }
+                };
+                if (kcl > 16) dw_block(std::integral_constant<int, 4>{});
+                else if (kcl > 8) dw_block(std::integral_constant<int, 2>{});
+                else dw_block(std::integral_constant<int, 1>{});
                 // ---- partial of dX = delta . W^T over this tile's columns, from the pre-update W in shared memory
                 if (need_dx && tm.active) {
                     const int seg = KT / tm.KG, nbeg = tm.kg * seg;

@@ -22,7 +22,7 @@ class Config(C.Structure):
         ("weight_decay", C.c_float), ("gemm_path", C.c_int32), ("use_graph", C.c_int32),
         ("force_dp", C.c_int32), ("fuse_sgd", C.c_int32), ("use_layernorm", C.c_int32), ("dropout_p", C.c_float),
         ("clip_grad", C.c_float), ("device_wait_ms", C.c_int32), ("check_finite", C.c_int32),
-        ("step_kernel", C.c_int32),
+        ("step_kernel", C.c_int32), ("dp_exchange", C.c_int32),
     ]
 
 

@@ -19,6 +19,7 @@ ACTIVATIONS = {"relu": 0, "sigmoid": 1, "tanh": 2, "leaky_relu": 3, "leakyrelu":
                "": 0}
 OPTIMIZERS = {"sgd": 0, "adam": 1, "adamw": 2, "adagrad": 3, "sgd_momentum": 4}
 GEMM_PATHS = {"auto": 0, "ffma": 1, "tensor": 2, "tensor_pair": 3}
+DP_EXCHANGE = {"nccl": 0, "peer_kernel": 1, "peer_copy": 2}
 
 
 def _ptr(a):
@@ -54,7 +55,7 @@ class TrainHandle:
     def __init__(self, layers, activation="relu", optimizer="sgd", batch=1, *, global_batch=0, world_size=1, rank=0,
                  unique_id: bytes | None = None, momentum=0.0, weight_decay=0.0, gemm_path="auto", use_graph=True,
                  force_dp=False, fuse_sgd=False, dropout_p=0.0, use_layernorm=False, clip_grad=0.0, device_wait_ms=0,
-                 check_finite=False, step_kernel=0):
+                 check_finite=False, step_kernel=0, dp_exchange="nccl"):
         act = activation.lower()
         opt = optimizer.lower()
         if act not in ACTIVATIONS:
@@ -95,6 +96,8 @@ class TrainHandle:
         cfg.device_wait_ms = int(device_wait_ms)
         cfg.check_finite = 1 if check_finite else 0
         cfg.step_kernel = int(step_kernel)   # 0 auto, 1 per-kernel schedule, 2 require the persistent step kernel
+        # what attach_peers switches the exchange to: "nccl"/"peer_kernel" (the fused kernel) or "peer_copy"
+        cfg.dp_exchange = DP_EXCHANGE[dp_exchange]
         self.dropout_p = float(dropout_p)
         self._cfg = cfg
         h = C.c_void_p()
