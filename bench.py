@@ -53,10 +53,10 @@ def measured_peaks():
 # CTA-pair GEMM at configuration 4's widths, captured at batch 8192; the traffic of these GEMMs grows
 # in proportion to the batch, so a full launch is rows x this figure.
 NCU_TRAFFIC_PER_ROW = {
-    "fwd_gemm_nn_Bx4096x4096": (620.196096e6 + 245.701376e6) / 8192,
+    "fwd_gemm_nn_Bx4096x4096": (620.370688e6 + 246.531584e6) / 8192,
     "fwd_gemm_nn_Bx1024x4096": (200.767232e6 + 44.852224e6) / 8192,
-    "dX_gemm_nt_Bx4096x4096": (754.354176e6 + 131.911168e6) / 8192,
-    "dW_gemm_tn_4096x4096xB": (628.525824e6 + 67.879424e6) / 8192,
+    "dX_gemm_nt_Bx4096x4096": (754.393088e6 + 131.598336e6) / 8192,
+    "dW_gemm_tn_4096x4096xB": (615.041280e6 + 130.149376e6) / 8192,   # K split in two: two slabs written
 }
 
 

@@ -16,6 +16,16 @@
 // every reduce-update kernel of the handle returns at once without reading or writing any rank's
 // memory - a missing rank neither hangs the GPU nor gets a partial sum applied, and the host
 // refuses further steps with VB200_ERR_DEVICE_WAIT.
+//
+// Exchange by copy (dp_gather_update_kernel, the handle's dp_exchange = VB200_DP_PEER_COPY): the same flag
+// barriers, but the gradients travel by the copy engines - the host side enqueues, per layer bucket, one
+// device-to-device copy of the bucket into this rank's receive slot in every peer's arena as soon as dW exists,
+// so that no SM is taken from the backward GEMMs that run meanwhile (a collective kernel that holds an SM for
+// the length of its transfer also blocks that SM's partner for the CTA-pair GEMM).  After the bucket's
+// barrier every rank holds all N copies locally; one streaming kernel adds them in rank order 0..N-1, stores
+// the sum as the gradient and applies the optimizer to the whole bucket: every rank keeps full optimizer
+// state and identical parameters without a second transfer.  N-1 times the gradient bytes cross NVLink per
+// rank instead of 2(N-1)/N, all of it underneath the backward pass.
 // The reference has no collective of any kind; parity target is the full-batch CPU oracle.
 #include "vb_common.cuh"
 #include "vb_optimizer.cuh"
