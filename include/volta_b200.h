@@ -122,7 +122,9 @@ void volta_b200_destroy(vb200_handle *h);
  * X is [batch x L0], Y is [batch x Ln], row-major fp32; each may be a host pointer
  * (pageable or pinned; copied to the device inside the call) or a device pointer.
  * The call returns once X and Y have been consumed from host memory; the step itself
- * completes asynchronously on the handle's stream. */
+ * completes asynchronously on the handle's stream.  A host X of at least 64 MB travels in 2-8 row chunks
+ * of at least 8192 rows, and the forward pass of a chunk starts as soon as it has landed, so that only the
+ * first chunk's copy is exposed (VOLTA_B200_IN_CHUNKS=1 switches that off). */
 int volta_b200_step(vb200_handle *h, const float *X, const float *Y, float lr);
 
 /* volta_train_loss (mlp_train_rust_codegen.rs:686): loss of the last step (computed

@@ -100,6 +100,15 @@ struct vb200_handle {
     cudaEvent_t ev_join = nullptr;
     std::vector<cudaEvent_t> ev_bucket;
     cudaGraphExec_t graph[2] = {nullptr, nullptr};
+    // Large HOST inputs: the rows arrive in `in_chunks` copies, and the forward pass (row-independent) runs as one
+    // captured graph per chunk as soon as that chunk has landed, followed by the graph of the rest of the step
+    static constexpr int kMaxInChunks = 8;
+    int in_chunks = 1;
+    bool chunked_now = false;     // the step being enqueued takes the chunked path
+    bool profiling_next = false;  // the step being enqueued is a profiled one (plain launches, whole forward)
+    cudaGraphExec_t graph_fwd[2][kMaxInChunks] = {};
+    cudaGraphExec_t graph_rest[2] = {nullptr, nullptr};
+    cudaEvent_t ev_chunk[2][kMaxInChunks] = {};
     // inference: pinned staging for host callers and one captured forward graph per row count
     float *infer_in = nullptr, *infer_out = nullptr;
     std::map<long long, cudaGraphExec_t> infer_graphs;
@@ -225,14 +234,15 @@ int enqueue_small_step(vb200_handle *h, int slot, int rows = 0);
 // Forward pass over the first `rows` rows of input slot `slot` (rows <= batch): every layer's GEMM
 // with bias and activation fused.  Used by the training step (rows = batch) and by inference.
 int enqueue_forward(vb200_handle *h, int slot, long long rows, bool training, const float *in_override = nullptr,
-                    float *out_override = nullptr) {
+                    float *out_override = nullptr, long long row0 = 0) {
     const int n = h->n, act = h->cfg.activation;
     const long long B = rows;
     const std::vector<int> &L = h->L;
     cudaStream_t s = h->stream;
-    const float *act0 = in_override ? in_override : h->xin[slot];
-    float *const last_out = out_override ? out_override : h->act[n];
-    auto A = [&](int i) -> float * { return i == 0 ? const_cast<float *>(act0) : h->act[i]; };
+    // row0 > 0: rows [row0, row0 + rows) of the batch (plain layers only: no row stage keeps per-row state)
+    const float *act0 = (in_override ? in_override : h->xin[slot]) + row0 * L[0];
+    float *const last_out = (out_override ? out_override : h->act[n]) + row0 * L[n];
+    auto A = [&](int i) -> float * { return i == 0 ? const_cast<float *>(act0) : h->act[i] + row0 * L[i]; };
     char nm[64];
     // inference of 9..64 rows: the persistent kernel's forward half, one launch (fewer rows take the
     // cluster kernel below, layer by layer, straight from and to pinned memory)
@@ -253,11 +263,11 @@ int enqueue_forward(vb200_handle *h, int slot, long long rows, bool training, co
             e.out0 = last_out;
         } else if (act == VB200_ACT_SOFTMAX) {
             e.mode = EPI_BIAS;  // the row kernel below turns the pre-activations into their softmax in place
-            e.out0 = h->act[i + 1];
+            e.out0 = h->act[i + 1] + row0 * c;
         } else {
             e.mode = EPI_BIAS_ACT;
-            e.out0 = h->act[i + 1];
-            e.out1 = h->keep_pre ? h->pre[i] : nullptr;
+            e.out0 = h->act[i + 1] + row0 * c;
+            e.out1 = h->keep_pre ? h->pre[i] + row0 * c : nullptr;
         }
         if (i == n - 1 && c == 1) {
             // width-one output layer: a row-dot, bandwidth-bound on act_i
@@ -364,7 +374,8 @@ int enqueue_small_step(vb200_handle *h, int slot, int rows) {
     return rows > 0 ? VB200_OK : enqueue_step_tail(h, slot);
 }
 
-int enqueue_step(vb200_handle *h, int slot) {
+// skip_forward: the forward pass has been enqueued already (in row chunks, see in_chunks).
+int enqueue_step(vb200_handle *h, int slot, bool skip_forward = false) {
     if (h->small_step) return enqueue_small_step(h, slot);
     const int n = h->n, B = h->B, act = h->cfg.activation;
     const std::vector<int> &L = h->L;
@@ -374,7 +385,7 @@ int enqueue_step(vb200_handle *h, int slot) {
     auto A = [&](int i) -> float * { return i == 0 ? const_cast<float *>(act0) : h->act[i]; };
     char nm[64];
 
-    {
+    if (!skip_forward) {
         int rc = enqueue_forward(h, slot, B, true);
         if (rc) return rc;
     }
@@ -654,20 +665,50 @@ int enqueue_step(vb200_handle *h, int slot) {
     return enqueue_step_tail(h, slot);
 }
 
+void destroy_step_graphs(vb200_handle *h) {
+    for (int s = 0; s < 2; ++s) {
+        if (h->graph[s]) cudaGraphExecDestroy(h->graph[s]);
+        if (h->graph_rest[s]) cudaGraphExecDestroy(h->graph_rest[s]);
+        h->graph[s] = h->graph_rest[s] = nullptr;
+        for (int c = 0; c < vb200_handle::kMaxInChunks; ++c) {
+            if (h->graph_fwd[s][c]) cudaGraphExecDestroy(h->graph_fwd[s][c]);
+            h->graph_fwd[s][c] = nullptr;
+        }
+    }
+}
+
+// Captures what `body` enqueues on the handle's stream into an executable graph.
+template <class Body>
+int capture_one(vb200_handle *h, cudaGraphExec_t *out, Body body) {
+    cudaGraph_t g = nullptr;
+    VB_CUDA(h, cudaStreamBeginCapture(h->stream, cudaStreamCaptureModeThreadLocal));
+    int rc = body();
+    cudaError_t e = cudaStreamEndCapture(h->stream, &g);
+    if (rc) {
+        if (g) cudaGraphDestroy(g);
+        return rc;
+    }
+    if (e != cudaSuccess) return h->fail(VB200_ERR_CUDA, std::string("cudaStreamEndCapture: ") + cudaGetErrorString(e));
+    e = cudaGraphInstantiate(out, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return h->fail(VB200_ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
+    return VB200_OK;
+}
+
 int capture_graphs(vb200_handle *h) {
     for (int slot = 0; slot < 2; ++slot) {
-        cudaGraph_t g = nullptr;
-        VB_CUDA(h, cudaStreamBeginCapture(h->stream, cudaStreamCaptureModeThreadLocal));
-        int rc = enqueue_step(h, slot);
-        cudaError_t e = cudaStreamEndCapture(h->stream, &g);
-        if (rc) {
-            if (g) cudaGraphDestroy(g);
-            return rc;
+        if (h->in_chunks > 1) {
+            // host inputs: one graph per row chunk of the forward pass, one for the rest of the step
+            const long long rows = h->B / h->in_chunks;
+            for (int c = 0; c < h->in_chunks; ++c) {
+                int rc = capture_one(h, &h->graph_fwd[slot][c], [&] { return enqueue_forward(h, slot, rows, true, nullptr, nullptr, c * rows); });
+                if (rc) return rc;
+            }
+            int rc = capture_one(h, &h->graph_rest[slot], [&] { return enqueue_step(h, slot, true); });
+            if (rc) return rc;
         }
-        if (e != cudaSuccess) return h->fail(VB200_ERR_CUDA, std::string("cudaStreamEndCapture: ") + cudaGetErrorString(e));
-        e = cudaGraphInstantiate(&h->graph[slot], g, 0);
-        cudaGraphDestroy(g);
-        if (e != cudaSuccess) return h->fail(VB200_ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
+        int rc = capture_one(h, &h->graph[slot], [&] { return enqueue_step(h, slot); });
+        if (rc) return rc;
     }
     return VB200_OK;
 }
@@ -707,9 +748,24 @@ int copy_inputs(vb200_handle *h, int slot, const float *X, const float *Y, bool 
     h->ss_x = (h->small_step && xdev) ? X : nullptr;
     h->ss_y = (h->small_step && ydev) ? Y : nullptr;
     *host_wait = !(xdev && ydev);
+    h->chunked_now = h->in_chunks > 1 && !xdev && h->graph_rest[slot] != nullptr && !h->profiling_next;
     if (h->ss_x && h->ss_y) return VB200_OK;
     // the slot is free once the step that last read it has finished
     VB_CUDA(h, cudaStreamWaitEvent(h->copy_stream, h->ev_slot_free[slot], 0));
+    if (h->chunked_now) {
+        // Y first (small), then X in row chunks with an event behind each: the forward graph of a chunk starts
+        // as soon as its rows have landed, while the later chunks are still on their way
+        VB_CUDA(h, cudaMemcpyAsync(h->yin[slot], Y, yb, ydev ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice,
+                                   h->copy_stream));
+        const size_t cb = xb / (size_t)h->in_chunks;
+        for (int c = 0; c < h->in_chunks; ++c) {
+            VB_CUDA(h, cudaMemcpyAsync(reinterpret_cast<char *>(h->xin[slot]) + c * cb, reinterpret_cast<const char *>(X) + c * cb,
+                                       cb, cudaMemcpyHostToDevice, h->copy_stream));
+            VB_CUDA(h, cudaEventRecord(h->ev_chunk[slot][c], h->copy_stream));
+        }
+        VB_CUDA(h, cudaEventRecord(h->ev_copied[slot], h->copy_stream));
+        return VB200_OK;
+    }
     if (!h->ss_x)
         VB_CUDA(h, cudaMemcpyAsync(h->xin[slot], X, xb, xdev ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice,
                                    h->copy_stream));
@@ -775,7 +831,9 @@ int do_step(vb200_handle *h, const float *X, const float *Y, float lr, bool prof
     }
     const int slot = profile ? 0 : (int)(h->steps_done & 1);
     bool host_wait = false;
+    h->profiling_next = profile;
     int rc = copy_inputs(h, slot, X, Y, &host_wait);
+    h->profiling_next = false;
     if (rc) return rc;
     const int opt = h->cfg.optimizer;
     if (opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW) h->adam_step += 1;
@@ -789,6 +847,13 @@ int do_step(vb200_handle *h, const float *X, const float *Y, float lr, bool prof
         rc = enqueue_step(h, slot);
         h->profiling = false;
         if (rc) return rc;
+    } else if (h->chunked_now) {
+        for (int c = 0; c < h->in_chunks; ++c) {
+            VB_CUDA(h, cudaStreamWaitEvent(h->stream, h->ev_chunk[slot][c], 0));
+            VB_CUDA(h, cudaGraphLaunch(h->graph_fwd[slot][c], h->stream));
+        }
+        VB_CUDA(h, cudaStreamWaitEvent(h->stream, h->ev_copied[slot], 0));
+        VB_CUDA(h, cudaGraphLaunch(h->graph_rest[slot], h->stream));
     } else {
         VB_CUDA(h, cudaGraphLaunch(h->graph[slot], h->stream));
     }
@@ -810,11 +875,7 @@ void destroy(vb200_handle *h) {
     if (h->comm_stream) cudaStreamSynchronize(h->comm_stream);
     // The captured graphs hold references on the communicator (NCCL waits for them in its
     // destroy call), so they must go first.
-    for (int s = 0; s < 2; ++s)
-        if (h->graph[s]) {
-            cudaGraphExecDestroy(h->graph[s]);
-            h->graph[s] = nullptr;
-        }
+    destroy_step_graphs(h);
     for (auto &kv : h->infer_graphs) cudaGraphExecDestroy(kv.second);
     h->infer_graphs.clear();
     if (h->infer_in) cudaFreeHost(h->infer_in);
@@ -832,6 +893,9 @@ void destroy(vb200_handle *h) {
         if (h->ev_clip[q]) cudaEventDestroy(h->ev_clip[q]);
     for (auto e : h->ev_bucket) cudaEventDestroy(e);
     for (auto e : h->ev_dx) cudaEventDestroy(e);
+    for (int s = 0; s < 2; ++s)
+        for (int c = 0; c < vb200_handle::kMaxInChunks; ++c)
+            if (h->ev_chunk[s][c]) cudaEventDestroy(h->ev_chunk[s][c]);
     for (void *m : h->peer_mappings) cudaIpcCloseMemHandle(m);
     if (h->arena) cudaFree(h->arena);
     if (h->mirror_params) cudaFreeHost(h->mirror_params);
@@ -1153,6 +1217,24 @@ int build(vb200_handle *h) {
             h->status = VB200_OK;
             h->error.clear();
         }
+    }
+    // Host inputs of at least 64 MB: copy and forward pass in row chunks of at least 8192 rows (the GEMMs keep
+    // their efficiency at that height), so that only the first chunk's copy is exposed.  VOLTA_B200_IN_CHUNKS=1
+    // switches it off, another value in 2..8 that divides the batch sets the count.
+    if (!h->small_step && h->use_graph && !h->row_opts) {
+        int want = 0;
+        if (const char *e = getenv("VOLTA_B200_IN_CHUNKS")) want = atoi(e);
+        int chunks = 1;
+        if (want >= 2 && want <= vb200_handle::kMaxInChunks && B % want == 0) {
+            chunks = want;
+        } else if (want == 0 && (long long)B * L[0] * 4 >= (64LL << 20)) {
+            for (int cnum = vb200_handle::kMaxInChunks; cnum >= 2; cnum /= 2)
+                if (B % cnum == 0 && B / cnum >= 8192) { chunks = cnum; break; }
+        }
+        h->in_chunks = chunks;
+        if (chunks > 1)
+            for (int sl = 0; sl < 2; ++sl)
+                for (int cc = 0; cc < chunks; ++cc) VB_CUDA(h, cudaEventCreateWithFlags(&h->ev_chunk[sl][cc], cudaEventDisableTiming));
     }
     if (h->small_step) {
         h->kernels_per_step = 1;   // launched directly every step, with the step's scalars as an argument
@@ -1842,11 +1924,7 @@ int volta_b200_dp_attach_peers(vb200_handle *h, const uint8_t *handles, int32_t 
         h->peers.base[q] = static_cast<char *>(p);
     }
     // from now on the step graph uses the peer-memory buckets instead of NCCL + the flat optimizer
-    for (int sl = 0; sl < 2; ++sl)
-        if (h->graph[sl]) {
-            cudaGraphExecDestroy(h->graph[sl]);
-            h->graph[sl] = nullptr;
-        }
+    destroy_step_graphs(h);
     (by_copy ? h->dp_copy : h->dp_fused) = true;
     if (h->use_graph) {
         int rc = capture_graphs(h);
