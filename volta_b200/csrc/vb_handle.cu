@@ -401,6 +401,7 @@ int enqueue_step(vb200_handle *h, int slot, bool skip_forward = false) {
     // the dW epilogue, dX_i (which must read the pre-update W_i) goes first.  With the clip every
     // delta must exist before any dW is taken (:936-955), so the dW GEMMs form a second sweep.
     const bool two_sweeps = h->clip > 0.0f;
+    const bool nccl_bucket_update = h->dp && !h->dp_fused && !h->dp_copy && !two_sweeps && !h->layernorm;
     // LayerNorm backward -> dropout mask -> activation backward on the raw delta of hidden layer i
     auto do_rows = [&](int i) -> int {
         if (!h->row_opts || i == n - 1) return VB200_OK;
@@ -520,9 +521,24 @@ int enqueue_step(vb200_handle *h, int slot, bool skip_forward = false) {
         }
         const bool fused = h->fuse_sgd && c != 1;
         if (fused) VB_TRY(do_dx(i));
+        // the first layer's bias gradient goes ahead of its dW, so that behind the step's last GEMM only that
+        // GEMM's own bucket is left to exchange
+        if (i == 0 && h->dp) VB_TRY(do_db(i));
         VB_TRY(do_dw(i));
-        VB_TRY(do_db(i));
+        if (!(i == 0 && h->dp)) VB_TRY(do_db(i));
         if (!fused) VB_TRY(do_dx(i));
+        if (nccl_bucket_update) {
+            // NCCL buckets: once this rank is past dX_i (nothing reads W_i any more) the bucket's optimizer pass
+            // follows its all-reduce on the side stream, underneath the remaining backward GEMMs
+            const int opt = h->cfg.optimizer;
+            const bool has1 = opt != VB200_OPT_SGD, has2 = opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW;
+            VB_CUDA(h, cudaEventRecord(h->ev_dx[i], s));
+            VB_CUDA(h, cudaStreamWaitEvent(h->comm_stream, h->ev_dx[i], 0));
+            h->kernels_per_step++;
+            VB_CUDA(h, launch_optimizer(opt, h->params + h->off_w[i], has1 ? h->s1 + h->off_w[i] : h->s1,
+                                        has2 ? h->s2 + h->off_w[i] : h->s2, h->grads + h->off_w[i], pad64(r * c), pad64(r * c),
+                                        h->scalars, h->comm_stream));
+        }
         if (h->dp_copy) {
             // bucket i, on the side stream: once this rank is past dX_i (nothing reads W_i any more) and a barrier
             // shows that every rank's push of the bucket has landed, add the copies and update W_i
@@ -648,6 +664,13 @@ int enqueue_step(vb200_handle *h, int slot, bool skip_forward = false) {
             Scope sc(h, "optimizer_bias", 0.0, bpp * nb);
             VB_CUDA(h, launch_optimizer(opt, h->params + h->n_weights_padded, h->s1, h->s2, h->grads + h->n_weights_padded,
                                         nb, 0, h->scalars, s));
+        } else if (nccl_bucket_update) {
+            // the weights were updated bucket by bucket on the side stream; the biases follow here
+            const bool has1 = opt != VB200_OPT_SGD, has2 = opt == VB200_OPT_ADAM || opt == VB200_OPT_ADAMW;
+            const int64_t w = h->n_weights_padded, nb = h->n_params_padded - w;
+            Scope sc(h, "optimizer_bias", 0.0, bpp * nb);
+            VB_CUDA(h, launch_optimizer(opt, h->params + w, has1 ? h->s1 + w : h->s1, has2 ? h->s2 + w : h->s2, h->grads + w, nb, 0,
+                                        h->scalars, s));
         } else {
             Scope sc(h, "optimizer", 0.0, bpp * h->n_params_padded);
             VB_CUDA(h, launch_optimizer(opt, h->params, h->s1, h->s2, h->grads, h->n_params_padded, h->n_weights_padded,
