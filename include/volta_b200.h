@@ -299,6 +299,13 @@ int volta_b200_gemm(int32_t layout, int32_t path, float *C, const float *A, cons
  * assumed 16-byte aligned, as every buffer of a handle is. */
 enum { VB200_ROUTE_FFMA = 0, VB200_ROUTE_TENSOR_SINGLE = 1, VB200_ROUTE_TENSOR_PAIR = 2, VB200_ROUTE_SMALL_ROWS = 3 };
 int volta_b200_gemm_route(int32_t layout, int32_t path, int64_t m, int64_t n, int64_t k, int32_t *splits);
+/* Self-check of the persistent step kernel's optimizer arithmetic (four elements side by side through
+ * straight-line division / square-root cores, with a pre-check that sends a group with extreme operands to the
+ * library routines) against the streaming optimizer's: `groups` seeded groups of four elements at Adam step t,
+ * operands from the range training produces (wide = 0) or from all exponents (wide = 1).  counts[0] = elements
+ * that differ in any bit of parameter or state (must be 0), [1] / [2] = groups that took the cores / the library
+ * path.  optimizer: VB200_OPT_ADAM, _ADAMW or _ADAGRAD.  No counterpart in the reference. */
+int volta_b200_update_selftest(int32_t optimizer, uint64_t seed, int64_t groups, int32_t wide, uint64_t t, uint64_t counts[3]);
 /* out[j] = sum over rows of in[rows x cols] in a fixed order; scratch must hold
  * volta_b200_colsum_scratch_floats(rows, cols) floats. */
 int64_t volta_b200_colsum_scratch_floats(int64_t rows, int64_t cols);

@@ -143,3 +143,29 @@ def test_where_the_kernel_does_not_apply_it_is_refused_or_bypassed():
     g = TrainHandle([32, 32, 1], "relu", "sgd", 8, gemm_path="ffma")           # an explicit GEMM path also means per-kernel
     assert g.kernels_per_step > 1
     g.free()
+
+
+@pytest.mark.parametrize("opt", ["adam", "adamw", "adagrad"])
+@pytest.mark.parametrize("wide", [0, 1])
+def test_step_kernel_optimizer_arithmetic_equals_the_streaming_optimizers(opt, wide):
+    """The persistent kernel runs its elements side by side through straight-line division / square-root cores
+    (vb_optimizer.cuh) where the streaming optimizer calls the library's IEEE routines.  Bit for bit the same, on
+    operands from the range training produces (nearly all groups take the cores) and on operands from all
+    exponents (most groups fail the pre-check and take the library path; those at the edges of the cores' range
+    do not)."""
+    import ctypes as C
+    from volta_b200 import load_library
+    lib = load_library()
+    code = {"adam": 1, "adamw": 2, "adagrad": 3}[opt]
+    for t in (1, 7, 100000):
+        counts = (C.c_uint64 * 3)()
+        groups = 1 << 22
+        rc = lib.volta_b200_update_selftest(code, 20240 + t, groups, wide, t, C.byref(counts))
+        assert rc == 0
+        assert counts[1] + counts[2] == groups
+        assert counts[0] == 0, (opt, wide, t, list(counts))
+        if wide:
+            assert counts[1] > 1000 and counts[2] > groups // 2
+        else:
+            # (Adagrad's sum is drawn with either sign here; a negative one sends its group to the library path)
+            assert counts[1] > groups * (0.02 if opt == "adagrad" else 0.9)

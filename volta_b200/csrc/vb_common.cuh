@@ -275,6 +275,10 @@ cudaError_t launch_gemv_rows(const float *x, const float *W, long long m, long l
 cudaError_t launch_optimizer(int optimizer, float *p, float *s1, float *s2, const float *g, long long n,
                              long long n_decay, const StepScalars *sc, cudaStream_t s);
 cudaError_t launch_set_scalars(StepScalars *dst, StepScalars v, cudaStream_t s);
+// update_rows (the persistent step kernel's optimizer) against update_one on `groups` seeded groups of four
+// elements; counts[0..2] (device, zeroed by the caller) += differing elements, core groups, library groups.
+cudaError_t launch_update_selftest(int optimizer, unsigned long long seed, long long groups, int wide, const StepScalars &sc,
+                                   unsigned long long *counts, cudaStream_t s);
 // first_bad[0..3] = min(first_bad[r], smallest index of an inf/NaN in g[0..n_grads), p, s1, s2 [0..n));
 // null regions are skipped; the caller presets the four words to all ones.
 cudaError_t launch_finite_guard(const float *p, const float *g, const float *s1, const float *s2, long long n,

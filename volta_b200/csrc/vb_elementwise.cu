@@ -389,4 +389,78 @@ cudaError_t launch_mse_seed(float *delta, float *loss_sum, const float *out, con
     return launch_pdl(mse_pass2, dim3(1), dim3(MSE_THREADS), 0, s, loss_sum, (const float *)scratch, nb);
 }
 
+// ---------------------------------------------------------------------------------------
+// Self-check of update_rows (vb_optimizer.cuh: the persistent step kernel's optimizer) against
+// update_one.  Group i of four elements is derived from a 64-bit mix of (seed, i): gradients and moments
+// with random sign and mantissa and an exponent drawn either from the range training produces or from
+// anywhere (so that groups the pre-check sends to the library path occur too), some exactly zero.
+// counts[0] = elements whose p, s1 or s2 differ in any bit, [1] = groups that took the cores, [2] = groups
+// that took the library path.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+    z += 0x9E3779B97F4A7C15ULL;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+    return z ^ (z >> 31);
+}
+__device__ __forceinline__ float operand_from(unsigned long long h, int lo, int span, bool allow_negative) {
+    if ((h >> 58) == 0) return 0.0f;                                   // 1 in 64 exactly zero
+    const unsigned mant = (unsigned)(h & 0x7FFFFFu);
+    const unsigned ex = (unsigned)(127 + lo) + (unsigned)((h >> 23) % (unsigned)span);
+    const unsigned sign = allow_negative ? (unsigned)((h >> 57) & 1u) : 0u;
+    return __uint_as_float((sign << 31) | (ex << 23) | mant);
+}
+template <int OPT>
+__global__ void __launch_bounds__(256) update_selftest_kernel(unsigned long long seed, long long groups, int wide, StepScalars sc,
+                                                              unsigned long long *counts) {
+    unsigned long long diff = 0, fast = 0, slow = 0;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < groups; i += stride) {
+        float pe[4], ge[4], ae[4], be[4];
+        bool ok = core_scalars_ok<OPT>(sc);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const unsigned long long h = mix64(seed + 4ULL * (unsigned long long)i + u);
+            const unsigned long long h2 = mix64(h), h3 = mix64(h2), h4 = mix64(h3);
+            pe[u] = operand_from(h, -8, 8, true);
+            // narrow: gradients 2^-30..2^2, first moments around them, second moments around their squares
+            ge[u] = wide ? operand_from(h2, -126, 253, true) : operand_from(h2, -30, 32, true);
+            ae[u] = wide ? operand_from(h3, -126, 253, true) : operand_from(h3, -34, 36, true);
+            be[u] = wide ? operand_from(h4, -126, 253, false) : operand_from(h4, -70, 72, false);
+            ok = ok && core_operands_ok<OPT>(ae[u], be[u], ge[u], sc);
+        }
+        float4 p[1] = {make_float4(pe[0], pe[1], pe[2], pe[3])}, a[1] = {make_float4(ae[0], ae[1], ae[2], ae[3])},
+               b[1] = {make_float4(be[0], be[1], be[2], be[3])};
+        const float g[1][4] = {{ge[0], ge[1], ge[2], ge[3]}};
+        update_rows<OPT, 1>(p, a, b, g, sc, sc.weight_decay);
+        const float pr[4] = {p[0].x, p[0].y, p[0].z, p[0].w}, ar[4] = {a[0].x, a[0].y, a[0].z, a[0].w},
+                    br[4] = {b[0].x, b[0].y, b[0].z, b[0].w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            float rp = pe[u], ra = ae[u], rb = be[u];
+            update_one<OPT>(rp, ra, rb, ge[u], sc, sc.weight_decay);
+            const bool same = __float_as_uint(rp) == __float_as_uint(pr[u]) && __float_as_uint(ra) == __float_as_uint(ar[u]) &&
+                              __float_as_uint(rb) == __float_as_uint(br[u]);
+            // NaN results compare by bits too; both paths produce them through the same instructions or not at all
+            diff += same ? 0 : 1;
+        }
+        (ok ? fast : slow) += 1;
+    }
+    atomicAdd(&counts[0], diff);
+    atomicAdd(&counts[1], fast);
+    atomicAdd(&counts[2], slow);
+}
+
+cudaError_t launch_update_selftest(int optimizer, unsigned long long seed, long long groups, int wide, const StepScalars &sc,
+                                   unsigned long long *counts, cudaStream_t s) {
+    const int blocks = sm_count() * 8;
+    switch (optimizer) {
+    case VB200_OPT_ADAM: update_selftest_kernel<VB200_OPT_ADAM><<<blocks, 256, 0, s>>>(seed, groups, wide, sc, counts); break;
+    case VB200_OPT_ADAMW: update_selftest_kernel<VB200_OPT_ADAMW><<<blocks, 256, 0, s>>>(seed, groups, wide, sc, counts); break;
+    case VB200_OPT_ADAGRAD: update_selftest_kernel<VB200_OPT_ADAGRAD><<<blocks, 256, 0, s>>>(seed, groups, wide, sc, counts); break;
+    default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
 }  // namespace vb

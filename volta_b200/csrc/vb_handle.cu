@@ -2060,6 +2060,29 @@ int volta_b200_gemm(int32_t layout, int32_t path, float *C, const float *A, cons
     return err == cudaSuccess ? VB200_OK : VB200_ERR_CUDA;
 }
 
+int volta_b200_update_selftest(int32_t optimizer, uint64_t seed, int64_t groups, int32_t wide, uint64_t t, uint64_t counts[3]) {
+    if (!counts || groups <= 0 || t == 0 ||
+        !(optimizer == VB200_OPT_ADAM || optimizer == VB200_OPT_ADAMW || optimizer == VB200_OPT_ADAGRAD)) {
+        set_global_error(VB200_ERR_INVALID, "update_selftest: adam, adamw or adagrad; groups and t positive");
+        return VB200_ERR_INVALID;
+    }
+    StepScalars sc{};
+    sc.lr = 1e-3f; sc.beta1 = 0.9f; sc.beta2 = 0.999f; sc.eps = 1e-8f; sc.weight_decay = 0.01f; sc.momentum = 0.9f;
+    sc.bc1 = 1.0f - powf(sc.beta1, (float)t);
+    sc.bc2 = 1.0f - powf(sc.beta2, (float)t);
+    unsigned long long *d = nullptr;
+    if (cudaMalloc(&d, 3 * sizeof(unsigned long long)) != cudaSuccess) return VB200_ERR_OOM;
+    cudaError_t e = cudaMemset(d, 0, 3 * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = launch_update_selftest(optimizer, seed, groups, wide, sc, d, nullptr);
+    if (e == cudaSuccess) e = cudaMemcpy(counts, d, 3 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+    cudaFree(d);
+    if (e != cudaSuccess) {
+        set_global_error(VB200_ERR_CUDA, std::string("update_selftest: ") + cudaGetErrorString(e));
+        return VB200_ERR_CUDA;
+    }
+    return VB200_OK;
+}
+
 int volta_b200_gemm_route(int32_t layout, int32_t path, int64_t m, int64_t n, int64_t k, int32_t *splits) {
     if (splits) *splits = 1;
     if (m <= 0 || n <= 0 || k <= 0 || layout < GEMM_NN || layout > GEMM_TN) return -VB200_ERR_INVALID;

@@ -113,36 +113,40 @@ __device__ __forceinline__ void load_tile(float *dst, int dst_ld, const float *s
 
 struct Barrier {
     unsigned *count, *abort_word, *status;
+    unsigned phase;   // top bit of *count as of the last barrier this CTA passed (thread 0's copy is the one used)
 };
 
 // Grid-wide barrier on ONE word: CTA 0 adds 2^31 - (G - 1), every other CTA adds 1, so the word's top bit
 // flips exactly when all G have arrived (and its low bits are back where they were: no reset, no second
-// word).  One atomic per CTA, then a spin on the same word.  Bounded: after ~2 s without release the CTA
-// records the failure and nobody waits any more.
+// word).  Per CTA one fire-and-forget reduction, then a spin on the same word until its top bit differs from
+// the phase the CTA remembers (read once at kernel start: the bit cannot flip before this CTA's own first
+// arrival), so that an arrival costs no round trip of its own.  Bounded: after ~2 s without release the CTA
+// records the failure in the status word and raises the abort word, which every spinning CTA looks at now
+// and then; from there on the barriers of this launch fall through after a few hundred polls.
 __device__ __forceinline__ void grid_barrier(Barrier &b) {
     __syncthreads();
     if (threadIdx.x == 0) {
-        if (*reinterpret_cast<volatile unsigned *>(b.abort_word) == 0u) {
-            __threadfence();
-            const unsigned inc = blockIdx.x == 0 ? 0x80000000u - (gridDim.x - 1u) : 1u;
-            const unsigned old = atomicAdd(b.count, inc);
-            unsigned long long t0 = 0;
-            for (unsigned it = 0;; ++it) {
-                if (((old ^ *reinterpret_cast<volatile unsigned *>(b.count)) & 0x80000000u) != 0u) break;
-                if ((it & 1023u) == 1023u) {
-                    if (*reinterpret_cast<volatile unsigned *>(b.abort_word) != 0u) break;
-                    unsigned long long now;
-                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-                    if (t0 == 0) t0 = now;
-                    if (now - t0 > 2000000000ull) {
-                        atomicOr(b.status, ST_GRID_BARRIER);
-                        atomicExch(b.abort_word, 1u);
-                        break;
-                    }
+        __threadfence();
+        const unsigned inc = blockIdx.x == 0 ? 0x80000000u - (gridDim.x - 1u) : 1u;
+        asm volatile("red.global.add.u32 [%0], %1;" ::"l"(b.count), "r"(inc) : "memory");
+        const unsigned before = b.phase;
+        unsigned long long t0 = 0;
+        for (unsigned it = 0;; ++it) {
+            if (((*reinterpret_cast<volatile unsigned *>(b.count)) & 0x80000000u) != before) break;
+            if ((it & 255u) == 255u) {
+                if (*reinterpret_cast<volatile unsigned *>(b.abort_word) != 0u) break;
+                unsigned long long now;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (t0 == 0) t0 = now;
+                if (now - t0 > 2000000000ull) {
+                    atomicOr(b.status, ST_GRID_BARRIER);
+                    atomicExch(b.abort_word, 1u);
+                    break;
                 }
             }
-            __threadfence();
         }
+        b.phase = before ^ 0x80000000u;
+        __threadfence();
     }
     __syncthreads();
 }
@@ -254,6 +258,7 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
     bar.count = A.barrier;
     bar.abort_word = A.barrier + 2;
     bar.status = A.status;
+    bar.phase = tid == 0 ? (*reinterpret_cast<volatile unsigned *>(A.barrier) & 0x80000000u) : 0u;
 
     // ---- ask for this CTA's share of parameters and optimizer state to be brought into L2
     if (tid < 3) {
@@ -539,22 +544,28 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                             }
                             continue;
                         }
+                        if (vec) {
+                            // all rows of the thread side by side (the optimizer's chains interleave), then the stores
+                            float4 pv[RPT];
 #pragma unroll
-                        for (int i = 0; i < RPT; ++i) {
-                            const int kk = kk0 + i;
-                            if (kk >= krows) continue;
-                            const long long e = L.off_w + (long long)(k0 + kk) * c + nb + 4 * ng;
-                            if (vec) {
-                                float4 pv = *reinterpret_cast<const float4 *>(ws + kk * LD + 4 * ng);   // pre-update W
-                                update_one<OPT>(pv.x, st1[i].x, st2[i].x, g[i][0], sc, wd);
-                                update_one<OPT>(pv.y, st1[i].y, st2[i].y, g[i][1], sc, wd);
-                                update_one<OPT>(pv.z, st1[i].z, st2[i].z, g[i][2], sc, wd);
-                                update_one<OPT>(pv.w, st1[i].w, st2[i].w, g[i][3], sc, wd);
-                                *reinterpret_cast<float4 *>(A.params + e) = pv;
+                            for (int i = 0; i < RPT; ++i)   // pre-update W from the tile (zero rows beyond krows)
+                                pv[i] = *reinterpret_cast<const float4 *>(ws + (kk0 + i) * LD + 4 * ng);
+                            update_rows<OPT, RPT>(pv, st1, st2, g, sc, wd);
+#pragma unroll
+                            for (int i = 0; i < RPT; ++i) {
+                                if (kk0 + i >= krows) continue;
+                                const long long e = L.off_w + (long long)(k0 + kk0 + i) * c + nb + 4 * ng;
+                                *reinterpret_cast<float4 *>(A.params + e) = pv[i];
                                 if (HAS1) *reinterpret_cast<float4 *>(A.s1 + e) = st1[i];
                                 if (HAS2) *reinterpret_cast<float4 *>(A.s2 + e) = st2[i];
                                 *reinterpret_cast<float4 *>(A.grads + e) = make_float4(g[i][0], g[i][1], g[i][2], g[i][3]);
-                            } else {
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < RPT; ++i) {
+                                const int kk = kk0 + i;
+                                if (kk >= krows) continue;
+                                const long long e = L.off_w + (long long)(k0 + kk) * c + nb + 4 * ng;
 #pragma unroll
                                 for (int u = 0; u < 4; ++u)
                                     if (4 * ng + u < nn)
