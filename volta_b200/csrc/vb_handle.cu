@@ -1214,10 +1214,12 @@ int build(vb200_handle *h) {
                 h->ss_grid = grid;
                 h->ss_cluster = cl;
                 h->ss_forward = true;
-                // where it applies by default: up to 4 M parameters.  Beyond that the per-kernel schedule's
-                // streaming optimizer (64 warps per SM against this kernel's 8) makes up for its launches
-                // (measured on the 6.3 M-parameter configuration: both take 0.22 ms per step).
-                if (B <= 64 && (c.step_kernel == 2 || h->n_params_padded <= (4LL << 20))) {
+                // where it applies by default: up to 8 M parameters (VOLTA_B200_SMALL_STEP_MAX_PARAMS).  Beyond
+                // that the per-kernel schedule's streaming optimizer (64 warps per SM against this kernel's 8)
+                // makes up for its launches (measured on the 6.3 M-parameter configuration: 0.205 ms per step
+                // here, 0.224 ms through the per-kernel schedule).
+                static const long long max_params = [] { const char *e = getenv("VOLTA_B200_SMALL_STEP_MAX_PARAMS"); return e ? atoll(e) : (8LL << 20); }();
+                if (B <= 64 && (c.step_kernel == 2 || h->n_params_padded <= max_params)) {
                     h->small_step = true;
                     h->fuse_sgd = false;
                 }
