@@ -434,9 +434,9 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                 const float *ds = bufA + (t & 1) * BUF_A, *ws = bufB + (t & 1) * BUF_B;
                 const int nb = n0 + t * KT, nn = min(KT, n0 + nlen - nb);
                 // ---- bias gradient: of the NA clusters that own rows of this W, cluster j takes the tile's columns
-                // j, j + NA, ... (all of them hold the same delta tile).  The sums are taken by warp 0 behind its first
+                // j, j + NA, ... (all of them hold the same delta tile).  The sums are taken by warp 0 inside its first
                 // block of products (lane l: columns 4l .. 4l+3, rows ascending); the parameter and its state are asked
-                // for there and used at the end of the tile.
+                // for behind it and used at the end of the tile.
                 float db_g = 0.0f, db_p = 0.0f, db_s1 = 0.0f, db_s2 = 0.0f;
                 long long db_e = -1;
                 auto db_finish = [&]() {
@@ -474,6 +474,8 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                                 if (HAS2) st2[i] = load_early(A.s2 + e);
                             }
                         }
+                        const bool do_db = kgp == 0 && pass == 0;
+                        float cs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 4
                         for (int b = 0; b < B; ++b) {
                             float a4[RPT];
@@ -494,14 +496,11 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                                 g[i][2] = fmaf(a4[i], dv.z, g[i][2]);
                                 g[i][3] = fmaf(a4[i], dv.w, g[i][3]);
                             }
-                        }
-                        if (kgp == 0 && pass == 0) {
-                            float cs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 8
-                            for (int b = 0; b < B; ++b) {
-                                const float4 dv = *reinterpret_cast<const float4 *>(ds + b * LD + 4 * ng);
+                            if (do_db) {   // warp 0: the column sums of the delta tile ride along (rows ascending)
                                 cs[0] += dv.x; cs[1] += dv.y; cs[2] += dv.z; cs[3] += dv.w;
                             }
+                        }
+                        if (do_db) {
                             const int NA = ceil_div(r, kcl);   // clusters with krows > 0
 #pragma unroll
                             for (int u = 0; u < 4; ++u) {
