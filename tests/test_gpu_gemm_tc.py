@@ -104,3 +104,30 @@ def test_cta_pair_gemm_exact_on_integers_and_close_on_reals(layout, m, n, k):
     ref = A.astype(np.float64) @ B.astype(np.float64)
     bound = np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64)
     assert float((np.abs(got - ref) / (bound + 1e-30)).max()) <= 2.0e-6
+
+
+# The CTA-pair kernel with its own (unsplit) epilogue on ragged edges in every dimension: K short enough that no
+# split is taken, so that the masked, staged stores of the kernel itself run in all three layouts.
+PAIR_RAGGED = [(2300, 2308, 480), (516, 772, 260), (260, 1028, 36)]
+
+
+@pytest.mark.parametrize("layout", [NT, NN, TN])
+@pytest.mark.parametrize("m,n,k", PAIR_RAGGED)
+def test_pair_kernel_unsplit_on_ragged_shapes(layout, m, n, k):
+    import ctypes as C
+    lib = load_library()
+    splits = C.c_int32()
+    assert lib.volta_b200_gemm_route(layout, 3, m, n, k, C.byref(splits)) == 2 and splits.value == 1
+    rs = np.random.RandomState(m + n + k + layout)
+    A = rs.randint(-4, 5, size=(m, k)).astype(np.float32)
+    B = rs.randint(-4, 5, size=(k, n)).astype(np.float32)
+    rc, got = _run(layout, 3, A, B)
+    assert rc == 0
+    assert np.array_equal(got, (A.astype(np.float64) @ B.astype(np.float64)).astype(np.float32))
+    A = rs.randn(m, k).astype(np.float32)
+    B = rs.randn(k, n).astype(np.float32)
+    rc, got = _run(layout, 3, A, B)
+    ref = A.astype(np.float64) @ B.astype(np.float64)
+    bound = np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64)
+    assert float(np.max(np.abs(got - ref) / (bound + 1e-30))) <= 1.0e-6
+

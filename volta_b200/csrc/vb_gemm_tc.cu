@@ -83,7 +83,7 @@ Route choose_route(long long m, long long n, long long k, bool force_pair, bool 
     // candidates in order of preference: fewer splits first, the pair kernel first; a later one must be
     // strictly faster to be taken, and by 3 % if it splits further (its slabs cost arena memory)
     for (int s = 1; s <= (split_on && may_split ? 8 : 1); ++s) {
-        if (s > 1 && kblocks / s < 32) break;   // a split keeps at least 1024 of K
+        if (s > 1 && kblocks / s < 16) break;   // a split keeps at least 512 of K
         for (int p = pair_ok ? 1 : 0; p >= ((force_pair && pair_ok) ? 1 : 0); --p) {
             const double t = candidate_us(p != 0, s, m, n, k);
             if (best_t < 0.0 || t < best_t * (s > best.splits ? 0.97 : 1.0)) {
