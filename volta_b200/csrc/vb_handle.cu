@@ -1000,7 +1000,8 @@ void make_plan(const vb200_config &c, ArenaPlan &pl, PlanIdx &ix, std::vector<in
     // exchange by copy: rank q's copy engines write its gradients (and loss sum) into slot q
     if (c.dp_exchange == VB200_DP_PEER_COPY && (c.world_size > 1 || c.force_dp == 1))
         ix.recv = pl.add("dp_receive_slots", (int64_t)(c.world_size > 1 ? c.world_size : 1) * (P + 64) * 4, 0, end, true);
-    long long mse = std::max<long long>(loss_blocks((long long)B * L[n]), 256);   // >= one loss partial per CTA of the persistent step
+    // >= one loss partial per CTA of the persistent step, and behind them its per-cluster partial outputs [<= 160][64]
+    long long mse = std::max<long long>(loss_blocks((long long)B * L[n]), 256 + 64 * 160);
     if (clip) {  // block partials of every delta's sum of squares
         long long all = 0;
         for (int i = 0; i < n; ++i) all += loss_blocks((long long)B * L[i + 1]);

@@ -56,7 +56,8 @@ constexpr int LDW = WMAX + 4;   // pitch of a [.. x WMAX] tile
 constexpr int BUF_A = BM * LD;          // activation / delta tile [BM][LD]
 constexpr int BUF_B = KT * LDW;         // W tile: forward [KT][LDW]; backward [WMAX][LD] (8448 <= 8704)
 constexpr int PART = T * 16;            // every thread's 4 x 4 partial sums
-constexpr int SMEM_FLOATS = 2 * BUF_A + 2 * BUF_B + BM * LDW + PART + 64;
+constexpr int RECV = BM * WMAX;          // the cluster's partials of this CTA's rows: [S][BM / S][<= WMAX]
+constexpr int SMEM_FLOATS = 2 * BUF_A + 2 * BUF_B + BM * LDW + PART + RECV + 64;
 constexpr unsigned ST_GRID_BARRIER = 128u;
 
 
@@ -198,27 +199,30 @@ __device__ __forceinline__ TileMap tile_map(int width) {
     return m;
 }
 
-// The KG partial tiles of this CTA, part[kg][row][col], summed in k-group order into the first one.
-__device__ __forceinline__ void fold_kgroups(float *part, int KG, int PLD) {
+// The KG partial tiles of this CTA, part[kg][row][col], are summed in k-group order and every row of the sum is
+// PUSHED into the shared memory of the CTA that owns the row (rows RB*o .. RB*o + RB - 1 belong to rank o), into
+// this rank's slot there: recv[rank][row - RB*o][col].  After the cluster barrier that follows, an owner finds all
+// S ranks' partials of its rows in its own shared memory (no remote read on the critical path).
+__device__ __forceinline__ void fold_and_push(cg::cluster_group &cluster, const float *part, float *recv, int KG, int PLD, int S,
+                                              int q) {
     __syncthreads();
-    if (KG > 1) {
-        const int n4 = (BM * PLD) >> 2;
-        for (int e = threadIdx.x; e < n4; e += T) {
-            float4 v = reinterpret_cast<const float4 *>(part)[e];
-            for (int g = 1; g < KG; ++g) {
-                const float4 w = reinterpret_cast<const float4 *>(part + g * BM * PLD)[e];
-                v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
-            }
-            reinterpret_cast<float4 *>(part)[e] = v;
+    const int RB = BM / S, n4 = (BM * PLD) >> 2, p4 = PLD >> 2;
+    for (int e = threadIdx.x; e < n4; e += T) {
+        float4 v = reinterpret_cast<const float4 *>(part)[e];
+        for (int g = 1; g < KG; ++g) {
+            const float4 w = reinterpret_cast<const float4 *>(part + g * BM * PLD)[e];
+            v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
         }
+        const int row = e / p4, c4 = e - row * p4, owner = row / RB, rl = row - owner * RB;
+        float *dst = cluster.map_shared_rank(recv, owner) + ((q * RB + rl) * PLD + (c4 << 2));
+        *reinterpret_cast<float4 *>(dst) = v;
     }
 }
-// Element `idx` of every rank's folded tile, added in rank order.  All remote loads are issued before
-// the first addition, so their latencies overlap.
-__device__ __forceinline__ float gather_ranks(cg::cluster_group &cluster, float *part, int S, int idx) {
+// Element (row_local, col) of the S ranks' partials in this CTA's receive slots, added in rank order.
+__device__ __forceinline__ float sum_ranks(const float *recv, int S, int RB, int PLD, int row_local, int col) {
     float v[8];
 #pragma unroll
-    for (int p = 0; p < 8; ++p) v[p] = p < S ? cluster.map_shared_rank(part, p)[idx] : 0.0f;
+    for (int p = 0; p < 8; ++p) v[p] = p < S ? recv[((p * RB) + row_local) * PLD + col] : 0.0f;
     float sum = v[0];
 #pragma unroll
     for (int p = 1; p < 8; ++p)
@@ -246,7 +250,8 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
     float *bufB = bufA + 2 * BUF_A;            // [2][BUF_B]
     float *actc = bufB + 2 * BUF_B;            // backward: act slice [BM][LDW]
     float *part = actc + BM * LDW;             // [PART]
-    float *red = part + PART;                  // [64]
+    float *recv = part + PART;                 // [RECV]
+    float *red = recv + RECV;                  // [64]
 
     cg::cluster_group cluster = cg::this_cluster();
     const int S = (int)cluster.num_blocks(), q = (int)cluster.block_rank();
@@ -276,8 +281,16 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
     }
     const StepScalars &sc = A.scalars;
 
+    // A width-one output layer (every regression head) is not given phases of its own: its forward is a dot
+    // product per row, which the clusters take over their slabs of the last hidden layer while they still hold
+    // them (partials to zpart, summed in cluster order behind the next grid barrier by whoever needs the
+    // result), and its backward is elementwise in dX and a 64-term sum per weight, which the tail phase below
+    // does without tiles, shared-memory reductions or cluster barriers.  Two grid phases less per step.
+    const bool fuse_tail = !A.forward_only && n >= 2 && A.L[n - 1].c == 1;
+    float *zpart = A.loss_partials + 256;   // [cluster][BM]
+
     // =================================================================================== forward
-    for (int li = 0; li < n; ++li) {
+    for (int li = 0; li < (fuse_tail ? n - 1 : n); ++li) {
         const SmallStepLayer &L = A.L[li];
         const int r = L.r, c = L.c;
         const int ncl = round4(ceil_div(c, NC));                 // columns per cluster (<= WMAX, checked on the host)
@@ -345,19 +358,22 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                     *reinterpret_cast<float4 *>(part + ((tm.kg * BM) + tm.rg + 16 * i) * PLD + 4 * tm.cg) =
                         make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
             }
-            fold_kgroups(part, tm.KG, PLD);
+            fold_and_push(cluster, part, recv, tm.KG, PLD, S, q);
             cluster.sync();
             // this CTA adds the S ranks' tiles of its rows in rank order and finishes the elements
             const float *bias = A.params + L.off_b;
             for (int e = tid; e < RB * ncols; e += T) {
-                const int row = q * RB + e / ncols, col = e % ncols;
+                const int rl = e / ncols, row = q * RB + rl, col = e % ncols;
                 if (row >= B) continue;
-                const float sum = gather_ranks(cluster, part, S, row * PLD + col);
+                const float sum = sum_ranks(recv, S, RB, PLD, rl, col);
                 const long long o = (long long)row * c + n0 + col;
                 const float z = sum + bias[n0 + col];
                 if (!last) {
                     if (L.pre_out) L.pre_out[o] = z;
-                    L.act_out[o] = act_forward(A.act, z);
+                    const float a = act_forward(A.act, z);
+                    L.act_out[o] = a;
+                    // fused tail: this element's term of the output layer's dot product (w_out is a column)
+                    if (fuse_tail && li == n - 2) part[rl * PLD + col] = __fmul_rn(a, A.params[A.L[n - 1].off_w + n0 + col]);
                 } else if (A.forward_only) {
                     L.act_out[o] = z;
                 } else {
@@ -368,7 +384,17 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                     L.delta[o] = __fdiv_rn(__fmul_rn(2.0f, d), A.nt_global);
                 }
             }
-            // (no second cluster barrier: `part` is next written behind the next grid barrier, or never)
+            // (no second cluster barrier: the next pushes into `recv` come behind the next grid barrier, or never)
+            if (fuse_tail && li == n - 2) {
+                // this cluster's partial of every row's output: the terms of the row in column order; cluster 0
+                // starts from the output bias (read here, where nobody writes it)
+                __syncthreads();
+                if (tid < RB && q * RB + tid < B) {
+                    float zp = j == 0 ? A.params[A.L[n - 1].off_b] : 0.0f;
+                    for (int col = 0; col < ncols; ++col) zp = __fadd_rn(zp, part[tid * PLD + col]);
+                    zpart[j * BM + q * RB + tid] = zp;
+                }
+            }
         }
         if (last && A.forward_only) break;   // inference: the outputs are stored, nothing follows
         if (last) {
@@ -384,8 +410,81 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
         }
     }
 
+    // =================================================================================== fused tail
+    if (fuse_tail) {
+        const SmallStepLayer &L = A.L[n - 1];                    // r x 1
+        const SmallStepLayer &P = A.L[n - 2];
+        const int r = L.r;
+        const int kcl = round4(ceil_div(r, NC));
+        const int k0 = j * kcl, krows = min(kcl, r - k0);        // rows of w_out this cluster owns; rank q: kk = q, q + S, ..
+        const int NAf = ceil_div(P.c, round4(ceil_div(P.c, NC)));   // clusters that wrote a partial
+        float *dl = part, *sq = part + BM;                       // seed gradient and squared residual per row
+        grid_barrier(bar);
+        if (tid < BM && (krows > 0 || blockIdx.x == 0)) {
+            float dv = 0.0f, d2 = 0.0f;
+            if (tid < B) {
+                float z = __ldcg(zpart + tid);
+#pragma unroll 8
+                for (int jj = 1; jj < NAf; ++jj) z = __fadd_rn(z, __ldcg(zpart + jj * BM + tid));
+                // MSE and its seed gradient (mlp_train_rust_codegen.rs:793-798)
+                const float d = __fsub_rn(z, A.y[tid]);
+                dv = __fdiv_rn(__fmul_rn(2.0f, d), A.nt_global);
+                d2 = __fmul_rn(d, d);
+                if (blockIdx.x == 0) {
+                    L.act_out[tid] = z;
+                    L.delta[tid] = dv;
+                }
+            }
+            dl[tid] = dv;
+            sq[tid] = d2;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float t = 0.0f;
+            if (blockIdx.x == 0)
+                for (int b = 0; b < B; ++b) t = __fadd_rn(t, sq[b]);
+            A.loss_partials[blockIdx.x] = t;
+        }
+        if (krows > 0) {
+            const float wd = OPT == VB200_OPT_ADAMW ? sc.weight_decay : 0.0f;
+            // dX of this rank's rows of w_out: delta_prev[b][k] = (delta[b] * w[k]) * f'(saved[b][k])
+            const int nk = (krows - q + S - 1) / S;
+            for (int e = tid; e < B * nk; e += T) {
+                const int b = e / nk, k = k0 + q + S * (e - b * nk);
+                const long long o = (long long)b * r + k;
+                L.delta_prev[o] = __fmul_rn(__fmul_rn(dl[b], A.params[L.off_w + k]), act_backward(A.act, __ldcg(L.saved_prev + o)));
+            }
+            __syncthreads();   // every read of the pre-update w_out rows is done
+            // dW of the same rows (warp per row; lane l: batch rows l and l + 32, then a fixed shuffle tree), update
+            const int lane = tid & 31;
+            for (int kk = q + S * (tid >> 5); kk < krows; kk += S * (T / 32)) {
+                const int k = k0 + kk;
+                const float a0 = lane < B ? __ldcg(L.act_in + (long long)lane * r + k) : 0.0f;
+                const float a1 = lane + 32 < B ? __ldcg(L.act_in + (long long)(lane + 32) * r + k) : 0.0f;
+                float v = fmaf(a1, dl[lane + 32], __fmul_rn(a0, dl[lane]));
+#pragma unroll
+                for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) {
+                    const long long e = L.off_w + k;
+                    update_elem<OPT>(A.params + e, A.s1 + e, A.s2 + e, A.grads + e, v, sc, wd);
+                }
+            }
+        }
+        if (blockIdx.x == 0 && (tid >> 5) == T / 32 - 1) {
+            // the output bias: sum of the seed gradients (nobody reads the bias in this phase)
+            const int lane = tid & 31;
+            float v = __fadd_rn(dl[lane], dl[lane + 32]);
+#pragma unroll
+            for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) {
+                const long long e = L.off_b;
+                update_elem<OPT>(A.params + e, A.s1 + e, A.s2 + e, A.grads + e, v, sc, 0.0f);
+            }
+        }
+    }
+
     // =================================================================================== backward
-    for (int li = A.forward_only ? -1 : n - 1; li >= 0; --li) {
+    for (int li = A.forward_only ? -1 : (fuse_tail ? n - 2 : n - 1); li >= 0; --li) {
         const SmallStepLayer &L = A.L[li];
         const int r = L.r, c = L.c;
         const int kcl = round4(ceil_div(r, NC));                 // rows of W per cluster (<= WMAX)
@@ -601,16 +700,16 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
 #pragma unroll
                         for (int u = 0; u < 4; ++u) part[((tm.kg * BM) + tm.rg + 16 * i) * PLD + tm.cg + tm.CG * u] = acc[i][u];
                 }
-                fold_kgroups(part, tm.KG, PLD);
+                fold_and_push(cluster, part, recv, tm.KG, PLD, S, q);
                 cluster.sync();
                 for (int e = tid; e < RB * krows; e += T) {
-                    const int row = q * RB + e / krows, kk = e % krows;
+                    const int rl = e / krows, row = q * RB + rl, kk = e % krows;
                     if (row >= B) continue;
-                    const float sum = gather_ranks(cluster, part, S, row * PLD + kk);
+                    const float sum = sum_ranks(recv, S, RB, PLD, rl, kk);
                     const long long o = (long long)row * r + k0 + kk;
                     L.delta_prev[o] = sum * act_backward(A.act, __ldcg(L.saved_prev + o));
                 }
-                // (no second cluster barrier: the next phase writes `part` behind its grid barrier)
+                // (no second cluster barrier: the next phase's pushes come behind its grid barrier)
             }
         }
     }
@@ -630,7 +729,7 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
             __threadfence_system();
         }
     }
-    cluster.sync();   // no CTA leaves while a peer may still read its shared memory
+    cluster.sync();   // no CTA leaves while a peer may still write into its shared memory
 }
 
 bool g_smem_set[kMaxDevices][5] = {};
