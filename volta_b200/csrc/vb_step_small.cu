@@ -420,12 +420,18 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
         const int NAf = ceil_div(P.c, round4(ceil_div(P.c, NC)));   // clusters that wrote a partial
         float *dl = part, *sq = part + BM;                       // seed gradient and squared residual per row
         grid_barrier(bar);
-        if (tid < BM && (krows > 0 || blockIdx.x == 0)) {
+        const bool wanted = krows > 0 || blockIdx.x == 0;
+        float *zz = bufA;   // [NAf][BM]: all partials, fetched by the whole CTA at once (one L2 latency, not NAf / 8)
+        if (wanted) {
+#pragma unroll 4
+            for (int e = tid; e < NAf * BM; e += T) zz[e] = __ldcg(zpart + e);
+        }
+        __syncthreads();
+        if (tid < BM && wanted) {
             float dv = 0.0f, d2 = 0.0f;
             if (tid < B) {
-                float z = __ldcg(zpart + tid);
-#pragma unroll 8
-                for (int jj = 1; jj < NAf; ++jj) z = __fadd_rn(z, __ldcg(zpart + jj * BM + tid));
+                float z = zz[tid];
+                for (int jj = 1; jj < NAf; ++jj) z = __fadd_rn(z, zz[jj * BM + tid]);
                 // MSE and its seed gradient (mlp_train_rust_codegen.rs:793-798)
                 const float d = __fsub_rn(z, A.y[tid]);
                 dv = __fdiv_rn(__fmul_rn(2.0f, d), A.nt_global);
@@ -441,8 +447,12 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
         __syncthreads();
         if (tid == 0) {
             float t = 0.0f;
-            if (blockIdx.x == 0)
+            if (blockIdx.x == 0) {
+                // the loss is this CTA's alone here: published now, where nobody waits for it
                 for (int b = 0; b < B; ++b) t = __fadd_rn(t, sq[b]);
+                *A.loss_sum = t;
+                if (A.host_loss) *reinterpret_cast<volatile float *>(A.host_loss) = t;
+            }
             A.loss_partials[blockIdx.x] = t;
         }
         if (krows > 0) {
@@ -511,6 +521,11 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
             issue_w(0);
         }
         grid_barrier(bar);
+        if (li == 0 && blockIdx.x == 0 && tid == 0 && A.host_status) {
+            // the step's last barrier: CTA 0 passed every one, so no CTA can still be about to give up on one and
+            // the status word is final; published here, where nobody waits for it
+            *reinterpret_cast<volatile unsigned *>(A.host_status) = *reinterpret_cast<volatile unsigned *>(A.status);
+        }
         if (krows > 0) {
             float acc[4][4];
 #pragma unroll
@@ -713,7 +728,7 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
             }
         }
     }
-    if (blockIdx.x == 0 && !A.forward_only) {
+    if (blockIdx.x == 0 && !A.forward_only && !fuse_tail) {
         // The loss: every CTA's partial (final since the barrier behind the last forward layer), added in CTA
         // order.  Done here, where nobody waits for CTA 0: warp 0 fetches the partials in parallel, thread 0 adds.
         float *lp = bufA;   // the staging buffers are idle by now
@@ -724,9 +739,6 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
             for (unsigned b = 0; b < gridDim.x; ++b) t += lp[b];
             *A.loss_sum = t;
             if (A.host_loss) *reinterpret_cast<volatile float *>(A.host_loss) = t;
-            // CTA 0 passed every barrier, so no other CTA can still be about to give up on one: the status word is final
-            if (A.host_status) *reinterpret_cast<volatile unsigned *>(A.host_status) = *reinterpret_cast<volatile unsigned *>(A.status);
-            __threadfence_system();
         }
     }
     cluster.sync();   // no CTA leaves while a peer may still write into its shared memory
