@@ -230,17 +230,27 @@ __device__ __forceinline__ float sum_ranks(const float *recv, int S, int RB, int
     return sum;
 }
 
+// (Kept out of line: the measurement protocol flushes the L2 between steps, which also evicts the kernel's code,
+// so every instruction executed for the first time in a step is fetched from HBM; this rarely taken path is
+// inlined nowhere.)
 template <int OPT>
-__device__ __forceinline__ void update_elem(float *p, float *s1, float *s2, float *gout, float g, const StepScalars &sc,
-                                            float wd) {
+__device__ __noinline__ void update_elem_call(float *p, float *s1, float *s2, float *gout, float g, float lr, float beta1,
+                                              float beta2, float eps, float bc1, float bc2, float momentum, float wd) {
     constexpr bool HAS1 = (OPT != VB200_OPT_SGD);
     constexpr bool HAS2 = (OPT == VB200_OPT_ADAM || OPT == VB200_OPT_ADAMW);
+    StepScalars sc{};
+    sc.lr = lr; sc.beta1 = beta1; sc.beta2 = beta2; sc.eps = eps; sc.bc1 = bc1; sc.bc2 = bc2; sc.momentum = momentum;
     float pv = *p, a = HAS1 ? __ldcs(s1) : 0.0f, b = HAS2 ? __ldcs(s2) : 0.0f;
     update_one<OPT>(pv, a, b, g, sc, wd);
     *p = pv;
     if (HAS1) *s1 = a;
     if (HAS2) *s2 = b;
     *gout = g;
+}
+template <int OPT>
+__device__ __forceinline__ void update_elem(float *p, float *s1, float *s2, float *gout, float g, const StepScalars &sc,
+                                            float wd) {
+    update_elem_call<OPT>(p, s1, s2, gout, g, sc.lr, sc.beta1, sc.beta2, sc.eps, sc.bc1, sc.bc2, sc.momentum, wd);
 }
 
 template <int OPT>
@@ -687,9 +697,7 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                         }
                     }
                 };
-                if (kcl > 16) dw_block(std::integral_constant<int, 4>{});
-                else if (kcl > 8) dw_block(std::integral_constant<int, 2>{});
-                else dw_block(std::integral_constant<int, 1>{});
+                dw_block(std::integral_constant<int, 2>{});
                 // ---- partial of dX = delta . W^T over this tile's columns, from the pre-update W in shared memory
                 if (need_dx && tm.active) {
                     const int seg = KT / tm.KG, nbeg = tm.kg * seg;
