@@ -52,6 +52,14 @@ SHAPES = [
     ([100, 2100, 36, 7], 61),               # close to the widest layer the kernel takes; ragged batch
     ([64, 64], 1),                          # one layer, one row
     ([300, 20, 300, 20, 4], 33),
+    # width-one outputs, which get no phases of their own: behind the FIRST layer (no barrier ahead of the partial
+    # dot products), behind the widest hidden layer the kernel takes (16 rows of the output weights per CTA), behind
+    # a hidden layer narrower than the cluster count (most clusters write no partial), a ragged batch, and a
+    # single-layer model (nothing to fuse into: the output layer keeps its own phases)
+    ([40, 2100, 1], 61),
+    ([128, 24, 1], 5),
+    ([96, 160, 130, 1], 64),
+    ([70, 1], 9),
 ]
 
 
