@@ -296,7 +296,7 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
     // them (partials to zpart, summed in cluster order behind the next grid barrier by whoever needs the
     // result), and its backward is elementwise in dX and a 64-term sum per weight, which the tail phase below
     // does without tiles, shared-memory reductions or cluster barriers.  Two grid phases less per step.
-    const bool fuse_tail = !A.forward_only && n >= 2 && A.L[n - 1].c == 1;
+    const bool fuse_tail = n >= 2 && A.L[n - 1].c == 1;
     float *zpart = A.loss_partials + 256;   // [cluster][BM]
 
     // =================================================================================== forward
@@ -430,7 +430,8 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
         const int NAf = ceil_div(P.c, round4(ceil_div(P.c, NC)));   // clusters that wrote a partial
         float *dl = part, *sq = part + BM;                       // seed gradient and squared residual per row
         grid_barrier(bar);
-        const bool wanted = krows > 0 || blockIdx.x == 0;
+        // (inference: only the outputs are wanted, and only CTA 0 writes them)
+        const bool wanted = A.forward_only ? blockIdx.x == 0 : (krows > 0 || blockIdx.x == 0);
         float *zz = bufA;   // [NAf][BM]: all partials, fetched by the whole CTA at once (one L2 latency, not NAf / 8)
         if (wanted) {
 #pragma unroll 4
@@ -442,20 +443,24 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
             if (tid < B) {
                 float z = zz[tid];
                 for (int jj = 1; jj < NAf; ++jj) z = __fadd_rn(z, zz[jj * BM + tid]);
-                // MSE and its seed gradient (mlp_train_rust_codegen.rs:793-798)
-                const float d = __fsub_rn(z, A.y[tid]);
-                dv = __fdiv_rn(__fmul_rn(2.0f, d), A.nt_global);
-                d2 = __fmul_rn(d, d);
-                if (blockIdx.x == 0) {
+                if (A.forward_only) {
                     L.act_out[tid] = z;
-                    L.delta[tid] = dv;
+                } else {
+                    // MSE and its seed gradient (mlp_train_rust_codegen.rs:793-798)
+                    const float d = __fsub_rn(z, A.y[tid]);
+                    dv = __fdiv_rn(__fmul_rn(2.0f, d), A.nt_global);
+                    d2 = __fmul_rn(d, d);
+                    if (blockIdx.x == 0) {
+                        L.act_out[tid] = z;
+                        L.delta[tid] = dv;
+                    }
                 }
             }
             dl[tid] = dv;
             sq[tid] = d2;
         }
         __syncthreads();
-        if (tid == 0) {
+        if (tid == 0 && !A.forward_only) {
             float t = 0.0f;
             if (blockIdx.x == 0) {
                 // the loss is this CTA's alone here: published now, where nobody waits for it
@@ -465,7 +470,7 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
             }
             A.loss_partials[blockIdx.x] = t;
         }
-        if (krows > 0) {
+        if (krows > 0 && !A.forward_only) {
             const float wd = OPT == VB200_OPT_ADAMW ? sc.weight_decay : 0.0f;
             // dX of this rank's rows of w_out: delta_prev[b][k] = (delta[b] * w[k]) * f'(saved[b][k])
             const int nk = (krows - q + S - 1) / S;
@@ -490,7 +495,7 @@ __global__ void __launch_bounds__(T, 1) small_step_kernel(const __grid_constant_
                 }
             }
         }
-        if (blockIdx.x == 0 && (tid >> 5) == T / 32 - 1) {
+        if (blockIdx.x == 0 && (tid >> 5) == T / 32 - 1 && !A.forward_only) {
             // the output bias: sum of the seed gradients (nobody reads the bias in this phase)
             const int lane = tid & 31;
             float v = __fadd_rn(dl[lane], dl[lane + 32]);
