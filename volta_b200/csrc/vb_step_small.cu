@@ -9,15 +9,19 @@
 //
 // Work split.  Forward layer i (act[B x r] . W[r x c]): cluster j owns a slab of output columns, its S
 // CTAs split the r input features; each CTA multiplies its [B x r/S] slice by its [r/S x cols] block,
-// and the S partial results are added in rank order through distributed shared memory by the CTA
-// that owns the rows (bias, activation, and for the last layer the loss and the seed gradient are
-// applied there).  Backward layer i: cluster j owns a slab of W's ROWS, its CTAs split the columns;
+// and the S partial results are added in rank order by the CTA that owns the rows: every CTA pushes the
+// rows of its partial into the owner's shared memory (distributed shared memory), the owner adds its S
+// slots behind the cluster barrier and applies bias, activation, and for the last layer the loss and the
+// seed gradient.  Backward layer i: cluster j owns a slab of W's ROWS, its CTAs split the columns;
 // a CTA computes its block of dW = act^T . delta (the sum over the batch is local), applies the
 // optimizer to exactly that block of W, m and v (streamed once), and computes its partial of
 // dX = delta . W^T from the same block of (pre-update) W; the partials over the column split are
 // again added in rank order through distributed shared memory, times the activation derivative.
-// Cluster 0 also sums the bias gradients.  Nothing is reduced through global memory, there are no
-// atomics on data, and every sum has a fixed order: results are bit-identical from run to run.
+// Bias gradients are column sums that warp 0 takes inside its product loop, spread over the clusters.
+// A width-one output layer gets no phases of its own (see fuse_tail in the kernel); its per-cluster partial
+// dot products (64 floats per cluster) are the only partial sums that pass through global memory, and they
+// are added in cluster order.  There are no atomics on data, and every sum has a fixed order: results are
+// bit-identical from run to run.
 //
 // One launch, nothing else: the step's scalars travel as a kernel argument, inputs that already live on
 // the device are read where they lie, and CTA 0 stores the loss sum and the status word straight into
