@@ -387,6 +387,8 @@ int volta_b200_program_update(vb200_program *p, const vb200_optimizer_config *cf
                               const int32_t *grad_ids, int32_t count, uint64_t step);
 
 const char *volta_b200_version(void);
+/* sizeof(vb200_config) as the library was built with: a binding checks its own mirror of the struct against it. */
+int32_t volta_b200_config_size(void);
 
 #ifdef __cplusplus
 }

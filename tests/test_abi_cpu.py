@@ -29,6 +29,18 @@ def test_library_exports_every_declared_symbol():
     assert b"sm_100a" in lib.volta_b200_version()
 
 
+def test_binding_mirrors_the_configuration_struct_byte_for_byte():
+    """The ctypes mirror and the header's struct have the same size (the loader refuses a library that disagrees),
+    and the mirror names every field of the header in the header's order."""
+    lib = load_library()
+    assert lib.volta_b200_config_size() == C.sizeof(Config)
+    text = open(os.path.join(ROOT, "include", "volta_b200.h")).read()
+    body = text[text.index("typedef struct vb200_config {"):text.index("} vb200_config;")]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    declared = re.findall(r"\b(?:int32_t|float|uint8_t)\s+([a-z_0-9]+)\s*(?:\[[^\]]*\])?\s*;", body)
+    assert declared == [name for name, _ in Config._fields_]
+
+
 def _cfg(cfg, batch=None, world=1):
     c = Config()
     c.n_sizes = len(cfg.layers)

@@ -1282,6 +1282,7 @@ int build(vb200_handle *h) {
 extern "C" {
 
 const char *volta_b200_version(void) { return "volta_b200 0.1 (sm_100a)"; }
+int32_t volta_b200_config_size(void) { return (int32_t)sizeof(vb200_config); }
 
 int volta_b200_create(const vb200_config *cfg, vb200_handle **out) {
     if (out) *out = nullptr;

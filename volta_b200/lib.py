@@ -52,7 +52,7 @@ EXPORTS = [
     "volta_b200_checkpoint_load", "volta_b200_checkpoint_parse", "volta_b200_checkpoint_count", "volta_b200_checkpoint_entry",
     "volta_b200_export_checkpoint", "volta_b200_import_checkpoint", "volta_b200_export_checkpoint_named",
     "volta_b200_import_checkpoint_named", "volta_b200_checkpoint_match", "volta_b200_dp_wait_selftest", "volta_b200_dp_check",
-    "volta_b200_gemm_route", "volta_b200_update_selftest",
+    "volta_b200_gemm_route", "volta_b200_update_selftest", "volta_b200_config_size",
     "volta_b200_program_new", "volta_b200_program_free", "volta_b200_program_error", "volta_b200_program_add",
     "volta_b200_program_mark_output", "volta_b200_program_compile", "volta_b200_program_bind", "volta_b200_program_run",
     "volta_b200_program_fetch", "volta_b200_program_update",
@@ -127,6 +127,7 @@ def load_library():
         "volta_b200_dp_check": (C.c_int, [C.c_char_p, i32, i32, vp, i64, vp]),
         "volta_b200_gemm_route": (C.c_int, [i32, i32, i64, i64, i64, C.POINTER(i32)]),
         "volta_b200_update_selftest": (C.c_int, [i32, C.c_uint64, i64, i32, C.c_uint64, C.POINTER(C.c_uint64 * 3)]),
+        "volta_b200_config_size": (i32, []),
         "volta_b200_program_new": (vp, []),
         "volta_b200_program_free": (None, [vp]),
         "volta_b200_program_error": (C.c_char_p, [vp]),
@@ -142,5 +143,8 @@ def load_library():
         fn = getattr(lib, name)
         fn.restype = res
         fn.argtypes = args
+    if lib.volta_b200_config_size() != C.sizeof(Config):
+        raise VoltaB200Error(-1, "%s was built with a vb200_config of %d bytes, this binding mirrors %d: rebuild the library"
+                             % (path, lib.volta_b200_config_size(), C.sizeof(Config)))
     _lib = lib
     return lib
