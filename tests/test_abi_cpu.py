@@ -98,6 +98,29 @@ def _check_no_live_overlap(total, bufs):
                 assert a[1] + a[2] <= b[1] or b[1] + b[2] <= a[1], (a, b)
 
 
+def test_memory_plan_of_the_copy_exchange_holds_one_receive_slot_per_rank():
+    """dp_exchange = copy: the arena (the one allocation the peers map) also holds world x (parameters + loss slot)
+    floats for the peers' pushes, persistent and overlapping nothing; the other exchanges plan no such region."""
+    world = 4
+    c = _cfg(CONFIGS["c4"], world=world)
+    base_total, _, base = _plan(c)
+    assert not any(b[0] == "dp_receive_slots" for b in base)
+    c.dp_exchange = 2
+    total, _, bufs = _plan(c)
+    _check_no_live_overlap(total, bufs)
+    recv = [b for b in bufs if b[0] == "dp_receive_slots"]
+    assert len(recv) == 1 and recv[0][5] == 1
+    L = list(CONFIGS["c4"].layers)
+    pad64 = lambda v: (v + 63) // 64 * 64
+    P = sum(pad64(r * k) for r, k in zip(L[:-1], L[1:])) + sum(pad64(k) for k in L[1:])   # the flat parameter layout
+    assert world * (P + 64) * 4 <= recv[0][2] < world * (P + 64) * 4 + 1024
+    assert total >= base_total + recv[0][2]
+    c.dp_exchange = 3
+    lib = load_library()
+    t, u = C.c_int64(), C.c_int64()
+    assert lib.volta_b200_plan(C.byref(c), C.byref(t), C.byref(u), None, 0) != 0   # unknown exchange refused
+
+
 def test_memory_plan_with_the_optional_stages():
     """Dropout masks (one byte per hidden element), the LayerNorm parameters and 1/sigma rows, and
     pre-activations for relu once the stored output is no longer the activation's own; the clip keeps
